@@ -1,0 +1,123 @@
+"""tcgen05 GEMM core vs a plain fp32 PyTorch matmul (all four operand layouts, epilogues, groups)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _mk(shape, seed, scale=1.0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(torch.bfloat16).cuda()
+
+
+def _ref(a, b, a_mn, b_mn):
+    af = a.float().t() if a_mn else a.float()
+    bf = b.float() if b_mn else b.float().t()
+    return af @ bf
+
+
+def _check(out, ref, K):
+    tol = 2e-2 * (K ** 0.5) * 0.05 + 1e-2
+    err = (out.float() - ref).abs().max().item()
+    rel = err / (ref.abs().max().item() + 1e-6)
+    assert rel < 1e-2 or err < tol, f"max abs err {err}, rel {rel}"
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (200, 328, 136), (1000, 1280, 1176), (64, 40, 2048)])
+@pytest.mark.parametrize("bn", [0, 64, 128, 256])
+def test_layouts(a_mn, b_mn, M, N, K, bn):
+    from wallx_b200.ops import gemm as G
+
+    if (a_mn and M % 8) or (b_mn and N % 8) or ((not a_mn or not b_mn) and K % 8):
+        pytest.skip("pitch not 16-byte aligned for this layout")
+    a = _mk((K, M) if a_mn else (M, K), 1)
+    b = _mk((K, N) if b_mn else (N, K), 2)
+    out = G.gemm(a, b, a_mn=a_mn, b_mn=b_mn, force_bn=bn)
+    torch.cuda.synchronize()
+    G.check_status()
+    _check(out, _ref(a, b, a_mn, b_mn), K)
+
+
+def test_epilogues():
+    from wallx_b200.ops import gemm as G
+
+    M, N, K = 300, 512, 320
+    a, b = _mk((M, K), 3), _mk((N, K), 4, 0.1)
+    bias = _mk((N,), 5)
+    res = _mk((M, N), 6)
+    ref = a.float() @ b.float().t()
+    out = G.gemm(a, b, bias=bias)
+    _check(out, ref + bias.float(), K)
+    out = G.gemm(a, b, bias=bias, flags=G.ACT_GELU)
+    _check(out, torch.nn.functional.gelu(ref + bias.float()), K)
+    out = G.gemm(a, b, residual=res)
+    _check(out, ref + res.float(), K)
+    out = G.gemm(a, b, flags=G.OUT_FP32)
+    assert out.dtype == torch.float32
+    _check(out, ref, K)
+    acc = torch.ones((M, N), device="cuda", dtype=torch.float32)
+    G.gemm(a, b, out=acc, flags=G.OUT_FP32 | G.ACCUMULATE)
+    _check(acc, ref + 1.0, K)
+    accb = torch.ones((M, N), device="cuda", dtype=torch.bfloat16)
+    G.gemm(a, b, out=accb, flags=G.ACCUMULATE)
+    _check(accb, ref + 1.0, K)
+    G.check_status()
+
+
+def test_swiglu_interleaved():
+    from wallx_b200.ops import gemm as G
+
+    M, I, K = 260, 192, 256
+    a = _mk((M, K), 7)
+    wg, wu = _mk((I, K), 8, 0.1), _mk((I, K), 9, 0.1)
+    w = torch.stack([wg.view(I // 16, 16, K), wu.view(I // 16, 16, K)], dim=1).reshape(2 * I, K).contiguous()
+    raw = torch.empty((M, 2 * I), device="cuda", dtype=torch.bfloat16)
+    h = torch.empty((M, I), device="cuda", dtype=torch.bfloat16)
+    G.launch([G.GemmSpec(a, w, h, out2=raw, flags=G.ACT_SWIGLU)])
+    g = (a.float() @ wg.float().t()).bfloat16().float()
+    u = (a.float() @ wu.float().t()).bfloat16().float()
+    _check(h, torch.nn.functional.silu(g) * u, K)
+    _check(raw.view(M, I // 16, 2, 16)[:, :, 0].reshape(M, I), g, K)
+    _check(raw.view(M, I // 16, 2, 16)[:, :, 1].reshape(M, I), u, K)
+    G.check_status()
+
+
+def test_grouped_two_problems_with_row_map_and_dyn():
+    from wallx_b200.ops import gemm as G
+
+    K, N0, N1 = 256, 384, 128
+    M0, M1 = 200, 72
+    M0p = 256
+    T = M0p + 128
+    x = _mk((T, K), 10)
+    w0, w1 = _mk((N0, K), 11, 0.1), _mk((N1, K), 12, 0.1)
+    out = torch.zeros((T, N0), device="cuda", dtype=torch.bfloat16)
+    dyn0 = torch.tensor([0, M0, 0, K], dtype=torch.int32, device="cuda")
+    dyn1 = torch.tensor([M0p, M1, 0, K], dtype=torch.int32, device="cuda")
+    perm = torch.randperm(T, device="cuda").to(torch.int32)
+    G.launch([
+        G.GemmSpec(x, w0, out, M=T, dyn=dyn0, row_map=perm),
+        G.GemmSpec(x, w1, out, M=T, dyn=dyn1, row_map=perm),
+    ])
+    ref = torch.zeros((T, N0), device="cuda")
+    ref[perm[:M0].long()] = x[:M0].float() @ w0.float().t()
+    r1 = torch.zeros((M1, N0), device="cuda")
+    r1[:, :N1] = x[M0p:M0p + M1].float() @ w1.float().t()
+    ref[perm[M0p:M0p + M1].long()] = r1
+    _check(out, ref, K)
+    G.check_status()
+
+
+def test_k_offset_segment_reduction():
+    """wgrad over a token segment: reduction range [k0, k0+K) of MN-major operands."""
+    from wallx_b200.ops import gemm as G
+
+    T, N, H = 512, 256, 192
+    dy, x = _mk((T, N), 13), _mk((T, H), 14)
+    k0, K = 128, 256
+    out = G.gemm(dy[: k0 + K], x[: k0 + K], a_mn=True, b_mn=True, flags=G.OUT_FP32) * 0  # shape only
+    G.launch([G.GemmSpec(dy[: k0 + K], x[: k0 + K], out, a_mn=True, b_mn=True, K=K, k0=k0, flags=G.OUT_FP32)])
+    ref = dy[k0:k0 + K].float().t() @ x[k0:k0 + K].float()
+    _check(out, ref, K)
+    G.check_status()

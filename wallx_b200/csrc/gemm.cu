@@ -1,0 +1,529 @@
+// tcgen05 / TMEM / TMA GEMM core for sm_100a.
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0      TMA producer   (one lane): global -> 128B-swizzled shared-memory stages
+//   warp 1      MMA issuer     (one lane): tcgen05.mma 128 x BN x 16 per instruction, fp32
+//                                          accumulators in tensor memory, double buffered
+//   warps 2..5  epilogue       (128 thr):  tcgen05.ld -> bias / GELU / SwiGLU / residual /
+//                                          row scatter / accumulate -> global
+// The producer, the issuer and the epilogue are decoupled by mbarriers, so the epilogue of tile
+// i overlaps the main loop of tile i+1. All four operand layouts are handled with UMMA
+// descriptors (K-major and MN-major, 128-byte swizzle), so forward, dgrad and wgrad need no
+// transposed copies. No load uses cluster multicast.
+//
+// Reference parity: csrc/dual_asym_grouped_gemm.cu:49-136 (two problems, four layouts) and the
+// cuBLAS calls behind every nn.Linear in wall_x/model.
+#include "gemm.h"
+#include "ptx.cuh"
+
+#include <mutex>
+
+namespace wx {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kThreads = 192;
+constexpr int kEpiWarp0 = 2;
+
+struct Problem {
+  CUtensorMap tmA;
+  CUtensorMap tmB;
+  void* D;
+  void* D2;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  const int* row_map;
+  const int* dyn;
+  long ldd, ldd2, ldr;
+  int M, N, K, m0, k0, flags;
+};
+
+struct GemmArgs {
+  Problem p[2];
+  int nprob;
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128) ? 6 : 8;
+  static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+struct TileInfo {
+  int prob, mt, nt;
+};
+
+struct Dims {
+  int M[2], K[2], m0[2], k0[2], tiles_m[2], tiles_n[2], tiles[2];
+};
+
+template <int BN>
+__device__ __forceinline__ void load_dims(const GemmArgs& args, Dims& d) {
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (i < args.nprob) {
+      const Problem& p = args.p[i];
+      int M = p.M, K = p.K, m0 = p.m0, k0 = p.k0;
+      if (p.dyn != nullptr) {
+        m0 = p.dyn[0];
+        M = min(p.dyn[1], p.M);
+        k0 = p.dyn[2];
+        K = p.dyn[3];
+      }
+      d.M[i] = M;
+      d.K[i] = K;
+      d.m0[i] = m0;
+      d.k0[i] = k0;
+      d.tiles_m[i] = (M + BM - 1) / BM;
+      d.tiles_n[i] = (p.N + BN - 1) / BN;
+      d.tiles[i] = (K > 0) ? d.tiles_m[i] * d.tiles_n[i] : 0;
+    } else {
+      d.M[i] = d.K[i] = d.m0[i] = d.k0[i] = d.tiles_m[i] = d.tiles_n[i] = d.tiles[i] = 0;
+    }
+  }
+}
+
+__device__ __forceinline__ TileInfo decode_tile(const Dims& d, int t) {
+  TileInfo ti;
+  ti.prob = 0;
+  if (t >= d.tiles[0]) {
+    ti.prob = 1;
+    t -= d.tiles[0];
+  }
+  // m fastest: CTAs that run concurrently share the same few B (weight) tiles in L2.
+  const int tm = d.tiles_m[ti.prob];
+  ti.nt = t / tm;
+  ti.mt = t - ti.nt * tm;
+  return ti;
+}
+
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + C::STAGES;
+  uint64_t* tfull_bar = empty_bar + C::STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == kEpiWarp0) {
+    tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  Dims d;
+  load_dims<BN>(args, d);
+  const int total_tiles = d.tiles[0] + d.tiles[1];
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int i = 0; i < args.nprob; ++i) {
+        tma_prefetch_desc(&args.p[i].tmA);
+        tma_prefetch_desc(&args.p[i].tmB);
+      }
+      int s = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const TileInfo ti = decode_tile(d, t);
+        const Problem& p = args.p[ti.prob];
+        const int m_base = d.m0[ti.prob] + ti.mt * BM;
+        const int n_base = ti.nt * BN;
+        const int k_base = d.k0[ti.prob];
+        const int nkb = (d.K[ti.prob] + BK - 1) / BK;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&empty_bar[s], phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sA = smem + s * C::STAGE_BYTES;
+          uint8_t* sB = sA + C::A_BYTES;
+          mbar_arrive_expect_tx(&full_bar[s], C::STAGE_BYTES);
+          const int kc = k_base + kb * BK;
+          if (!A_MN) {
+            tma_load_2d(sA, &p.tmA, &full_bar[s], kc, m_base);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sA + j * 8192, &p.tmA, &full_bar[s], m_base + 64 * j, kc);
+          }
+          if (!B_MN) {
+            tma_load_2d(sB, &p.tmB, &full_bar[s], kc, n_base);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sB + j * 8192, &p.tmB, &full_bar[s], n_base + 64 * j, kc);
+          }
+          if (++s == C::STAGES) {
+            s = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      int s = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
+        const TileInfo ti = decode_tile(d, t);
+        const int nkb = (d.K[ti.prob] + BK - 1) / BK;
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!mbar_wait(&full_bar[s], phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + C::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = A_MN ? make_smem_desc_sw128(a_addr + k * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(a_addr + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc_sw128(b_addr + k * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(b_addr + k * 32, 16, 1024);
+            tc_mma_bf16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[s]);
+          if (++s == C::STAGES) {
+            s = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) tc_commit(&tfull_bar[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    int it = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+      const TileInfo ti = decode_tile(d, t);
+      const Problem& p = args.p[ti.prob];
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) break;
+      tc_fence_after();
+
+      const int row_in_prob = ti.mt * BM + quarter * 32 + lane;
+      const bool row_ok = row_in_prob < d.M[ti.prob];
+      long drow = static_cast<long>(d.m0[ti.prob]) + row_in_prob;
+      bool store_ok = row_ok;
+      if (row_ok && p.row_map != nullptr) {
+        const int r = p.row_map[drow];
+        store_ok = r >= 0;
+        drow = r;
+      }
+      const int flags = p.flags;
+      const bool swiglu = (flags & GEMM_ACT_SWIGLU) != 0;
+      const bool out_fp32 = (flags & GEMM_OUT_FP32) != 0;
+      const bool accum = (flags & GEMM_ACCUMULATE) != 0;
+      const int n_base = ti.nt * BN;
+      const uint32_t taddr0 = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr0 + c * 32, r);
+        tmem_ld_wait();
+        const int n0 = n_base + c * 32;
+        if (!store_ok || n0 >= p.N) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        const int nvalid = min(32, p.N - n0);
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < nvalid) v[j] += __bfloat162float(p.bias[n0 + j]);
+        }
+        if (swiglu) {
+          // columns [n0, n0+16) are gate, [n0+16, n0+32) are up; N is a multiple of 32 here.
+          if (p.D2 != nullptr) {
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D2) + drow * p.ldd2 + n0);
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              dst[q] = make_uint4(pack_bf16x2(v[8 * q + 0], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                                  pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+          }
+          float h[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            // round gate and up to bf16 first so that the result equals the unfused path
+            const float g = __bfloat162float(__float2bfloat16(v[j]));
+            const float u = __bfloat162float(__float2bfloat16(v[16 + j]));
+            h[j] = silu_f(g) * u;
+          }
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + drow * p.ldd + (n0 >> 1));
+#pragma unroll
+          for (int q = 0; q < 2; ++q)
+            dst[q] = make_uint4(pack_bf16x2(h[8 * q + 0], h[8 * q + 1]), pack_bf16x2(h[8 * q + 2], h[8 * q + 3]),
+                                pack_bf16x2(h[8 * q + 4], h[8 * q + 5]), pack_bf16x2(h[8 * q + 6], h[8 * q + 7]));
+          continue;
+        }
+        if (flags & GEMM_ACT_GELU) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+        }
+        if (p.residual != nullptr) {
+          const __nv_bfloat16* rs = p.residual + drow * p.ldr + n0;
+          if (nvalid == 32 && (p.ldr & 7) == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0) {
+            const uint4* rs4 = reinterpret_cast<const uint4*>(rs);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint4 x = rs4[q];
+              const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(xb[e]);
+                v[8 * q + 2 * e] += f.x;
+                v[8 * q + 2 * e + 1] += f.y;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < nvalid) v[j] += __bfloat162float(rs[j]);
+          }
+        }
+        if (out_fp32) {
+          float* dst = reinterpret_cast<float*>(p.D) + drow * p.ldd + n0;
+          if (nvalid == 32 && (p.ldd & 3) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15) == 0) {
+            float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+              if (accum) {
+                const float4 old = d4[q];
+                o.x += old.x;
+                o.y += old.y;
+                o.z += old.z;
+                o.w += old.w;
+              }
+              d4[q] = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < nvalid) dst[j] = accum ? dst[j] + v[j] : v[j];
+          }
+        } else {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.D) + drow * p.ldd + n0;
+          if (nvalid == 32 && (p.ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15) == 0) {
+            uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (accum) {
+                const uint4 x = d4[q];
+                const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 f = __bfloat1622float2(xb[e]);
+                  v[8 * q + 2 * e] += f.x;
+                  v[8 * q + 2 * e + 1] += f.y;
+                }
+              }
+              d4[q] = make_uint4(pack_bf16x2(v[8 * q + 0], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                                 pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < nvalid) dst[j] = __float2bfloat16(accum ? __bfloat162float(dst[j]) + v[j] : v[j]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag) atomicExch(status, 1);
+  if (warp == kEpiWarp0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// --------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 2-D bf16 tensor map with 128-byte swizzle; `inner` is the contiguous extent.
+bool make_tmap(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t pitch_elems,
+               uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {pitch_elems * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+int num_sms() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+int launch_t(const GemmArgs& args, int grid, cudaStream_t stream, int* status) {
+  using C = Cfg<BN>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set = true;
+  }
+  kern<<<grid, kThreads, C::SMEM_BYTES, stream>>>(args, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <int BN>
+int launch_bn(const GemmArgs& args, bool a_mn, bool b_mn, int grid, cudaStream_t stream, int* status) {
+  if (!a_mn && !b_mn) return launch_t<BN, false, false>(args, grid, stream, status);
+  if (!a_mn && b_mn) return launch_t<BN, false, true>(args, grid, stream, status);
+  if (a_mn && !b_mn) return launch_t<BN, true, false>(args, grid, stream, status);
+  return launch_t<BN, true, true>(args, grid, stream, status);
+}
+
+}  // namespace
+
+int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* status, int force_bn) {
+  if (ncalls < 1 || ncalls > 2) return -1;
+  const bool a_mn = calls[0].a_mn, b_mn = calls[0].b_mn;
+  for (int i = 1; i < ncalls; ++i)
+    if (calls[i].a_mn != a_mn || calls[i].b_mn != b_mn) return -2;
+
+  // Tile width: the widest BN that still gives every SM a tile.
+  const int sms = num_sms();
+  auto count_tiles = [&](int bn) {
+    long t = 0;
+    for (int i = 0; i < ncalls; ++i)
+      t += static_cast<long>((calls[i].M + BM - 1) / BM) * ((calls[i].N + bn - 1) / bn);
+    return t;
+  };
+  int bn = 64;
+  if (force_bn == 64 || force_bn == 128 || force_bn == 256) {
+    bn = force_bn;
+  } else {
+    int max_n = 0;
+    for (int i = 0; i < ncalls; ++i) max_n = calls[i].N > max_n ? calls[i].N : max_n;
+    if (max_n > 128 && count_tiles(256) >= sms * 3 / 4)
+      bn = 256;
+    else if (max_n > 64 && count_tiles(128) >= sms * 3 / 4)
+      bn = 128;
+    else
+      bn = (max_n > 64 && count_tiles(64) > 4L * sms) ? 128 : 64;
+  }
+  for (int i = 0; i < ncalls; ++i)
+    if ((calls[i].flags & GEMM_ACT_SWIGLU) && (calls[i].N % 32 != 0)) return -3;
+
+  GemmArgs args;
+  args.nprob = ncalls;
+  for (int i = 0; i < ncalls; ++i) {
+    const GemmCall& c = calls[i];
+    Problem& p = args.p[i];
+    bool ok;
+    if (!c.a_mn)
+      ok = make_tmap(&p.tmA, c.A, c.a_extent_k, c.a_extent_mn, c.lda, BK, BM);
+    else
+      ok = make_tmap(&p.tmA, c.A, c.a_extent_mn, c.a_extent_k, c.lda, 64, BK);
+    if (!ok) return -4;
+    if (!c.b_mn)
+      ok = make_tmap(&p.tmB, c.B, c.b_extent_k, c.b_extent_mn, c.ldb, BK, bn);
+    else
+      ok = make_tmap(&p.tmB, c.B, c.b_extent_mn, c.b_extent_k, c.ldb, 64, BK);
+    if (!ok) return -5;
+    p.D = c.D;
+    p.D2 = c.D2;
+    p.bias = reinterpret_cast<const __nv_bfloat16*>(c.bias);
+    p.residual = reinterpret_cast<const __nv_bfloat16*>(c.residual);
+    p.row_map = c.row_map;
+    p.dyn = c.dyn;
+    p.ldd = c.ldd;
+    p.ldd2 = c.ldd2;
+    p.ldr = c.ldr;
+    p.M = c.M;
+    p.N = c.N;
+    p.K = c.K;
+    p.m0 = c.m0;
+    p.k0 = c.k0;
+    p.flags = c.flags;
+  }
+  long tiles = count_tiles(bn);
+  if (tiles <= 0) return 0;
+  int grid = tiles < sms ? static_cast<int>(tiles) : sms;
+  if (bn == 256) return launch_bn<256>(args, a_mn, b_mn, grid, stream, status);
+  if (bn == 128) return launch_bn<128>(args, a_mn, b_mn, grid, stream, status);
+  return launch_bn<64>(args, a_mn, b_mn, grid, stream, status);
+}
+
+}  // namespace wx

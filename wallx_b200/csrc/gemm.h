@@ -1,0 +1,57 @@
+// Host API of the tcgen05 GEMM core (no torch types: raw pointers + a CUDA stream).
+//
+// One launch computes up to two independent problems ("dual asymmetric grouped GEMM": the two
+// FFN experts have different row counts and different widths), each
+//     D[m, n] = epilogue( sum_k A(m, k) * B(n, k) )
+// with bf16 operands and fp32 accumulation in tensor memory.
+//
+// Parity: this covers the reference's csrc/dual_asym_grouped_gemm.cu:49-136 (NN/NT/TN/TT CUTLASS
+// GemmGrouped for two problems) and every nn.Linear it runs through cuBLAS.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace wx {
+
+enum GemmFlags : int {
+  GEMM_OUT_FP32 = 1,     // D is fp32 (else bf16)
+  GEMM_ACCUMULATE = 2,   // D += result (fp32 or bf16 read-modify-write)
+  GEMM_ACT_GELU = 4,     // exact (erf) GELU after bias
+  GEMM_ACT_SWIGLU = 8,   // B rows interleaved [16 gate | 16 up]: D[:, j] = silu(g_j) * u_j, ld = N/2
+};
+
+struct GemmCall {
+  // A(m, k): a_mn == false -> memory [a_rows][>=k0+K], k contiguous, pitch lda elements.
+  //          a_mn == true  -> memory [k rows][a_rows'], m contiguous, pitch lda elements.
+  const void* A;
+  long lda;
+  long a_extent_mn;  // number of valid m positions in memory (tensor-map bound along m)
+  long a_extent_k;   // number of valid k positions in memory (tensor-map bound along k)
+  bool a_mn;
+  const void* B;
+  long ldb;
+  long b_extent_mn;
+  long b_extent_k;
+  bool b_mn;
+  int M, N, K;
+  int m0;  // offset along m applied to A coordinates and D rows
+  int k0;  // offset along k applied to A and B coordinates
+  // Optional device int[4] = {m0, M, k0, K}: overrides the static values (data-dependent sizes
+  // without a host sync). The static M must then be an upper bound.
+  const int* dyn;
+  void* D;
+  long ldd;
+  void* D2;  // optional raw pre-activation output (bf16), SWIGLU only: [*, ldd2], N wide
+  long ldd2;
+  const void* bias;      // bf16 [N] or nullptr
+  const void* residual;  // bf16 [*, ldr] added after activation, indexed by destination row
+  long ldr;
+  const int* row_map;  // optional: D row r is written to row row_map[r]; negative -> dropped
+  int flags;
+};
+
+// Launches on `stream`. `status` is a device int that the kernel sets non-zero when one of its
+// bounded waits ran out (the kernel then returns normally). Returns a CUDA error code (0 = ok).
+int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* status, int force_bn);
+
+}  // namespace wx

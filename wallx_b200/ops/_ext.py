@@ -1,0 +1,104 @@
+"""Loader and builder of the in-tree sm_100a extension.
+
+The extension is built in-tree (``wallx_b200/_build/_wallx_C.so``) so that the binary travels
+with the source tree. On a machine with a GPU the ops refuse to run without it: there is no
+silent PyTorch fallback for CUDA tensors.
+"""
+from __future__ import annotations
+
+import importlib.util
+import os
+import sys
+import threading
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_PKG = os.path.dirname(_HERE)
+CSRC = os.path.join(_PKG, "csrc")
+BUILD_DIR = os.path.join(_PKG, "_build")
+EXT_NAME = "_wallx_C"
+
+SOURCES = [
+    "bindings.cpp",
+    "kernel_bindings.cpp",
+    "gemm.cu",
+]
+
+NVCC_FLAGS = [
+    "-gencode",
+    "arch=compute_100a,code=sm_100a",
+    "-lineinfo",
+    "-O3",
+    "-std=c++17",
+    "--expt-relaxed-constexpr",
+    "-Xptxas",
+    "-v",
+]
+
+_lock = threading.Lock()
+_mod = None
+_tried = False
+
+
+def so_path() -> str:
+    return os.path.join(BUILD_DIR, EXT_NAME + ".so")
+
+
+def build(verbose: bool = False):
+    """Compile every CUDA source for sm_100a (cross-compiles without a GPU) and load the result."""
+    global _mod, _tried
+    from torch.utils import cpp_extension
+
+    os.makedirs(BUILD_DIR, exist_ok=True)
+    srcs = [os.path.join(CSRC, s) for s in SOURCES]
+    mod = cpp_extension.load(
+        name=EXT_NAME,
+        sources=srcs,
+        extra_cflags=["-O3", "-std=c++17"],
+        extra_cuda_cflags=NVCC_FLAGS,
+        extra_include_paths=[CSRC],
+        build_directory=BUILD_DIR,
+        verbose=verbose,
+        with_cuda=True,
+    )
+    with _lock:
+        _mod = mod
+        _tried = True
+    return mod
+
+
+def _load_prebuilt():
+    path = so_path()
+    if not os.path.exists(path):
+        return None
+    import torch  # noqa: F401  (libtorch symbols must be loaded first)
+
+    spec = importlib.util.spec_from_file_location(EXT_NAME, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    sys.modules[EXT_NAME] = mod
+    return mod
+
+
+def get(required: bool = True):
+    """Return the extension module; raise if it is missing and ``required``."""
+    global _mod, _tried
+    if _mod is None and not _tried:
+        with _lock:
+            if _mod is None and not _tried:
+                _tried = True
+                try:
+                    _mod = _load_prebuilt()
+                except Exception as e:  # pragma: no cover - depends on the box
+                    if required:
+                        raise RuntimeError(f"wallx_b200: cannot load {so_path()}: {e}") from e
+                    _mod = None
+    if _mod is None and required:
+        raise RuntimeError(
+            "wallx_b200: the sm_100a extension is not built "
+            f"({so_path()} missing). Run `python -c 'import __graft_entry__ as g; g.build()'`."
+        )
+    return _mod
+
+
+def available() -> bool:
+    return get(required=False) is not None

@@ -1,0 +1,71 @@
+"""Low-level Python face of the tcgen05 GEMM core.
+
+``D[m, n] = epilogue(sum_k A(m, k) * B(n, k))`` with bf16 operands and fp32 accumulation.
+Operand memory layouts:
+
+* ``a_mn=False``: ``A`` is a ``[M, K]`` tensor (k contiguous);  ``a_mn=True``: ``A`` is ``[K, M]``.
+* ``b_mn=False``: ``B`` is a ``[N, K]`` tensor (k contiguous);  ``b_mn=True``: ``B`` is ``[K, N]``.
+
+So ``x @ w.T`` is ``(False, False)``, ``dy @ w`` is ``(False, True)`` and ``dy.T @ x`` is
+``(True, True)`` -- no transposed copies are made (reference: the NN/NT/TN/TT instantiations of
+csrc/dual_asym_grouped_gemm.cu:49-136).
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from . import _ext
+
+OUT_FP32 = 1
+ACCUMULATE = 2
+ACT_GELU = 4
+ACT_SWIGLU = 8
+
+
+class GemmSpec:
+    """One problem of a (possibly grouped) launch."""
+
+    __slots__ = ("a", "a_mn", "b", "b_mn", "out", "M", "N", "K", "bias", "residual", "row_map", "dyn", "out2",
+                 "flags", "m0", "k0")
+
+    def __init__(self, a, b, out, *, a_mn=False, b_mn=False, M=None, N=None, K=None, bias=None, residual=None,
+                 row_map=None, dyn=None, out2=None, flags=0, m0=0, k0=0):
+        self.a, self.b, self.out = a, b, out
+        self.a_mn, self.b_mn = bool(a_mn), bool(b_mn)
+        self.M = int(M if M is not None else (a.shape[1] if a_mn else a.shape[0]))
+        self.N = int(N if N is not None else (b.shape[1] if b_mn else b.shape[0]))
+        self.K = int(K if K is not None else (a.shape[0] if a_mn else a.shape[1]))
+        self.bias, self.residual, self.row_map, self.dyn, self.out2 = bias, residual, row_map, dyn, out2
+        self.flags, self.m0, self.k0 = int(flags), int(m0), int(k0)
+
+    def as_tuple(self):
+        return (self.a, self.a_mn, self.b, self.b_mn, self.out, self.M, self.N, self.K, self.bias, self.residual,
+                self.row_map, self.dyn, self.out2, self.flags, self.m0, self.k0)
+
+
+def launch(specs: Sequence[GemmSpec], force_bn: int = 0) -> None:
+    """Run one or two problems in a single persistent launch."""
+    _ext.get().gemm_grouped([s.as_tuple() for s in specs], int(force_bn))
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn=False, b_mn=False, out: Optional[torch.Tensor] = None,
+         bias=None, residual=None, flags: int = 0, force_bn: int = 0) -> torch.Tensor:
+    """Single dense problem; allocates the output when none is given."""
+    M = a.shape[1] if a_mn else a.shape[0]
+    N = b.shape[1] if b_mn else b.shape[0]
+    if out is None:
+        width = N // 2 if (flags & ACT_SWIGLU) else N
+        out = torch.empty((M, width), device=a.device,
+                          dtype=torch.float32 if (flags & OUT_FP32) else torch.bfloat16)
+    launch([GemmSpec(a, b, out, a_mn=a_mn, b_mn=b_mn, bias=bias, residual=residual, flags=flags)], force_bn)
+    return out
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+    """Raise if a kernel gave up on one of its bounded waits since the last check (synchronises)."""
+    idx = torch.cuda.current_device() if device is None else (torch.device(device).index or 0)
+    st = _ext.get().read_status(idx)
+    if st != 0:
+        raise RuntimeError(f"wallx_b200: a device-side wait timed out (status {st}); results are invalid")
