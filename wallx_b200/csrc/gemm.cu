@@ -70,11 +70,12 @@ __device__ __forceinline__ void load_dims(const GemmArgs& args, Dims& d) {
     if (i < args.nprob) {
       const Problem& p = args.p[i];
       int M = p.M, K = p.K, m0 = p.m0, k0 = p.k0;
-      if (p.dyn != nullptr) {
-        m0 = p.dyn[0];
-        M = min(p.dyn[1], p.M);
-        k0 = p.dyn[2];
-        K = p.dyn[3];
+      if (p.dyn != nullptr) {  // negative entries keep the static value
+        const int d0 = p.dyn[0], d1 = p.dyn[1], d2 = p.dyn[2], d3 = p.dyn[3];
+        if (d0 >= 0) m0 = d0;
+        if (d1 >= 0) M = min(d1, p.M);
+        if (d2 >= 0) k0 = d2;
+        if (d3 >= 0) K = d3;
       }
       d.M[i] = M;
       d.K[i] = K;
@@ -248,7 +249,10 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
       const int row_in_prob = ti.mt * BM + quarter * 32 + lane;
       const bool row_ok = row_in_prob < d.M[ti.prob];
       long drow = static_cast<long>(d.m0[ti.prob]) + row_in_prob;
-      bool store_ok = row_ok;
+      // Rows between M and the end of the 128-row tile are zero-filled on request, so that a
+      // 128-aligned token segment can later be reduced over without reading garbage.
+      const bool zero_row = !row_ok && (p.flags & GEMM_ZERO_PAD_ROWS) != 0 && p.row_map == nullptr;
+      bool store_ok = row_ok || zero_row;
       if (row_ok && p.row_map != nullptr) {
         const int r = p.row_map[drow];
         store_ok = r >= 0;
@@ -257,7 +261,7 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
       const int flags = p.flags;
       const bool swiglu = (flags & GEMM_ACT_SWIGLU) != 0;
       const bool out_fp32 = (flags & GEMM_OUT_FP32) != 0;
-      const bool accum = (flags & GEMM_ACCUMULATE) != 0;
+      const bool accum = (flags & GEMM_ACCUMULATE) != 0 && !zero_row;
       const int n_base = ti.nt * BN;
       const uint32_t taddr0 = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
 
@@ -270,9 +274,9 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
         if (!store_ok || n0 >= p.N) continue;
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        for (int j = 0; j < 32; ++j) v[j] = zero_row ? 0.f : __uint_as_float(r[j]);
         const int nvalid = min(32, p.N - n0);
-        if (p.bias != nullptr) {
+        if (p.bias != nullptr && !zero_row) {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
             if (j < nvalid) v[j] += __bfloat162float(p.bias[n0 + j]);
@@ -305,7 +309,7 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
         }
-        if (p.residual != nullptr) {
+        if (p.residual != nullptr && !zero_row) {
           const __nv_bfloat16* rs = p.residual + drow * p.ldr + n0;
           if (nvalid == 32 && (p.ldr & 7) == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0) {
             const uint4* rs4 = reinterpret_cast<const uint4*>(rs);

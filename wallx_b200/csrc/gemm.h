@@ -18,6 +18,7 @@ enum GemmFlags : int {
   GEMM_ACCUMULATE = 2,   // D += result (fp32 or bf16 read-modify-write)
   GEMM_ACT_GELU = 4,     // exact (erf) GELU after bias
   GEMM_ACT_SWIGLU = 8,   // B rows interleaved [16 gate | 16 up]: D[:, j] = silu(g_j) * u_j, ld = N/2
+  GEMM_ZERO_PAD_ROWS = 16,  // rows in [M, round_up(M, 128)) are written as zeros (no row_map)
 };
 
 struct GemmCall {
@@ -36,8 +37,8 @@ struct GemmCall {
   int M, N, K;
   int m0;  // offset along m applied to A coordinates and D rows
   int k0;  // offset along k applied to A and B coordinates
-  // Optional device int[4] = {m0, M, k0, K}: overrides the static values (data-dependent sizes
-  // without a host sync). The static M must then be an upper bound.
+  // Optional device int[4] = {m0, M, k0, K}: non-negative entries override the static values
+  // (data-dependent sizes without a host sync). The static M must then be an upper bound.
   const int* dyn;
   void* D;
   long ldd;

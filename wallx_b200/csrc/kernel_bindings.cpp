@@ -1,8 +1,177 @@
-// Bindings of the non-GEMM kernels.
+// Bindings of the non-GEMM kernels (allocation and checks here, arithmetic in kernels.cu).
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
 #include "kernels.h"
 
-void register_kernel_bindings(pybind11::module_& m) { (void)m; }
+namespace {
+
+using OptT = c10::optional<at::Tensor>;
+
+#define WX_CHECK_RC(rc, what) TORCH_CHECK((rc) == 0, what, " failed with code ", (rc))
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream(); }
+
+void check_bf16(const at::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.is_contiguous(), name, ": contiguous CUDA bf16 expected");
+}
+const int* opt_int(const OptT& t) {
+  if (!t.has_value() || !t->defined() || t->numel() == 0) return nullptr;
+  TORCH_CHECK(t->scalar_type() == at::kInt && t->is_cuda() && t->is_contiguous(), "int32 CUDA tensor expected");
+  return t->data_ptr<int>();
+}
+
+std::tuple<at::Tensor, at::Tensor> rms_norm_fwd(const at::Tensor& x, const at::Tensor& w, double eps, const OptT& dest,
+                                                int64_t out_rows) {
+  check_bf16(x, "x");
+  check_bf16(w, "w");
+  c10::cuda::CUDAGuard g(x.device());
+  const int T = x.size(0), C = x.size(1);
+  const int* dp = opt_int(dest);
+  at::Tensor y = dp ? at::zeros({out_rows, C}, x.options()) : at::empty({T, C}, x.options());
+  at::Tensor rstd = at::empty({T}, x.options().dtype(at::kFloat));
+  WX_CHECK_RC(wx::rms_norm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), dp, T, C,
+                               static_cast<float>(eps), cur_stream()),
+              "rms_norm_fwd");
+  return {y, rstd};
+}
+
+std::tuple<at::Tensor, at::Tensor> rms_norm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& w,
+                                                const at::Tensor& rstd, const OptT& dest) {
+  check_bf16(dy, "dy");
+  check_bf16(x, "x");
+  c10::cuda::CUDAGuard g(x.device());
+  const int T = x.size(0), C = x.size(1);
+  at::Tensor dx = at::empty_like(x);
+  at::Tensor dw = at::empty_like(w);
+  at::Tensor partial = at::empty({wx::rms_norm_bwd_blocks(T), C}, x.options().dtype(at::kFloat));
+  WX_CHECK_RC(wx::rms_norm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), opt_int(dest),
+                               dx.data_ptr(), partial.data_ptr<float>(), dw.data_ptr(), T, C, cur_stream()),
+              "rms_norm_bwd");
+  return {dx, dw};
+}
+
+at::Tensor swiglu_bwd(const at::Tensor& dh, const at::Tensor& gu) {
+  TORCH_CHECK(dh.is_cuda() && gu.is_cuda() && dh.scalar_type() == at::kBFloat16 && gu.scalar_type() == at::kBFloat16);
+  TORCH_CHECK(dh.dim() == 2 && gu.dim() == 2 && dh.stride(1) == 1 && gu.stride(1) == 1 && gu.size(1) == 2 * dh.size(1));
+  c10::cuda::CUDAGuard g(gu.device());
+  at::Tensor dgu = at::empty({gu.size(0), gu.size(1)}, gu.options());
+  WX_CHECK_RC(wx::swiglu_bwd(dh.data_ptr(), gu.data_ptr(), dgu.data_ptr(), gu.size(0), gu.size(1), dh.stride(0),
+                             gu.stride(0), cur_stream()),
+              "swiglu_bwd");
+  return dgu;
+}
+
+at::Tensor rope_qk(const at::Tensor& qkv, const at::Tensor& cos_t, const at::Tensor& sin_t, int64_t n_rot, int64_t D,
+                   bool inverse) {
+  check_bf16(qkv, "qkv");
+  TORCH_CHECK(cos_t.scalar_type() == at::kFloat && sin_t.scalar_type() == at::kFloat && cos_t.is_contiguous() &&
+              sin_t.is_contiguous() && cos_t.size(0) == qkv.size(0) && cos_t.size(1) == D,
+              "rope_qk: cos/sin must be fp32 [T, D]");
+  c10::cuda::CUDAGuard g(qkv.device());
+  at::Tensor out = at::empty_like(qkv);
+  WX_CHECK_RC(wx::rope_qk(qkv.data_ptr(), out.data_ptr(), cos_t.data_ptr<float>(), sin_t.data_ptr<float>(), qkv.size(0),
+                          qkv.size(1), n_rot, D, inverse ? 1 : 0, cur_stream()),
+              "rope_qk");
+  return out;
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> route_plan(const at::Tensor& types, int64_t E, int64_t rows) {
+  TORCH_CHECK(types.is_cuda() && types.scalar_type() == at::kInt && types.is_contiguous(), "route_plan: int32 types");
+  c10::cuda::CUDAGuard g(types.device());
+  const int T = types.numel();
+  auto io = types.options();
+  at::Tensor dest = at::empty({T}, io), seg = at::empty({E, 4}, io), segk = at::empty({E, 4}, io),
+             inv = at::empty({rows}, io);
+  WX_CHECK_RC(wx::route_plan(types.data_ptr<int>(), T, E, rows, dest.data_ptr<int>(), seg.data_ptr<int>(),
+                             segk.data_ptr<int>(), inv.data_ptr<int>(), cur_stream()),
+              "route_plan");
+  return {dest, seg, segk, inv};
+}
+
+at::Tensor permute_rows(const at::Tensor& x, const at::Tensor& dest, int64_t rows) {
+  check_bf16(x, "x");
+  c10::cuda::CUDAGuard g(x.device());
+  at::Tensor out = at::zeros({rows, x.size(1)}, x.options());
+  WX_CHECK_RC(wx::permute_rows(x.data_ptr(), dest.data_ptr<int>(), out.data_ptr(), x.size(0), x.size(1), cur_stream()),
+              "permute_rows");
+  return out;
+}
+
+at::Tensor gather_rows(const at::Tensor& x, const at::Tensor& idx) {
+  check_bf16(x, "x");
+  TORCH_CHECK(idx.scalar_type() == at::kInt && idx.is_cuda() && idx.is_contiguous());
+  c10::cuda::CUDAGuard g(x.device());
+  at::Tensor out = at::empty({idx.numel(), x.size(1)}, x.options());
+  WX_CHECK_RC(wx::gather_rows(x.data_ptr(), idx.data_ptr<int>(), out.data_ptr(), idx.numel(), x.size(1), cur_stream()),
+              "gather_rows");
+  return out;
+}
+
+at::Tensor column_sum(const at::Tensor& x) {
+  check_bf16(x, "x");
+  c10::cuda::CUDAGuard g(x.device());
+  at::Tensor acc = at::zeros({x.size(1)}, x.options().dtype(at::kFloat));
+  at::Tensor out = at::empty({x.size(1)}, x.options());
+  WX_CHECK_RC(wx::column_sum(x.data_ptr(), acc.data_ptr<float>(), out.data_ptr(), x.size(0), x.size(1), cur_stream()),
+              "column_sum");
+  return out;
+}
+
+void ce_fwd(const at::Tensor& logits, const at::Tensor& labels, at::Tensor& loss, at::Tensor& lse, at::Tensor& pred) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kBFloat16 && logits.stride(1) == 1);
+  TORCH_CHECK(labels.scalar_type() == at::kLong && labels.is_contiguous() && pred.scalar_type() == at::kLong);
+  c10::cuda::CUDAGuard g(logits.device());
+  WX_CHECK_RC(wx::ce_fwd(logits.data_ptr(), reinterpret_cast<const long*>(labels.data_ptr<int64_t>()),
+                         loss.data_ptr<float>(), lse.data_ptr<float>(), reinterpret_cast<long*>(pred.data_ptr<int64_t>()),
+                         logits.size(0), logits.size(1), logits.stride(0), cur_stream()),
+              "ce_fwd");
+}
+
+void ce_bwd(at::Tensor& logits, const at::Tensor& labels, const at::Tensor& lse, const at::Tensor& dloss) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kBFloat16 && logits.stride(1) == 1);
+  c10::cuda::CUDAGuard g(logits.device());
+  WX_CHECK_RC(wx::ce_bwd(logits.data_ptr(), reinterpret_cast<const long*>(labels.data_ptr<int64_t>()),
+                         lse.data_ptr<float>(), dloss.data_ptr<float>(), logits.size(0), logits.size(1),
+                         logits.stride(0), cur_stream()),
+              "ce_bwd");
+}
+
+void sumsq_bf16(const at::Tensor& g, at::Tensor& out) {
+  TORCH_CHECK(g.is_cuda() && g.scalar_type() == at::kBFloat16 && g.is_contiguous() && out.scalar_type() == at::kFloat);
+  c10::cuda::CUDAGuard guard(g.device());
+  WX_CHECK_RC(wx::sumsq_bf16(g.data_ptr(), g.numel(), out.data_ptr<float>(), cur_stream()), "sumsq_bf16");
+}
+
+void adamw_step(at::Tensor& p16, at::Tensor& p32, at::Tensor& m, at::Tensor& v, const at::Tensor& g,
+                const at::Tensor& hyper, const OptT& norm_sq) {
+  TORCH_CHECK(p16.is_cuda() && p16.scalar_type() == at::kBFloat16 && g.scalar_type() == at::kBFloat16);
+  TORCH_CHECK(p32.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat);
+  TORCH_CHECK(p16.is_contiguous() && p32.is_contiguous() && m.is_contiguous() && v.is_contiguous() && g.is_contiguous());
+  const int64_t n = p16.numel();
+  TORCH_CHECK(p32.numel() == n && m.numel() == n && v.numel() == n && g.numel() == n, "adamw: size mismatch");
+  TORCH_CHECK(hyper.scalar_type() == at::kFloat && hyper.numel() >= 9 && hyper.is_cuda());
+  c10::cuda::CUDAGuard guard(p16.device());
+  const float* ns = (norm_sq.has_value() && norm_sq->defined()) ? norm_sq->data_ptr<float>() : nullptr;
+  WX_CHECK_RC(wx::adamw_step(p16.data_ptr(), p32.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
+                             g.data_ptr(), n, hyper.data_ptr<float>(), ns, cur_stream()),
+              "adamw_step");
+}
+
+}  // namespace
+
+void register_kernel_bindings(pybind11::module_& m) {
+  m.def("rms_norm_fwd", &rms_norm_fwd);
+  m.def("rms_norm_bwd", &rms_norm_bwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("rope_qk", &rope_qk);
+  m.def("route_plan", &route_plan);
+  m.def("permute_rows", &permute_rows);
+  m.def("gather_rows", &gather_rows);
+  m.def("column_sum", &column_sum);
+  m.def("ce_fwd", &ce_fwd);
+  m.def("ce_bwd", &ce_bwd);
+  m.def("sumsq_bf16", &sumsq_bf16);
+  m.def("adamw_step", &adamw_step);
+}

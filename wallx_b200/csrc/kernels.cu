@@ -1,0 +1,651 @@
+// Bandwidth- and latency-bound kernels: RMSNorm (+ fused token-type permutation), rotary on the
+// packed q|k|v buffer, SwiGLU backward, routing plan for the dual-expert FFN, row permutation,
+// column sums, cross entropy over a logits block, grad-norm and fused AdamW on flat buffers.
+// All of them use 16-byte accesses and take an explicit stream.
+//
+// Reference parity: csrc/permute.cu (row map + gather/scatter), csrc/rope.cu (mRoPE fwd/bwd), the
+// ATen chains behind Qwen2RMSNorm (modeling_qwen2_5_vl.py:122-139), SiLU*mul, CrossEntropyLoss
+// and torch.optim.AdamW (qwen_vl_act_trainer.py:577-581).
+#include "kernels.h"
+
+#include <cuda_bf16.h>
+#include <math.h>
+
+namespace wx {
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum; `red` is a shared float[32]. Every thread gets the result.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  float t = (lane < nw) ? red[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  float t = (lane < nw) ? red[lane] : -INFINITY;
+  t = warp_max(t);
+  return t;
+}
+
+struct alignas(16) BF8 {
+  __nv_bfloat162 v[4];
+};
+__device__ __forceinline__ void unpack8(const BF8& b, float* f) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(b.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ BF8 pack8(const float* f) {
+  BF8 b;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) b.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return b;
+}
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_MAX_CHUNKS = 4;  // C <= 256 * 8 * 4 = 8192
+
+// ------------------------------------------------------------------------------ RMSNorm forward
+__global__ void __launch_bounds__(NORM_THREADS)
+rms_norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                    __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, const int* __restrict__ dest, int T,
+                    int C, float eps) {
+  __shared__ float red[32];
+  const int nchunk = C >> 3;
+  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+    const BF8* xr = reinterpret_cast<const BF8*>(x + static_cast<size_t>(row) * C);
+    float v[NORM_MAX_CHUNKS][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+      const int i = threadIdx.x + c * NORM_THREADS;
+      if (i < nchunk) {
+        unpack8(xr[i], v[c]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += v[c][e] * v[c][e];
+      }
+    }
+    ss = block_sum(ss, red);
+    const float rstd = rsqrtf(ss / static_cast<float>(C) + eps);
+    if (threadIdx.x == 0) rstd_out[row] = rstd;
+    const int orow = dest ? dest[row] : row;
+    BF8* yr = reinterpret_cast<BF8*>(y + static_cast<size_t>(orow) * C);
+    const BF8* wr = reinterpret_cast<const BF8*>(w);
+#pragma unroll
+    for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+      const int i = threadIdx.x + c * NORM_THREADS;
+      if (i < nchunk) {
+        float wf[8], o[8];
+        unpack8(wr[i], wf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = wf[e] * bf16_round(v[c][e] * rstd);
+        yr[i] = pack8(o);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------ RMSNorm backward
+// dx = rstd * (g - xhat * mean(g * xhat)), g = dy * w, xhat = x * rstd; dw partials per block.
+__global__ void __launch_bounds__(NORM_THREADS)
+rms_norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
+                    const int* __restrict__ dest, __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int T,
+                    int C) {
+  __shared__ float red[32];
+  const int nchunk = C >> 3;
+  float dwacc[NORM_MAX_CHUNKS][8];
+#pragma unroll
+  for (int c = 0; c < NORM_MAX_CHUNKS; ++c)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dwacc[c][e] = 0.f;
+  const BF8* wr = reinterpret_cast<const BF8*>(w);
+  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+    const int grow = dest ? dest[row] : row;
+    const BF8* xr = reinterpret_cast<const BF8*>(x + static_cast<size_t>(row) * C);
+    const BF8* gr = reinterpret_cast<const BF8*>(dy + static_cast<size_t>(grow) * C);
+    const float rstd = rstd_in[row];
+    float xh[NORM_MAX_CHUNKS][8], g[NORM_MAX_CHUNKS][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+      const int i = threadIdx.x + c * NORM_THREADS;
+      if (i < nchunk) {
+        float xf[8], df[8], wf[8];
+        unpack8(xr[i], xf);
+        unpack8(gr[i], df);
+        unpack8(wr[i], wf);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          xh[c][e] = xf[e] * rstd;
+          g[c][e] = df[e] * wf[e];
+          dot += g[c][e] * xh[c][e];
+          dwacc[c][e] += df[e] * bf16_round(xh[c][e]);
+        }
+      }
+    }
+    dot = block_sum(dot, red) / static_cast<float>(C);
+    BF8* dxr = reinterpret_cast<BF8*>(dx + static_cast<size_t>(row) * C);
+#pragma unroll
+    for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+      const int i = threadIdx.x + c * NORM_THREADS;
+      if (i < nchunk) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = rstd * (g[c][e] - xh[c][e] * dot);
+        dxr[i] = pack8(o);
+      }
+    }
+  }
+  float* dp = dw_partial + static_cast<size_t>(blockIdx.x) * C;
+#pragma unroll
+  for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+    const int i = threadIdx.x + c * NORM_THREADS;
+    if (i < nchunk) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dp[i * 8 + e] = dwacc[c][e];
+    }
+  }
+}
+
+__global__ void reduce_partials_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int nblk,
+                                       int C) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float s = 0.f;
+  for (int b = 0; b < nblk; ++b) s += partial[static_cast<size_t>(b) * C + c];
+  out[c] = __float2bfloat16(s);
+}
+
+// ------------------------------------------------------------------------------ SwiGLU backward
+// gu is [R, ld_gu] with 32-column blocks [16 gate | 16 up]; dh is [R, ld_dh]; one thread per block.
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dh, const __nv_bfloat16* __restrict__ gu,
+                                  __nv_bfloat16* __restrict__ dgu, int R, int nblk, long ld_dh, long ld_gu) {
+  const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long>(R) * nblk) return;
+  const int r = static_cast<int>(idx / nblk);
+  const int b = static_cast<int>(idx - static_cast<long>(r) * nblk);
+  const BF8* gp = reinterpret_cast<const BF8*>(gu + r * ld_gu + b * 32);
+  const BF8* dp = reinterpret_cast<const BF8*>(dh + r * ld_dh + b * 16);
+  BF8* op = reinterpret_cast<BF8*>(dgu + r * ld_gu + b * 32);
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float g[8], u[8], d[8], dg[8], du[8];
+    unpack8(gp[h], g);
+    unpack8(gp[2 + h], u);
+    unpack8(dp[h], d);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float sg = 1.f / (1.f + __expf(-g[e]));
+      const float silu = g[e] * sg;
+      du[e] = d[e] * silu;
+      dg[e] = d[e] * u[e] * (sg * (1.f + g[e] * (1.f - sg)));
+    }
+    op[h] = pack8(dg);
+    op[2 + h] = pack8(du);
+  }
+}
+
+// ------------------------------------------------------------------------------ rotary on q|k|v
+// One thread rotates 8 channels of the first half of a head and their partners in the second
+// half; v columns (heads >= n_rot) are copied. `inverse` applies the transposed rotation.
+__global__ void rope_qk_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                               const float* __restrict__ cos_t, const float* __restrict__ sin_t, int T, int W,
+                               int n_rot, int D, int inverse) {
+  const int half = D >> 1;
+  const int chunks_per_head = half >> 3;
+  const int rot_chunks = n_rot * chunks_per_head;
+  const int copy_chunks = (W - n_rot * D) >> 3;
+  const int per_row = rot_chunks + copy_chunks;
+  const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long>(T) * per_row) return;
+  const int t = static_cast<int>(idx / per_row);
+  const int c = static_cast<int>(idx - static_cast<long>(t) * per_row);
+  const __nv_bfloat16* row = in + static_cast<size_t>(t) * W;
+  __nv_bfloat16* orow = out + static_cast<size_t>(t) * W;
+  if (c >= rot_chunks) {
+    const int off = n_rot * D + (c - rot_chunks) * 8;
+    *reinterpret_cast<BF8*>(orow + off) = *reinterpret_cast<const BF8*>(row + off);
+    return;
+  }
+  const int h = c / chunks_per_head;
+  const int d0 = (c - h * chunks_per_head) * 8;
+  float a[8], b[8], oa[8], ob[8];
+  unpack8(*reinterpret_cast<const BF8*>(row + h * D + d0), a);
+  unpack8(*reinterpret_cast<const BF8*>(row + h * D + half + d0), b);
+  const float* cs = cos_t + static_cast<size_t>(t) * D;
+  const float* sn = sin_t + static_cast<size_t>(t) * D;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float c1 = cs[d0 + e], s1 = sn[d0 + e], c2 = cs[half + d0 + e], s2 = sn[half + d0 + e];
+    if (!inverse) {
+      oa[e] = a[e] * c1 - b[e] * s1;
+      ob[e] = b[e] * c2 + a[e] * s2;
+    } else {
+      oa[e] = a[e] * c1 + b[e] * s2;
+      ob[e] = b[e] * c2 - a[e] * s1;
+    }
+  }
+  *reinterpret_cast<BF8*>(orow + h * D + d0) = pack8(oa);
+  *reinterpret_cast<BF8*>(orow + h * D + half + d0) = pack8(ob);
+}
+
+// ------------------------------------------------------------------------------ routing plan
+// Single block: stable grouping of T tokens by expert id (E <= 8) with 128-row aligned segments.
+constexpr int ROUTE_THREADS = 1024;
+constexpr int ROUTE_MAX_E = 8;
+__global__ void __launch_bounds__(ROUTE_THREADS)
+route_plan_kernel(const int* __restrict__ types, int T, int E, int rows, int* __restrict__ dest,
+                  int* __restrict__ seg, int* __restrict__ segk, int* __restrict__ inv) {
+  __shared__ int counts[ROUTE_MAX_E];
+  __shared__ int starts[ROUTE_MAX_E];
+  __shared__ int warp_cnt[ROUTE_MAX_E][32];
+  __shared__ int running[ROUTE_MAX_E];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x < ROUTE_MAX_E) counts[threadIdx.x] = 0;
+  for (int i = threadIdx.x; i < rows; i += ROUTE_THREADS) inv[i] = -1;
+  __syncthreads();
+  // pass 1: counts
+  int local[ROUTE_MAX_E];
+#pragma unroll
+  for (int e = 0; e < ROUTE_MAX_E; ++e) local[e] = 0;
+  for (int i = threadIdx.x; i < T; i += ROUTE_THREADS) {
+    const int tt = types[i];
+#pragma unroll
+    for (int e = 0; e < ROUTE_MAX_E; ++e) local[e] += (tt == e);
+  }
+#pragma unroll
+  for (int e = 0; e < ROUTE_MAX_E; ++e) {
+    int v = local[e];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0 && v && e < E) atomicAdd(&counts[e], v);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int s = 0;
+    for (int e = 0; e < E; ++e) {
+      const int c = counts[e];
+      const int p = (c + 127) / 128 * 128;
+      starts[e] = s;
+      running[e] = s;
+      seg[e * 4 + 0] = s;
+      seg[e * 4 + 1] = c;
+      seg[e * 4 + 2] = -1;
+      seg[e * 4 + 3] = -1;
+      segk[e * 4 + 0] = -1;
+      segk[e * 4 + 1] = -1;
+      segk[e * 4 + 2] = s;
+      segk[e * 4 + 3] = p;
+      s += p;
+    }
+  }
+  __syncthreads();
+  // pass 2: stable ranks, chunk by chunk
+  for (int base = 0; base < T; base += ROUTE_THREADS) {
+    const int i = base + threadIdx.x;
+    const int tt = (i < T) ? types[i] : -1;
+    int my_rank = 0;
+    for (int e = 0; e < E; ++e) {
+      const unsigned bal = __ballot_sync(0xffffffffu, tt == e);
+      if (tt == e) my_rank = __popc(bal & ((1u << lane) - 1u));
+      if (lane == 0) warp_cnt[e][warp] = __popc(bal);
+    }
+    __syncthreads();
+    if (tt >= 0 && tt < E) {
+      int off = running[tt];
+      for (int w2 = 0; w2 < warp; ++w2) off += warp_cnt[tt][w2];
+      const int d = off + my_rank;
+      dest[i] = d;
+      inv[d] = i;
+    }
+    __syncthreads();
+    if (threadIdx.x < E) {
+      int s = 0;
+      for (int w2 = 0; w2 < 32; ++w2) s += warp_cnt[threadIdx.x][w2];
+      running[threadIdx.x] += s;
+    }
+    __syncthreads();
+  }
+}
+
+// out[dest[t], :] = x[t, :]; out is zero-filled by the caller.
+__global__ void permute_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ dest,
+                                    __nv_bfloat16* __restrict__ out, int T, int C) {
+  const int nchunk = C >> 3;
+  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+    const BF8* src = reinterpret_cast<const BF8*>(x + static_cast<size_t>(row) * C);
+    BF8* dst = reinterpret_cast<BF8*>(out + static_cast<size_t>(dest[row]) * C);
+    for (int i = threadIdx.x; i < nchunk; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+// out[t, :] = x[idx[t], :]
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ idx,
+                                   __nv_bfloat16* __restrict__ out, int T, int C) {
+  const int nchunk = C >> 3;
+  for (int row = blockIdx.x; row < T; row += gridDim.x) {
+    const BF8* src = reinterpret_cast<const BF8*>(x + static_cast<size_t>(idx[row]) * C);
+    BF8* dst = reinterpret_cast<BF8*>(out + static_cast<size_t>(row) * C);
+    for (int i = threadIdx.x; i < nchunk; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+// ------------------------------------------------------------------------------ column sum
+__global__ void column_sum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ acc, int R, int C,
+                                  int rows_per_block) {
+  const int c2 = blockIdx.x * blockDim.x + threadIdx.x;  // pair index
+  if (c2 * 2 >= C) return;
+  const int r0 = blockIdx.y * rows_per_block;
+  const int r1 = min(R, r0 + rows_per_block);
+  float s0 = 0.f, s1 = 0.f;
+  if (c2 * 2 + 1 < C && (C & 1) == 0) {
+    for (int r = r0; r < r1; ++r) {
+      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x + static_cast<size_t>(r) * C + c2 * 2));
+      s0 += f.x;
+      s1 += f.y;
+    }
+    atomicAdd(&acc[c2 * 2], s0);
+    atomicAdd(&acc[c2 * 2 + 1], s1);
+  } else {
+    for (int r = r0; r < r1; ++r) {
+      s0 += __bfloat162float(x[static_cast<size_t>(r) * C + c2 * 2]);
+      if (c2 * 2 + 1 < C) s1 += __bfloat162float(x[static_cast<size_t>(r) * C + c2 * 2 + 1]);
+    }
+    atomicAdd(&acc[c2 * 2], s0);
+    if (c2 * 2 + 1 < C) atomicAdd(&acc[c2 * 2 + 1], s1);
+  }
+}
+__global__ void f32_to_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long n) {
+  const long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = __float2bfloat16(in[i]);
+}
+
+// ------------------------------------------------------------------------------ cross entropy
+constexpr int CE_THREADS = 512;
+__global__ void __launch_bounds__(CE_THREADS)
+ce_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const long* __restrict__ labels, float* __restrict__ loss,
+              float* __restrict__ lse_out, long* __restrict__ pred, int R, int V, long ld) {
+  __shared__ float red[32];
+  __shared__ float s_max;
+  __shared__ int s_arg[32];
+  __shared__ float s_val[32];
+  const int row = blockIdx.x;
+  if (row >= R) return;
+  const __nv_bfloat16* lr = logits + static_cast<size_t>(row) * ld;
+  float mx = -INFINITY;
+  int arg = 0;
+  for (int i = threadIdx.x; i < V; i += CE_THREADS) {
+    const float v = __bfloat162float(lr[i]);
+    if (v > mx) {
+      mx = v;
+      arg = i;
+    }
+  }
+  // argmax with lowest-index tie break
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, mx, o);
+    const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+    if (ov > mx || (ov == mx && oa < arg)) {
+      mx = ov;
+      arg = oa;
+    }
+  }
+  if (lane == 0) {
+    s_val[warp] = mx;
+    s_arg[warp] = arg;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float bm = s_val[0];
+    int ba = s_arg[0];
+    for (int w2 = 1; w2 < CE_THREADS / 32; ++w2)
+      if (s_val[w2] > bm || (s_val[w2] == bm && s_arg[w2] < ba)) {
+        bm = s_val[w2];
+        ba = s_arg[w2];
+      }
+    s_max = bm;
+    pred[row] = ba;
+  }
+  __syncthreads();
+  const float m = s_max;
+  float se = 0.f;
+  for (int i = threadIdx.x; i < V; i += CE_THREADS) se += __expf(__bfloat162float(lr[i]) - m);
+  se = block_sum(se, red);
+  if (threadIdx.x == 0) {
+    const float lse = m + logf(se);
+    lse_out[row] = lse;
+    const long lab = labels[row];
+    loss[row] = (lab >= 0 && lab < V) ? lse - __bfloat162float(lr[lab]) : 0.f;
+  }
+}
+
+// in place: logits -> dlogits = (softmax - onehot) * dloss[row]; ignored rows -> 0
+__global__ void __launch_bounds__(CE_THREADS)
+ce_bwd_kernel(__nv_bfloat16* __restrict__ logits, const long* __restrict__ labels, const float* __restrict__ lse,
+              const float* __restrict__ dloss, int R, int V, long ld) {
+  const int row = blockIdx.x;
+  if (row >= R) return;
+  __nv_bfloat16* lr = logits + static_cast<size_t>(row) * ld;
+  const long lab = labels[row];
+  const bool valid = lab >= 0 && lab < V;
+  const float g = valid ? dloss[row] : 0.f;
+  const float l = lse[row];
+  for (int i = threadIdx.x; i < V; i += CE_THREADS) {
+    float p = valid ? __expf(__bfloat162float(lr[i]) - l) : 0.f;
+    if (i == lab) p -= 1.f;
+    lr[i] = __float2bfloat16(p * g);
+  }
+}
+
+// ------------------------------------------------------------------------------ optimizer
+// sum of squares of a bf16 buffer accumulated (atomically) into out[0].
+__global__ void sumsq_bf16_kernel(const __nv_bfloat16* __restrict__ g, long n, float* __restrict__ out) {
+  __shared__ float red[32];
+  float s = 0.f;
+  const long n8 = n >> 3;
+  const BF8* g8 = reinterpret_cast<const BF8*>(g);
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    float f[8];
+    unpack8(g8[i], f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s += f[e] * f[e];
+  }
+  for (long i = (n8 << 3) + static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const float f = __bfloat162float(g[i]);
+    s += f * f;
+  }
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) atomicAdd(out, s);
+}
+
+// Fused: grad (bf16) * inv_accum * clip -> AdamW on fp32 master/m/v -> bf16 param.
+// `hyper` (device): [0] lr, [1] beta1, [2] beta2, [3] eps, [4] weight_decay, [5] bias_corr1,
+// [6] bias_corr2, [7] max_grad_norm (<=0: no clip), [8] grad_scale (1 / accumulation steps).
+// `norm_sq` (device): sum of squared *unscaled* gradients over the whole model. A non-finite norm
+// skips the update on every element (all ranks see the same norm, so all skip together).
+__global__ void adamw_kernel(__nv_bfloat16* __restrict__ p16, float* __restrict__ p32, float* __restrict__ m,
+                             float* __restrict__ v, const __nv_bfloat16* __restrict__ g, long n,
+                             const float* __restrict__ hyper, const float* __restrict__ norm_sq,
+                             const float* __restrict__ lr_scale_per_elem_unused) {
+  const float lr = hyper[0], b1 = hyper[1], b2 = hyper[2], eps = hyper[3], wd = hyper[4], bc1 = hyper[5],
+              bc2 = hyper[6], max_norm = hyper[7], gscale = hyper[8];
+  const float nsq = norm_sq ? norm_sq[0] : 0.f;
+  if (!(nsq == nsq) || isinf(nsq)) return;
+  float scale = gscale;
+  if (max_norm > 0.f && norm_sq) {
+    const float gnorm = sqrtf(nsq) * gscale;
+    const float coef = max_norm / (gnorm + 1e-6f);
+    if (coef < 1.f) scale *= coef;
+  }
+  const float step_size = lr / bc1;
+  const float inv_sqrt_bc2 = rsqrtf(bc2);
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const float gi = __bfloat162float(g[i]) * scale;
+    float pi = p32[i] * (1.f - lr * wd);
+    const float mi = b1 * m[i] + (1.f - b1) * gi;
+    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+    pi -= step_size * mi / (sqrtf(vi) * inv_sqrt_bc2 + eps);
+    m[i] = mi;
+    v[i] = vi;
+    p32[i] = pi;
+    p16[i] = __float2bfloat16(pi);
+  }
+}
+
+inline int blocks_for(long n, int threads, int cap = 148 * 16) {
+  long b = (n + threads - 1) / threads;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return static_cast<int>(b);
+}
+
+}  // namespace
+
+// ================================================================================ launchers
+int rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, const int* dest, int T, int C, float eps,
+                 cudaStream_t s) {
+  if (C % 8 != 0 || C > NORM_THREADS * 8 * NORM_MAX_CHUNKS) return -1;
+  if (T == 0) return 0;
+  const int grid = T < 148 * 8 ? T : 148 * 8;
+  rms_norm_fwd_kernel<<<grid, NORM_THREADS, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x),
+                                                     reinterpret_cast<const __nv_bfloat16*>(w),
+                                                     reinterpret_cast<__nv_bfloat16*>(y), rstd, dest, T, C, eps);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int rms_norm_bwd_blocks(int T) { return T < 148 * 2 ? (T > 0 ? T : 1) : 148 * 2; }
+
+int rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const int* dest, void* dx,
+                 float* dw_partial, void* dw, int T, int C, cudaStream_t s) {
+  if (C % 8 != 0 || C > NORM_THREADS * 8 * NORM_MAX_CHUNKS) return -1;
+  const int grid = rms_norm_bwd_blocks(T);
+  rms_norm_bwd_kernel<<<grid, NORM_THREADS, 0, s>>>(
+      reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x),
+      reinterpret_cast<const __nv_bfloat16*>(w), rstd, dest, reinterpret_cast<__nv_bfloat16*>(dx), dw_partial, T, C);
+  reduce_partials_kernel<<<(C + 255) / 256, 256, 0, s>>>(dw_partial, reinterpret_cast<__nv_bfloat16*>(dw), grid, C);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int swiglu_bwd(const void* dh, const void* gu, void* dgu, int R, int width_gu, long ld_dh, long ld_gu,
+               cudaStream_t s) {
+  if (width_gu % 32 != 0 || ld_dh % 8 != 0 || ld_gu % 8 != 0) return -1;
+  const int nblk = width_gu / 32;
+  const long total = static_cast<long>(R) * nblk;
+  if (total == 0) return 0;
+  swiglu_bwd_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(
+      reinterpret_cast<const __nv_bfloat16*>(dh), reinterpret_cast<const __nv_bfloat16*>(gu),
+      reinterpret_cast<__nv_bfloat16*>(dgu), R, nblk, ld_dh, ld_gu);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int rope_qk(const void* in, void* out, const float* cos_t, const float* sin_t, int T, int W, int n_rot, int D,
+            int inverse, cudaStream_t s) {
+  if (D % 16 != 0 || W % 8 != 0 || n_rot * D > W) return -1;
+  const long per_row = static_cast<long>(n_rot) * (D / 16) + (W - n_rot * D) / 8;
+  const long total = per_row * T;
+  if (total == 0) return 0;
+  rope_qk_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(
+      reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(out), cos_t, sin_t, T, W, n_rot, D,
+      inverse);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int route_plan(const int* types, int T, int E, int rows, int* dest, int* seg, int* segk, int* inv, cudaStream_t s) {
+  if (E < 1 || E > ROUTE_MAX_E) return -1;
+  route_plan_kernel<<<1, ROUTE_THREADS, 0, s>>>(types, T, E, rows, dest, seg, segk, inv);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int permute_rows(const void* x, const int* dest, void* out, int T, int C, cudaStream_t s) {
+  if (C % 8 != 0) return -1;
+  if (T == 0) return 0;
+  permute_rows_kernel<<<T < 148 * 16 ? T : 148 * 16, 128, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), dest,
+                                                                  reinterpret_cast<__nv_bfloat16*>(out), T, C);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int gather_rows(const void* x, const int* idx, void* out, int T, int C, cudaStream_t s) {
+  if (C % 8 != 0) return -1;
+  if (T == 0) return 0;
+  gather_rows_kernel<<<T < 148 * 16 ? T : 148 * 16, 128, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), idx,
+                                                                 reinterpret_cast<__nv_bfloat16*>(out), T, C);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int column_sum(const void* x, float* acc_zeroed, void* out_bf16, int R, int C, cudaStream_t s) {
+  if (R == 0 || C == 0) return 0;
+  const int pairs = (C + 1) / 2;
+  int ysplit = (R + 255) / 256;
+  if (ysplit > 256) ysplit = 256;
+  const int rpb = (R + ysplit - 1) / ysplit;
+  dim3 grid((pairs + 127) / 128, ysplit);
+  column_sum_kernel<<<grid, 128, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), acc_zeroed, R, C, rpb);
+  f32_to_bf16_kernel<<<(C + 255) / 256, 256, 0, s>>>(acc_zeroed, reinterpret_cast<__nv_bfloat16*>(out_bf16), C);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int ce_fwd(const void* logits, const long* labels, float* loss, float* lse, long* pred, int R, int V, long ld,
+           cudaStream_t s) {
+  if (R == 0) return 0;
+  ce_fwd_kernel<<<R, CE_THREADS, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(logits), labels, loss, lse, pred, R, V,
+                                         ld);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int ce_bwd(void* logits, const long* labels, const float* lse, const float* dloss, int R, int V, long ld,
+           cudaStream_t s) {
+  if (R == 0) return 0;
+  ce_bwd_kernel<<<R, CE_THREADS, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(logits), labels, lse, dloss, R, V, ld);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int sumsq_bf16(const void* g, long n, float* out, cudaStream_t s) {
+  if (n == 0) return 0;
+  sumsq_bf16_kernel<<<blocks_for(n / 8 + 1, 256, 148 * 8), 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(g), n,
+                                                                        out);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int adamw_step(void* p16, float* p32, float* m, float* v, const void* g, long n, const float* hyper,
+               const float* norm_sq, cudaStream_t s) {
+  if (n == 0) return 0;
+  adamw_kernel<<<blocks_for(n, 256, 148 * 16), 256, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(p16), p32, m, v,
+                                                            reinterpret_cast<const __nv_bfloat16*>(g), n, hyper,
+                                                            norm_sq, nullptr);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace wx

@@ -1,6 +1,30 @@
-// Host launchers of the non-GEMM kernels (raw pointers + stream; no torch types).
+// Host launchers of the non-GEMM kernels (raw pointers + stream; no torch types). Every function
+// returns a CUDA error code (0 = ok) or a negative value for an unsupported shape.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
 
-namespace wx {}  // namespace wx
+namespace wx {
+
+int rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, const int* dest, int T, int C, float eps,
+                 cudaStream_t s);
+int rms_norm_bwd_blocks(int T);
+int rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const int* dest, void* dx,
+                 float* dw_partial, void* dw, int T, int C, cudaStream_t s);
+int swiglu_bwd(const void* dh, const void* gu, void* dgu, int R, int width_gu, long ld_dh, long ld_gu,
+               cudaStream_t s);
+int rope_qk(const void* in, void* out, const float* cos_t, const float* sin_t, int T, int W, int n_rot, int D,
+            int inverse, cudaStream_t s);
+int route_plan(const int* types, int T, int E, int rows, int* dest, int* seg, int* segk, int* inv, cudaStream_t s);
+int permute_rows(const void* x, const int* dest, void* out, int T, int C, cudaStream_t s);
+int gather_rows(const void* x, const int* idx, void* out, int T, int C, cudaStream_t s);
+int column_sum(const void* x, float* acc_zeroed, void* out_bf16, int R, int C, cudaStream_t s);
+int ce_fwd(const void* logits, const long* labels, float* loss, float* lse, long* pred, int R, int V, long ld,
+           cudaStream_t s);
+int ce_bwd(void* logits, const long* labels, const float* lse, const float* dloss, int R, int V, long ld,
+           cudaStream_t s);
+int sumsq_bf16(const void* g, long n, float* out, cudaStream_t s);
+int adamw_step(void* p16, float* p32, float* m, float* v, const void* g, long n, const float* hyper,
+               const float* norm_sq, cudaStream_t s);
+
+}  // namespace wx

@@ -21,6 +21,7 @@ SOURCES = [
     "bindings.cpp",
     "kernel_bindings.cpp",
     "gemm.cu",
+    "kernels.cu",
 ]
 
 NVCC_FLAGS = [

@@ -1,0 +1,574 @@
+"""Differentiable operator API used by the model code.
+
+Dispatch rule (no multi-backend layer): a CUDA tensor runs the hand-written sm_100a kernels of the
+in-tree extension and raises if the extension is missing; a CPU tensor runs the PyTorch oracle in
+:mod:`wallx_b200.ops.ref`.
+
+Layouts are B200-first rather than the reference's: activations are token-packed ``[T, C]`` (no
+padding rows), q/k/v live in one ``[T, (Hq + 2 Hkv) * D]`` buffer written by one fused GEMM, FFN
+gate/up weights are interleaved in 16-row blocks so SwiGLU runs in the GEMM epilogue, and expert
+routing uses 128-row aligned segments so that forward, dgrad and wgrad are all tile-aligned.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import ref
+from . import gemm as G
+from . import _ext
+
+
+def _is_cuda(x: torch.Tensor) -> bool:
+    return x.is_cuda
+
+
+def _C():
+    return _ext.get()
+
+
+def _pitch_ok(t: torch.Tensor) -> bool:
+    return t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0
+
+
+def _aligned2d(t: torch.Tensor) -> torch.Tensor:
+    """Return ``t`` or a copy whose row pitch is a multiple of 16 bytes (view of a padded buffer)."""
+    if _pitch_ok(t):
+        return t
+    rows, cols = t.shape
+    pc = (cols + 7) // 8 * 8
+    buf = torch.zeros((rows, pc), device=t.device, dtype=t.dtype)
+    buf[:, :cols].copy_(t)
+    return buf[:, :cols]
+
+
+# ----------------------------------------------------------------------------- linear
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, b, residual):
+        x2 = _aligned2d(x)
+        w2 = _aligned2d(w)
+        out = torch.empty((x.shape[0], w.shape[0]), device=x.device, dtype=torch.bfloat16)
+        G.launch([G.GemmSpec(x2, w2, out, bias=b, residual=residual)])
+        ctx.save_for_backward(x, w)
+        ctx.has_bias = b is not None
+        ctx.has_res = residual is not None
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dy2 = _aligned2d(dy)
+        dx = dw = db = dres = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty_like(x)
+            # dx[m, k] = sum_n dy[m, n] w[n, k]: B(n'=k, k'=n) is w read as MN-major
+            G.launch([G.GemmSpec(dy2, _aligned2d(w), dx, b_mn=True)])
+        if ctx.needs_input_grad[1]:
+            dw = torch.empty_like(w)
+            # dw[n, k] = sum_m dy[m, n] x[m, k]: both operands MN-major over the token axis
+            G.launch([G.GemmSpec(dy2, _aligned2d(x), dw, a_mn=True, b_mn=True)])
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = column_sum(dy)
+        if ctx.has_res and ctx.needs_input_grad[3]:
+            dres = dy
+        return dx, dw, db, dres
+
+
+def column_sum(x: torch.Tensor) -> torch.Tensor:
+    """Sum over rows of a ``[R, C]`` tensor in fp32, returned in x's dtype (bias gradients)."""
+    if _is_cuda(x) and x.dtype == torch.bfloat16:
+        return _C().column_sum(x.contiguous())
+    return x.float().sum(0).to(x.dtype)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None,
+           residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ w.T + b (+ residual)`` over the last dimension; residual add is fused on CUDA."""
+    shp = x.shape
+    x2 = x.reshape(-1, shp[-1])
+    if _is_cuda(x2):
+        if x2.dtype != torch.bfloat16:
+            raise TypeError("CUDA path is bf16; cast the model and inputs to bfloat16")
+        r2 = residual.reshape(-1, w.shape[0]) if residual is not None else None
+        if r2 is not None and not (r2.stride(1) == 1):
+            r2 = r2.contiguous()
+        y = _LinearFn.apply(x2 if x2.stride(1) == 1 else x2.contiguous(), w, b, r2)
+    else:
+        y = ref.linear(x2, w, b)
+        if residual is not None:
+            y = y + residual.reshape(-1, w.shape[0])
+    return y.reshape(*shp[:-1], w.shape[0])
+
+
+def linear_gelu(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor]) -> torch.Tensor:
+    """``gelu(x @ w.T + b)`` (exact erf GELU). Fused into the GEMM epilogue when no grad is needed."""
+    if _is_cuda(x) and not (torch.is_grad_enabled() and (x.requires_grad or w.requires_grad)):
+        x2 = _aligned2d(x.reshape(-1, x.shape[-1]))
+        out = torch.empty((x2.shape[0], w.shape[0]), device=x.device, dtype=torch.bfloat16)
+        G.launch([G.GemmSpec(x2, _aligned2d(w), out, bias=b, flags=G.ACT_GELU)])
+        return out.reshape(*x.shape[:-1], w.shape[0])
+    return torch.nn.functional.gelu(linear(x, w, b))
+
+
+# ----------------------------------------------------------------------------- RMSNorm
+class _RmsNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps, dest, out_rows):
+        y, rstd = _C().rms_norm_fwd(x, w, float(eps), dest, int(out_rows))
+        ctx.save_for_backward(x, w, rstd, dest if dest is not None else torch.empty(0))
+        ctx.has_dest = dest is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, rstd, dest = ctx.saved_tensors
+        dx, dw = _C().rms_norm_bwd(dy.contiguous(), x, w, rstd, dest if ctx.has_dest else None)
+        return dx, dw, None, None, None
+
+
+def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float, dest: Optional[torch.Tensor] = None,
+             out_rows: int = 0) -> torch.Tensor:
+    """RMSNorm over the last dimension (fp32 statistics).
+
+    With ``dest`` (int32 ``[T]``) row ``t`` of the result is written to row ``dest[t]`` of a
+    zero-filled ``[out_rows, C]`` buffer: the token-type permutation of the expert FFN is fused
+    into the normalisation that precedes it.
+    """
+    shp = x.shape
+    x2 = x.reshape(-1, shp[-1])
+    if _is_cuda(x2):
+        y = _RmsNormFn.apply(x2.contiguous(), w, eps, dest, out_rows)
+        return y if dest is not None else y.reshape(shp)
+    y = ref.rms_norm(x2, w, eps)
+    if dest is not None:
+        return ref.permute_rows(y, dest.long(), out_rows)
+    return y.reshape(shp)
+
+
+# ----------------------------------------------------------------------------- SwiGLU FFN pieces
+class _GateUpFn(torch.autograd.Function):
+    """h = silu(g) * u with [g | u] = x @ w_gu.T (+ b) interleaved in 16-column blocks."""
+
+    @staticmethod
+    def forward(ctx, x, w_gu, b_gu):
+        M, N = x.shape[0], w_gu.shape[0]
+        gu = torch.empty((M, N), device=x.device, dtype=torch.bfloat16)
+        h = torch.empty((M, N // 2), device=x.device, dtype=torch.bfloat16)
+        G.launch([G.GemmSpec(x, w_gu, h, out2=gu, bias=b_gu, flags=G.ACT_SWIGLU)])
+        ctx.save_for_backward(x, w_gu, gu)
+        ctx.has_bias = b_gu is not None
+        return h
+
+    @staticmethod
+    def backward(ctx, dh):
+        x, w_gu, gu = ctx.saved_tensors
+        dgu = _C().swiglu_bwd(dh.contiguous(), gu)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty_like(x)
+            G.launch([G.GemmSpec(dgu, w_gu, dx, b_mn=True)])
+        if ctx.needs_input_grad[1]:
+            dw = torch.empty_like(w_gu)
+            G.launch([G.GemmSpec(dgu, x, dw, a_mn=True, b_mn=True)])
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = column_sum(dgu)
+        return dx, dw, db
+
+
+def gate_up_swiglu(x: torch.Tensor, w_gu: torch.Tensor, b_gu: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Fused gate/up projection + SwiGLU; ``w_gu`` is ``[2I, K]`` interleaved in 16-row blocks."""
+    x2 = x.reshape(-1, x.shape[-1])
+    if _is_cuda(x2):
+        h = _GateUpFn.apply(x2.contiguous(), w_gu, b_gu)
+    else:
+        h = ref.swiglu_interleaved(ref.linear(x2, w_gu, b_gu))
+    return h.reshape(*x.shape[:-1], w_gu.shape[0] // 2)
+
+
+# ----------------------------------------------------------------------------- dual-expert FFN
+class RoutePlan:
+    """Grouping of tokens by expert (token type) for one batch; shared by every decoder layer.
+
+    ``dest`` int32 ``[T]``: row of each token in the grouped buffer (segment starts are multiples of
+    128 rows). ``seg`` int32 ``[E, 4]`` = ``(start, count, -1, -1)`` and ``segk`` = ``(-1, -1, start,
+    padded_count)`` live on the device and are read by the grouped GEMM directly (row-segment
+    problems and reductions over a segment), so no launch needs host-side sizes. ``inv`` int32
+    ``[rows]`` maps a grouped row back to its token (-1 on padding rows). ``rows`` is the host-side
+    upper bound of the grouped buffer height.
+    """
+
+    def __init__(self, dest, seg, segk, inv, rows: int):
+        self.dest, self.seg, self.segk, self.inv, self.rows = dest, seg, segk, inv, rows
+
+
+def route_rows(T: int, num_experts: int) -> int:
+    return (T + 127) // 128 * 128 + 128 * (num_experts - 1)
+
+
+def make_route_plan(token_types: torch.Tensor, num_experts: int) -> RoutePlan:
+    """Build the plan. On CUDA this is one kernel (ballot + prefix count per expert id) and no host
+    sync: the buffer height is bounded by ``round_up(T, 128) + 128 (E - 1)``.
+
+    Replaces the reference's radix sort + row-map kernels (csrc/permute.cu:39-67, 450-494) and the
+    per-expert ``.sum()`` host syncs (modeling_qwen2_5_vl_act.py:1275-1283).
+    """
+    tt = token_types.reshape(-1)
+    T = tt.numel()
+    rows = route_rows(T, num_experts)
+    if _is_cuda(tt):
+        dest, seg, segk, inv = _C().route_plan(tt.to(torch.int32).contiguous(), int(num_experts), int(rows))
+        return RoutePlan(dest, seg, segk, inv, rows)
+    dest, seg3 = ref.route_plan(tt, num_experts, 128)
+    neg = torch.full_like(seg3[:, 0], -1)
+    seg = torch.stack([seg3[:, 0], seg3[:, 1], neg, neg], dim=1).to(torch.int32)
+    segk = torch.stack([neg, neg, seg3[:, 0], seg3[:, 2]], dim=1).to(torch.int32)
+    inv = torch.full((rows,), -1, dtype=torch.int32)
+    inv[dest] = torch.arange(T, dtype=torch.int32)
+    return RoutePlan(dest.to(torch.int32), seg, segk, inv, rows)
+
+
+class _MoeFfnFn(torch.autograd.Function):
+    """Grouped gate/up+SwiGLU, then grouped down-projection with the un-permute (row scatter) and
+    the residual add fused into its epilogue. Two problems (experts) per launch."""
+
+    @staticmethod
+    def forward(ctx, xp, residual, dest, seg, segk, inv, n_exp, *weights):
+        # weights = (w_gu_0, w_down_0, w_gu_1, w_down_1, ...)
+        rows, H = xp.shape
+        T = dest.numel()
+        wmax = max(weights[2 * e].shape[0] for e in range(n_exp))
+        gu = torch.empty((rows, wmax), device=xp.device, dtype=torch.bfloat16)
+        h = torch.empty((rows, wmax // 2), device=xp.device, dtype=torch.bfloat16)
+        out = torch.empty((T, H), device=xp.device, dtype=torch.bfloat16)
+        specs = [G.GemmSpec(xp, weights[2 * e], h, out2=gu, M=rows, dyn=seg[e],
+                            flags=G.ACT_SWIGLU | G.ZERO_PAD_ROWS) for e in range(n_exp)]
+        for i in range(0, n_exp, 2):
+            G.launch(specs[i:i + 2])
+        specs = []
+        for e in range(n_exp):
+            w_dn = weights[2 * e + 1]
+            specs.append(G.GemmSpec(h[:, : w_dn.shape[1]], w_dn, out, M=rows, dyn=seg[e], row_map=inv,
+                                    residual=residual))
+        for i in range(0, n_exp, 2):
+            G.launch(specs[i:i + 2])
+        ctx.save_for_backward(xp, dest, seg, segk, gu, h, *weights)
+        ctx.n_exp = n_exp
+        ctx.has_res = residual is not None
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        xp, dest, seg, segk, gu, h, *weights = ctx.saved_tensors
+        n_exp = ctx.n_exp
+        rows, H = xp.shape
+        dout = dout.contiguous()
+        dyp = _C().permute_rows(dout, dest, rows)  # grouped order, zero padding rows
+        wmax = gu.shape[1]
+        dh = torch.empty((rows, wmax // 2), device=xp.device, dtype=torch.bfloat16)
+        specs = []
+        for e in range(n_exp):
+            w_dn = weights[2 * e + 1]
+            specs.append(G.GemmSpec(dyp, w_dn, dh[:, : w_dn.shape[1]], M=rows, dyn=seg[e], b_mn=True,
+                                    flags=G.ZERO_PAD_ROWS))
+        for i in range(0, n_exp, 2):
+            G.launch(specs[i:i + 2])
+        grads = [None] * (2 * n_exp)
+        specs = []
+        for e in range(n_exp):
+            w_dn = weights[2 * e + 1]
+            I = w_dn.shape[1]
+            dw = torch.zeros_like(w_dn)  # stays zero when the expert has no tokens
+            grads[2 * e + 1] = dw
+            # dw[hid, i] = sum over the expert's (128-padded) token segment of dy[t, hid] h[t, i]
+            specs.append(G.GemmSpec(dyp, h[:, :I], dw, a_mn=True, b_mn=True, M=H, N=I, K=rows, dyn=segk[e]))
+        for i in range(0, n_exp, 2):
+            G.launch(specs[i:i + 2])
+        dgu = _C().swiglu_bwd(dh, gu)
+        dxp = torch.empty((rows, H), device=xp.device, dtype=torch.bfloat16)
+        specs = []
+        for e in range(n_exp):
+            w_gu = weights[2 * e]
+            specs.append(G.GemmSpec(dgu[:, : w_gu.shape[0]], w_gu, dxp, M=rows, dyn=seg[e], b_mn=True))
+        for i in range(0, n_exp, 2):
+            G.launch(specs[i:i + 2])
+        specs = []
+        for e in range(n_exp):
+            w_gu = weights[2 * e]
+            W = w_gu.shape[0]
+            dw = torch.zeros_like(w_gu)
+            grads[2 * e] = dw
+            specs.append(G.GemmSpec(dgu[:, :W], xp, dw, a_mn=True, b_mn=True, M=W, N=H, K=rows, dyn=segk[e]))
+        for i in range(0, n_exp, 2):
+            G.launch(specs[i:i + 2])
+        dres = dout if ctx.has_res else None
+        return (dxp, dres, None, None, None, None, None, *grads)
+
+
+def moe_ffn(xp: torch.Tensor, residual: Optional[torch.Tensor], plan: RoutePlan,
+            weights: Sequence[Tuple[torch.Tensor, torch.Tensor]]) -> torch.Tensor:
+    """Token-type-routed expert FFN on a grouped input.
+
+    ``xp`` ``[rows, H]`` is the grouped (permuted, zero-padded) input produced by
+    :func:`rms_norm` with ``dest=plan.dest``; ``weights[e] = (w_gate_up_interleaved [2 I_e, H],
+    w_down [H, I_e])``. Returns ``residual + ffn(x)`` in token order ``[T, H]``.
+
+    Reference path replaced: permute -> per-expert 3x cuBLAS loop -> unpermute
+    (modeling_qwen2_5_vl_act.py:138-157) and the dormant CUTLASS grouped GEMM
+    (fusions/ops.py:6-165).
+    """
+    n_exp = len(weights)
+    if _is_cuda(xp):
+        flat = []
+        for wg, wd in weights:
+            flat += [wg, wd]
+        return _MoeFfnFn.apply(xp, residual, plan.dest, plan.seg, plan.segk, plan.inv, n_exp, *flat)
+    T = plan.dest.numel()
+    out_p = torch.zeros_like(xp)
+    seg = plan.seg.tolist()
+    for e, (wg, wd) in enumerate(weights):
+        s, c = seg[e][0], seg[e][1]
+        if c == 0:
+            continue
+        he = ref.swiglu_interleaved(ref.linear(xp[s:s + c], wg))
+        out_p = out_p.clone()
+        out_p[s:s + c] = ref.linear(he, wd)
+    y = ref.unpermute_rows(out_p, plan.dest.long())
+    return y + residual if residual is not None else y
+
+
+# ----------------------------------------------------------------------------- rotary
+class _RopeQkFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, n_rot_heads, head_dim):
+        out = _C().rope_qk(qkv, cos, sin, int(n_rot_heads), int(head_dim), False)
+        ctx.save_for_backward(cos, sin)
+        ctx.n_rot_heads, ctx.head_dim = n_rot_heads, head_dim
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        cos, sin = ctx.saved_tensors
+        dqkv = _C().rope_qk(dout.contiguous(), cos, sin, int(ctx.n_rot_heads), int(ctx.head_dim), True)
+        return dqkv, None, None, None, None
+
+
+def rope_qk(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, n_rot_heads: int, head_dim: int) -> torch.Tensor:
+    """Rotate the first ``n_rot_heads`` heads (q then k) of a packed ``[T, heads*D]`` buffer;
+    the remaining (v) columns are copied. cos/sin are fp32 ``[T, D]`` (rotate-half form).
+
+    Replaces csrc/rope.cu:48-330 (forward and backward share one kernel here: the backward is the
+    inverse rotation)."""
+    if _is_cuda(qkv):
+        return _RopeQkFn.apply(qkv.contiguous(), cos, sin, n_rot_heads, head_dim)
+    T = qkv.shape[0]
+    rot = qkv[:, : n_rot_heads * head_dim].reshape(T, n_rot_heads, head_dim)
+    rot = ref.apply_rope(rot, cos, sin).reshape(T, -1)
+    return torch.cat([rot, qkv[:, n_rot_heads * head_dim:]], dim=-1)
+
+
+# ----------------------------------------------------------------------------- attention
+class AttnMeta:
+    """Host-side description of the packed sequences of one attention call.
+
+    Queries and keys may live in different buffers with different per-sequence lengths (prefix
+    reuse: few new queries against a long cached key range). The causal rule is bottom-right
+    aligned: query ``i`` of a sequence sees keys ``j <= i + (Lk - Lq)``; in addition a query
+    flagged in ``bidir_q`` sees every key flagged in ``bidir_k`` (the action-token block).
+    """
+
+    def __init__(self, cu_q: Sequence[int], device, causal: bool, bidir_q: Optional[torch.Tensor] = None,
+                 cu_k: Optional[Sequence[int]] = None, bidir_k: Optional[torch.Tensor] = None,
+                 cache_rows: Optional[torch.Tensor] = None):
+        self.cu_q_host = [int(c) for c in cu_q]
+        self.cu_k_host = [int(c) for c in cu_k] if cu_k is not None else self.cu_q_host
+        self.self_attn = cu_k is None
+        self.cu_q = torch.tensor(self.cu_q_host, dtype=torch.int32, device=device)
+        self.cu_k = self.cu_q if cu_k is None else torch.tensor(self.cu_k_host, dtype=torch.int32, device=device)
+        lq = [self.cu_q_host[i + 1] - self.cu_q_host[i] for i in range(len(self.cu_q_host) - 1)]
+        lk = [self.cu_k_host[i + 1] - self.cu_k_host[i] for i in range(len(self.cu_k_host) - 1)]
+        self.max_q = max(lq) if lq else 0
+        self.max_k = max(lk) if lk else 0
+        self.causal = bool(causal)
+        self.bidir_q = bidir_q
+        self.bidir_k = bidir_k if bidir_k is not None else (bidir_q if cu_k is None else None)
+        self.cache_rows = cache_rows
+        self._dev = {}
+
+    # legacy names used by the packed self-attention path
+    @property
+    def cu_host(self):
+        return self.cu_q_host
+
+    def device_tables(self, device):
+        """Per-token tables for the kernels: for every query row its key range and causal limit."""
+        t = self._dev.get("tables")
+        if t is None:
+            nq, nk = self.cu_q_host[-1], self.cu_k_host[-1]
+            k_lo = torch.empty(nq, dtype=torch.int32)
+            k_hi = torch.empty(nq, dtype=torch.int32)
+            k_lim = torch.empty(nq, dtype=torch.int32)  # last visible key (absolute row) under causality
+            q_lo = torch.empty(nk, dtype=torch.int32)
+            q_hi = torch.empty(nk, dtype=torch.int32)
+            for b in range(len(self.cu_q_host) - 1):
+                q0, q1 = self.cu_q_host[b], self.cu_q_host[b + 1]
+                k0, k1 = self.cu_k_host[b], self.cu_k_host[b + 1]
+                k_lo[q0:q1] = k0
+                k_hi[q0:q1] = k1
+                off = (k1 - k0) - (q1 - q0)
+                k_lim[q0:q1] = torch.arange(q1 - q0, dtype=torch.int32) + (k0 + off)
+                q_lo[k0:k1] = q0
+                q_hi[k0:k1] = q1
+            if not self.causal:
+                k_lim = k_hi - 1
+            fq = self.bidir_q.to(torch.int32).cpu() if self.bidir_q is not None else torch.zeros(nq, dtype=torch.int32)
+            fk = self.bidir_k.to(torch.int32).cpu() if self.bidir_k is not None else torch.zeros(nk, dtype=torch.int32)
+            qtab = torch.stack([k_lo, k_hi, k_lim, fq], dim=1).contiguous().to(device)
+            ktab = torch.stack([q_lo, q_hi, fk, torch.zeros_like(fk)], dim=1).contiguous().to(device)
+            t = (qtab, ktab)
+            self._dev["tables"] = t
+        return t
+
+
+def _attention_torch(q, k, v, meta: AttnMeta, hq, hkv, d, scale):
+    """Per-sequence PyTorch evaluation (CPU oracle path)."""
+    outs = []
+    rep = hq // hkv
+    for b in range(len(meta.cu_q_host) - 1):
+        q0, q1 = meta.cu_q_host[b], meta.cu_q_host[b + 1]
+        k0, k1 = meta.cu_k_host[b], meta.cu_k_host[b + 1]
+        lq, lk = q1 - q0, k1 - k0
+        qb = q[q0:q1].reshape(lq, hq, d).float()
+        kb = k[k0:k1].reshape(lk, hkv, d).float()
+        vb = v[k0:k1].reshape(lk, hkv, d).float()
+        if rep > 1:
+            kb = kb.repeat_interleave(rep, dim=1)
+            vb = vb.repeat_interleave(rep, dim=1)
+        s_ = torch.einsum("qhd,khd->hqk", qb, kb) * scale
+        if meta.causal:
+            ii = torch.arange(lq, device=q.device).unsqueeze(1) + (lk - lq)
+            jj = torch.arange(lk, device=q.device).unsqueeze(0)
+            allow = jj <= ii
+            if meta.bidir_q is not None and meta.bidir_k is not None:
+                allow = allow | (meta.bidir_q[q0:q1].bool().unsqueeze(1) & meta.bidir_k[k0:k1].bool().unsqueeze(0))
+            s_ = s_.masked_fill(~allow.unsqueeze(0), float("-inf"))
+        p = torch.softmax(s_, dim=-1)
+        outs.append(torch.einsum("hqk,khd->qhd", p, vb).reshape(lq, hq * d))
+    return torch.cat(outs, dim=0).to(q.dtype)
+
+
+class _AttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, meta, hq, hkv, d, scale):
+        qtab, ktab = meta.device_tables(q.device)
+        out, lse = _C().attn_fwd(q, k, v, qtab, int(hq), int(hkv), int(d), float(scale))
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.meta, ctx.hq, ctx.hkv, ctx.d, ctx.scale = meta, hq, hkv, d, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        qtab, ktab = ctx.meta.device_tables(q.device)
+        dq, dk, dv = _C().attn_bwd(dout.contiguous(), q, k, v, out, lse, qtab, ktab, int(ctx.hq), int(ctx.hkv),
+                                   int(ctx.d), float(ctx.scale))
+        return dq, dk, dv, None, None, None, None, None
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, meta: AttnMeta, hq: int, hkv: int, d: int,
+              scale: Optional[float] = None) -> torch.Tensor:
+    """Varlen attention. ``q [Tq, hq*d]``, ``k/v [Tk, hkv*d]`` (row-strided views are fine);
+    returns ``[Tq, hq*d]``. See :class:`AttnMeta` for the masking rule.
+
+    Replaces flash-attn's ``flash_attn_func`` / ``flash_attn_varlen_func``
+    (modeling_qwen2_5_vl.py:208-210, 1008-1015) and, with a key range longer than the query range,
+    the reference's full-sequence recompute per denoise step (modeling_qwen2_5_vl_act.py:1906-1952)."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    if _is_cuda(q):
+        return _AttnFn.apply(q, k, v, meta, hq, hkv, d, scale)
+    return _attention_torch(q, k, v, meta, hq, hkv, d, scale)
+
+
+def attention_packed(qkv: torch.Tensor, meta: AttnMeta, hq: int, hkv: int, d: int,
+                     scale: Optional[float] = None) -> torch.Tensor:
+    """Self-attention over a packed ``[T, (hq + 2 hkv) * d]`` q|k|v buffer -> ``[T, hq * d]``."""
+    q = qkv[:, : hq * d]
+    k = qkv[:, hq * d:(hq + hkv) * d]
+    v = qkv[:, (hq + hkv) * d:]
+    return attention(q, k, v, meta, hq, hkv, d, scale)
+
+
+# ----------------------------------------------------------------------------- fused LM head + CE
+class _LmHeadCeFn(torch.autograd.Function):
+    """Chunked LM head + cross entropy: logits exist only one vocabulary-wide row block at a time
+    and only for rows that carry a label."""
+
+    CHUNK = 4096
+
+    @staticmethod
+    def forward(ctx, hidden, weight, labels):
+        R = hidden.shape[0]
+        V = weight.shape[0]
+        loss = torch.empty(R, device=hidden.device, dtype=torch.float32)
+        pred = torch.empty(R, device=hidden.device, dtype=torch.int64)
+        lse = torch.empty(R, device=hidden.device, dtype=torch.float32)
+        w2 = _aligned2d(weight)
+        for s in range(0, R, _LmHeadCeFn.CHUNK):
+            e = min(R, s + _LmHeadCeFn.CHUNK)
+            logits = torch.empty((e - s, V), device=hidden.device, dtype=torch.bfloat16)
+            G.launch([G.GemmSpec(hidden[s:e], w2, logits)])
+            _C().ce_fwd(logits, labels[s:e], loss[s:e], lse[s:e], pred[s:e])
+        ctx.save_for_backward(hidden, weight, labels, lse)
+        ctx.mark_non_differentiable(pred)
+        return loss, pred
+
+    @staticmethod
+    def backward(ctx, dloss, _dpred):
+        hidden, weight, labels, lse = ctx.saved_tensors
+        R, V = hidden.shape[0], weight.shape[0]
+        w2 = _aligned2d(weight)
+        dh = torch.empty_like(hidden)
+        dw = torch.zeros((V, hidden.shape[1]), device=hidden.device, dtype=torch.float32)
+        dloss = dloss.contiguous().float()
+        for s in range(0, R, _LmHeadCeFn.CHUNK):
+            e = min(R, s + _LmHeadCeFn.CHUNK)
+            logits = torch.empty((e - s, V), device=hidden.device, dtype=torch.bfloat16)
+            G.launch([G.GemmSpec(hidden[s:e], w2, logits)])
+            _C().ce_bwd(logits, labels[s:e], lse[s:e], dloss[s:e])  # in place: logits -> dlogits
+            G.launch([G.GemmSpec(logits, w2, dh[s:e], b_mn=True)])
+            G.launch([G.GemmSpec(logits, hidden[s:e], dw, a_mn=True, b_mn=True, flags=G.OUT_FP32 | G.ACCUMULATE)])
+        return dh, dw.to(weight.dtype), None
+
+
+def lm_head_ce(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor):
+    """Per-row cross entropy (0 where ``labels == -100``) and arg-max ids for ``[R, H]`` rows.
+
+    The reference materialises ``[B, S, V]`` logits for every position and then computes an
+    unreduced CE (modeling_qwen2_5_vl_act.py:1406-1444); here only labelled rows reach the head
+    and logits live one row block at a time."""
+    if _is_cuda(hidden):
+        return _LmHeadCeFn.apply(hidden.contiguous(), weight, labels.contiguous())
+    return ref.lm_head_ce(hidden, weight, labels)
+
+
+# ----------------------------------------------------------------------------- misc gathers
+class _GatherRowsFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, idx, out_rows):
+        ctx.save_for_backward(idx)
+        ctx.in_rows = x.shape[0]
+        return x.index_select(0, idx)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (idx,) = ctx.saved_tensors
+        dx = dy.new_zeros((ctx.in_rows, dy.shape[1]))
+        dx.index_add_(0, idx, dy)
+        return dx, None, None
+
+
+def gather_rows(x: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    return x.index_select(0, idx)

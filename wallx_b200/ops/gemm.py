@@ -22,6 +22,7 @@ OUT_FP32 = 1
 ACCUMULATE = 2
 ACT_GELU = 4
 ACT_SWIGLU = 8
+ZERO_PAD_ROWS = 16
 
 
 class GemmSpec:
