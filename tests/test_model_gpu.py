@@ -1,0 +1,62 @@
+"""Tiny VLA model: GPU bf16 kernels path vs CPU fp32 oracle path (same weights, same noise)."""
+import copy
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _build(mode):
+    from wallx_b200.config import tiny_config
+    from wallx_b200.data.collator import add_pack_info
+    from wallx_b200.data.synthetic import make_batch, make_processor
+    from wallx_b200.models import Qwen2_5_VLMoEForAction
+
+    cfg = tiny_config()
+    proc = make_processor(cfg, 16)
+    torch.manual_seed(0)
+    model = Qwen2_5_VLMoEForAction(cfg, processor=proc, use_fast_tokenizer=(mode == "fast"))
+    g = torch.Generator().manual_seed(1)
+    batch = make_batch(cfg, proc, 3, views=2, image_hw=(112, 112), prompt_len=16, horizon=16, mode=mode,
+                       fast_tokens=12, generator=g)
+    batch = add_pack_info(batch, cfg)
+    return cfg, model, batch
+
+
+@pytest.mark.parametrize("mode", ["flow", "fast"])
+def test_tiny_model_gpu_matches_cpu(mode):
+    from wallx_b200.data.collator import to_device
+    from wallx_b200.ops import gemm as G
+
+    cfg, model, batch = _build(mode)
+    model_g = copy.deepcopy(model).to(torch.bfloat16).cuda()
+    model_c = copy.deepcopy(model_g).float().cpu()  # identical (bf16-rounded) weights
+    extra = {}
+    if mode == "flow":
+        gen = torch.Generator().manual_seed(2)
+        extra["flow_noise"] = torch.randn(batch["action_chunk"].shape, generator=gen)
+        extra["flow_time"] = torch.rand(batch["action_chunk"].shape[0], generator=gen) * 0.9
+    out_c = model_c(mode="train", **batch, **extra)
+    out_c.loss.backward()
+    bg = to_device(batch, "cuda", torch.bfloat16)
+    eg = {k: v.cuda() for k, v in extra.items()}
+    out_g = model_g(mode="train", **bg, **eg)
+    out_g.loss.backward()
+    torch.cuda.synchronize()
+    G.check_status()
+    lc, lg = out_c.loss.item(), out_g.loss.item()
+    assert abs(lc - lg) / max(abs(lc), 1e-3) < 0.03, (lc, lg)
+    # gradients: compare the direction of a few large tensors
+    pc = dict(model_c.named_parameters())
+    checked = 0
+    for name, p in model_g.named_parameters():
+        if p.grad is None or pc[name].grad is None or p.numel() < 4096:
+            continue
+        a, b = p.grad.float().cpu().flatten(), pc[name].grad.flatten()
+        if b.norm() < 1e-8:
+            continue
+        cos = torch.dot(a, b) / (a.norm() * b.norm() + 1e-12)
+        assert cos > 0.95, (name, cos.item())
+        checked += 1
+    assert checked > 10

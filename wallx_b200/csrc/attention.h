@@ -1,0 +1,28 @@
+// Host API of the tcgen05 varlen attention kernels (raw pointers + stream).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace wx {
+
+struct AttnShape {
+  int Tq, Tk, hq, hkv, D;
+  long ld_q, ld_k, ld_v;  // row pitch in elements of the q / k / v views
+  float scale;
+  int has_bidir;    // some query carries the bidirectional flag
+  int causal_self;  // self-attention, causal, no bidirectional block: lets dK/dV skip query blocks
+};
+
+// qtab: int32 [Tq, 4] = (k_lo, k_hi, k_lim, flag); ktab: int32 [Tk, 4] = (q_lo, q_hi, flag, 0).
+// lse: fp32 [hq, Tq] (natural log). `status` is set non-zero when a bounded wait ran out.
+int attn_fwd(const AttnShape& s, const void* q, const void* k, const void* v, const void* qtab, const void* ktab,
+             void* out, long ld_out, float* lse, cudaStream_t stream, int* status);
+
+// delta: fp32 scratch [hq, Tq]; part_k / part_v: fp32 scratch [hq/hkv, Tk, hkv*D], needed only
+// when hq != hkv (partial dK/dV per query head of a group, summed at the end).
+int attn_bwd(const AttnShape& s, const void* q, const void* k, const void* v, const void* out, long ld_o,
+             const void* dout, long ld_do, const float* lse, const void* qtab, const void* ktab, float* delta,
+             void* dq, long ld_dq, void* dk, long ld_dk, void* dv, long ld_dv, float* part_k, float* part_v,
+             cudaStream_t stream, int* status);
+
+}  // namespace wx

@@ -9,6 +9,7 @@
 #include <tuple>
 #include <vector>
 
+#include "attention.h"
 #include "gemm.h"
 #include "kernels.h"
 
@@ -104,6 +105,73 @@ void gemm_grouped(const std::vector<GemmTuple>& calls, int64_t force_bn) {
   TORCH_CHECK(rc == 0, "gemm_launch failed with code ", rc);
 }
 
+bool view2d_ok(const at::Tensor& t) {
+  return t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 2 && t.stride(1) == 1 && (t.stride(0) % 8) == 0 &&
+         (reinterpret_cast<uintptr_t>(t.data_ptr()) % 16) == 0;
+}
+
+wx::AttnShape attn_shape(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, int64_t hq, int64_t hkv,
+                         int64_t d, double scale, bool has_bidir, bool causal_self) {
+  TORCH_CHECK(view2d_ok(q) && view2d_ok(k) && view2d_ok(v), "attention: q/k/v must be bf16 2-D views with 16-byte aligned rows");
+  TORCH_CHECK(q.size(1) == hq * d && k.size(1) == hkv * d && v.size(1) == hkv * d && k.size(0) == v.size(0),
+              "attention: shape mismatch");
+  wx::AttnShape s;
+  s.Tq = q.size(0);
+  s.Tk = k.size(0);
+  s.hq = hq;
+  s.hkv = hkv;
+  s.D = d;
+  s.ld_q = q.stride(0);
+  s.ld_k = k.stride(0);
+  s.ld_v = v.stride(0);
+  s.scale = static_cast<float>(scale);
+  s.has_bidir = has_bidir ? 1 : 0;
+  s.causal_self = causal_self ? 1 : 0;
+  return s;
+}
+
+std::tuple<at::Tensor, at::Tensor> attn_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                                            const at::Tensor& qtab, const at::Tensor& ktab, int64_t hq, int64_t hkv,
+                                            int64_t d, double scale, bool has_bidir) {
+  wx::AttnShape s = attn_shape(q, k, v, hq, hkv, d, scale, has_bidir, false);
+  TORCH_CHECK(qtab.scalar_type() == at::kInt && qtab.is_contiguous() && qtab.size(0) == s.Tq && qtab.size(1) == 4);
+  TORCH_CHECK(ktab.scalar_type() == at::kInt && ktab.is_contiguous() && ktab.size(0) == s.Tk && ktab.size(1) == 4);
+  c10::cuda::CUDAGuard guard(q.device());
+  at::Tensor out = at::empty({s.Tq, hq * d}, q.options());
+  at::Tensor lse = at::empty({hq, s.Tq}, q.options().dtype(at::kFloat));
+  int rc = wx::attn_fwd(s, q.data_ptr(), k.data_ptr(), v.data_ptr(), qtab.data_ptr(), ktab.data_ptr(), out.data_ptr(),
+                        out.stride(0), lse.data_ptr<float>(), at::cuda::getCurrentCUDAStream(),
+                        status_tensor(q.device()).data_ptr<int>());
+  TORCH_CHECK(rc == 0, "attn_fwd failed with code ", rc);
+  return {out, lse};
+}
+
+// dq / dk / dv are written in place into caller-provided (possibly strided) views.
+void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+              const at::Tensor& out, const at::Tensor& lse, const at::Tensor& qtab, const at::Tensor& ktab,
+              at::Tensor& dq, at::Tensor& dk, at::Tensor& dv, int64_t hq, int64_t hkv, int64_t d, double scale,
+              bool has_bidir, bool causal_self) {
+  wx::AttnShape s = attn_shape(q, k, v, hq, hkv, d, scale, has_bidir, causal_self);
+  TORCH_CHECK(view2d_ok(dout) && view2d_ok(out) && view2d_ok(dq) && view2d_ok(dk) && view2d_ok(dv), "attn_bwd: views");
+  c10::cuda::CUDAGuard guard(q.device());
+  auto fo = q.options().dtype(at::kFloat);
+  at::Tensor delta = at::empty({hq, s.Tq}, fo);
+  const int rep = hq / hkv;
+  at::Tensor pk, pv;
+  float *ppk = nullptr, *ppv = nullptr;
+  if (rep > 1) {
+    pk = at::empty({rep, s.Tk, hkv * d}, fo);
+    pv = at::empty({rep, s.Tk, hkv * d}, fo);
+    ppk = pk.data_ptr<float>();
+    ppv = pv.data_ptr<float>();
+  }
+  int rc = wx::attn_bwd(s, q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), out.stride(0), dout.data_ptr(),
+                        dout.stride(0), lse.data_ptr<float>(), qtab.data_ptr(), ktab.data_ptr(), delta.data_ptr<float>(),
+                        dq.data_ptr(), dq.stride(0), dk.data_ptr(), dk.stride(0), dv.data_ptr(), dv.stride(0), ppk, ppv,
+                        at::cuda::getCurrentCUDAStream(), status_tensor(q.device()).data_ptr<int>());
+  TORCH_CHECK(rc == 0, "attn_bwd failed with code ", rc);
+}
+
 }  // namespace
 
 void register_kernel_bindings(pybind11::module_& m);
@@ -111,5 +179,7 @@ void register_kernel_bindings(pybind11::module_& m);
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_grouped", &gemm_grouped, "tcgen05 GEMM: one or two problems in one launch");
   m.def("read_status", &read_status, "read and clear the device-side wait-timeout status");
+  m.def("attn_fwd", &attn_fwd);
+  m.def("attn_bwd", &attn_bwd);
   register_kernel_bindings(m);
 }

@@ -22,6 +22,7 @@ SOURCES = [
     "kernel_bindings.cpp",
     "gemm.cu",
     "kernels.cu",
+    "attention.cu",
 ]
 
 NVCC_FLAGS = [

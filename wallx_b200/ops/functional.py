@@ -460,11 +460,18 @@ def _attention_torch(q, k, v, meta: AttnMeta, hq, hkv, d, scale):
     return torch.cat(outs, dim=0).to(q.dtype)
 
 
+def _attn_flags(meta: AttnMeta):
+    has_bidir = meta.causal and meta.bidir_q is not None and meta.bidir_k is not None
+    causal_self = meta.causal and meta.self_attn and not has_bidir
+    return has_bidir, causal_self
+
+
 class _AttnFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, meta, hq, hkv, d, scale):
         qtab, ktab = meta.device_tables(q.device)
-        out, lse = _C().attn_fwd(q, k, v, qtab, int(hq), int(hkv), int(d), float(scale))
+        has_bidir, _ = _attn_flags(meta)
+        out, lse = _C().attn_fwd(q, k, v, qtab, ktab, int(hq), int(hkv), int(d), float(scale), has_bidir)
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.meta, ctx.hq, ctx.hkv, ctx.d, ctx.scale = meta, hq, hkv, d, scale
         return out
@@ -473,9 +480,41 @@ class _AttnFn(torch.autograd.Function):
     def backward(ctx, dout):
         q, k, v, out, lse = ctx.saved_tensors
         qtab, ktab = ctx.meta.device_tables(q.device)
-        dq, dk, dv = _C().attn_bwd(dout.contiguous(), q, k, v, out, lse, qtab, ktab, int(ctx.hq), int(ctx.hkv),
-                                   int(ctx.d), float(ctx.scale))
+        has_bidir, causal_self = _attn_flags(ctx.meta)
+        dq = torch.empty((q.shape[0], q.shape[1]), device=q.device, dtype=q.dtype)
+        dk = torch.empty((k.shape[0], k.shape[1]), device=q.device, dtype=q.dtype)
+        dv = torch.empty((v.shape[0], v.shape[1]), device=q.device, dtype=q.dtype)
+        _C().attn_bwd(dout.contiguous(), q, k, v, out, lse, qtab, ktab, dq, dk, dv, int(ctx.hq), int(ctx.hkv),
+                      int(ctx.d), float(ctx.scale), has_bidir, causal_self)
         return dq, dk, dv, None, None, None, None, None
+
+
+class _AttnPackedFn(torch.autograd.Function):
+    """Self-attention on one packed q|k|v buffer; the three gradients are written straight into
+    the column ranges of one ``dqkv`` buffer (no slice-backward copies)."""
+
+    @staticmethod
+    def forward(ctx, qkv, meta, hq, hkv, d, scale):
+        qtab, ktab = meta.device_tables(qkv.device)
+        has_bidir, _ = _attn_flags(meta)
+        q, k, v = qkv[:, : hq * d], qkv[:, hq * d:(hq + hkv) * d], qkv[:, (hq + hkv) * d:]
+        out, lse = _C().attn_fwd(q, k, v, qtab, ktab, int(hq), int(hkv), int(d), float(scale), has_bidir)
+        ctx.save_for_backward(qkv, out, lse)
+        ctx.meta, ctx.hq, ctx.hkv, ctx.d, ctx.scale = meta, hq, hkv, d, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse = ctx.saved_tensors
+        hq, hkv, d = ctx.hq, ctx.hkv, ctx.d
+        qtab, ktab = ctx.meta.device_tables(qkv.device)
+        has_bidir, causal_self = _attn_flags(ctx.meta)
+        dqkv = torch.empty_like(qkv)
+        q, k, v = qkv[:, : hq * d], qkv[:, hq * d:(hq + hkv) * d], qkv[:, (hq + hkv) * d:]
+        dq, dk, dv = dqkv[:, : hq * d], dqkv[:, hq * d:(hq + hkv) * d], dqkv[:, (hq + hkv) * d:]
+        _C().attn_bwd(dout.contiguous(), q, k, v, out, lse, qtab, ktab, dq, dk, dv, int(hq), int(hkv), int(d),
+                      float(ctx.scale), has_bidir, causal_self)
+        return dqkv, None, None, None, None, None
 
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, meta: AttnMeta, hq: int, hkv: int, d: int,
@@ -495,6 +534,9 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, meta: AttnMeta,
 def attention_packed(qkv: torch.Tensor, meta: AttnMeta, hq: int, hkv: int, d: int,
                      scale: Optional[float] = None) -> torch.Tensor:
     """Self-attention over a packed ``[T, (hq + 2 hkv) * d]`` q|k|v buffer -> ``[T, hq * d]``."""
+    if _is_cuda(qkv):
+        scale = scale if scale is not None else 1.0 / math.sqrt(d)
+        return _AttnPackedFn.apply(qkv.contiguous(), meta, hq, hkv, d, scale)
     q = qkv[:, : hq * d]
     k = qkv[:, hq * d:(hq + hkv) * d]
     v = qkv[:, (hq + hkv) * d:]
