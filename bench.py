@@ -1,0 +1,275 @@
+"""Headline benchmark: FSDP-style fine-tune throughput (samples/s) of the WALL-OSS-size VLA model.
+
+    python bench.py --gpus N --steps K --warmup W [--impl ours|reference] [--mode flow|fast]
+
+One "step" is one optimizer step over the global batch (per-GPU batch 32 = micro-batch x
+accumulation; global batch 32 x N, i.e. 256 on 8 GPUs: weak scaling). Inputs are synthetic
+(uniform uint8 camera frames, uniform prompt ids, N(0,1) proprio, uniform actions) and the weights
+are random-init at the named architecture. Rank 0 prints one JSON line.
+
+``value`` is timed on the device (CUDA events, barrier + synchronize on both sides, max over
+ranks) with inputs already resident; ``e2e`` repeats the measurement through the public training
+call with, every step, the host-to-device copy of that step's inputs from pinned memory and a
+device-to-host read of the loss.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--mode", default="flow", choices=["flow", "fast"])
+    ap.add_argument("--per-gpu-batch", type=int, default=32)
+    ap.add_argument("--micro-batch", type=int, default=16)
+    ap.add_argument("--action-ffn", type=int, default=2048, help="action expert FFN width (not in the reference repo)")
+    ap.add_argument("--transport", default="auto", choices=["auto", "dist", "symm"])
+    ap.add_argument("--layers", type=int, default=0, help="debug only: override depth (invalidates the number)")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx = float(parts[2])
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def run_reference(args):
+    from wallx_b200.bench import reference_arm
+
+    reference_arm.main(args)
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+
+    from wallx_b200.config import wall_oss_config
+    from wallx_b200.data.collator import add_pack_info, pin_batch, to_device
+    from wallx_b200.data.synthetic import images_to_patches, make_batch, make_processor
+    from wallx_b200.models import Qwen2_5_VLMoEForAction
+    from wallx_b200.ops import _ext
+    from wallx_b200.ops import gemm as G
+    from wallx_b200.parallel.engine import TrainEngine
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+
+    cfg_kw = {}
+    if args.layers:
+        cfg_kw["num_hidden_layers"] = args.layers
+    cfg = wall_oss_config(action_expert_intermediate=args.action_ffn, **cfg_kw)
+    proc = make_processor(cfg, 2048)
+    torch.manual_seed(1234)
+    old = torch.get_default_dtype()
+    torch.set_default_dtype(torch.bfloat16)
+    with torch.device(dev):
+        model = Qwen2_5_VLMoEForAction(cfg, processor=proc, use_fast_tokenizer=(args.mode == "fast"))
+    torch.set_default_dtype(old)
+    model.train()
+
+    accum = max(1, args.per_gpu_batch // args.micro_batch)
+    micro = args.per_gpu_batch // accum
+    transport = args.transport
+    symm = None
+    if transport == "auto":
+        transport = "symm" if world > 1 else "local"
+    if world > 1 and transport == "symm":
+        from wallx_b200.parallel.symm import SymmComm
+
+        symm = SymmComm(dist.group.WORLD, dev)
+    engine = TrainEngine(model, lr=9e-5, weight_decay=0.1, max_grad_norm=1.0, grad_accum=accum, world=world, rank=rank,
+                         transport=transport if world > 1 else "local", symm=symm)
+    n_params = sum(b.numel for b in engine.buffers)
+
+    # ---- synthetic data: a small pool of distinct global batches, pinned on the host
+    gen = torch.Generator().manual_seed(100 + rank)
+    pool = []
+    for _ in range(2):
+        mbs = []
+        for _a in range(accum):
+            b = make_batch(cfg, proc, micro, views=3, image_hw=(256, 256), prompt_len=64, horizon=32, mode=args.mode,
+                           fast_tokens=48, generator=gen, raw_images=True)
+            b = pin_batch(add_pack_info(b, cfg))
+            mbs.append(b)
+        pool.append(mbs)
+    vc = cfg.vision_config
+
+    def stage(b_host):
+        """Host (pinned) -> device copy of one micro-batch, then patchify on the device."""
+        b = to_device(b_host, dev, torch.bfloat16, non_blocking=True)
+        imgs = b.pop("images_uint8")
+        pv, _ = images_to_patches(imgs, vc.patch_size, vc.temporal_patch_size, vc.spatial_merge_size, torch.bfloat16)
+        b["pixel_values"] = pv
+        return b
+
+    def h2d_bytes(b_host):
+        return sum(v.numel() * v.element_size() for k, v in b_host.items()
+                   if isinstance(v, torch.Tensor) and k != "seq_lens")
+
+    def train_step(mbs_dev):
+        loss = None
+        for mb in mbs_dev:
+            out = model(mode="train", **mb)
+            out.loss.backward()
+            loss = out.loss
+        engine.optimizer_step(9e-5)
+        return loss
+
+    resident = [[stage(b) for b in mbs] for mbs in pool]
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- warm-up
+    for i in range(args.warmup):
+        train_step(resident[i % len(resident)])
+    barrier()
+    G.check_status()
+
+    counter = _ext.LaunchCounter.install()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    # ---- timed: device-resident inputs
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        loss = train_step(resident[i % len(resident)])
+    e1.record()
+    barrier()
+    ms_dev = e0.elapsed_time(e1)
+    launches = counter.total
+    counter.uninstall()
+    clocks = sampler.stop() if rank == 0 else None
+    G.check_status()
+    loss_val = float(loss.item())
+
+    # ---- timed: end to end (pinned host -> device every step, loss read back every step)
+    ms_e2e = None
+    bi = bo = 0
+    if not args.no_e2e:
+        for i in range(1):
+            train_step([stage(b) for b in pool[i % len(pool)]])
+        barrier()
+        e0.record()
+        for i in range(args.steps):
+            mbs = [stage(b) for b in pool[i % len(pool)]]
+            l = train_step(mbs)
+            loss_host = l.float().cpu()  # device -> host read of the step's result
+        e1.record()
+        barrier()
+        ms_e2e = e0.elapsed_time(e1)
+        bi = sum(h2d_bytes(b) for b in pool[0])
+        bo = 4
+
+    t = torch.tensor([ms_dev, ms_e2e if ms_e2e is not None else 0.0], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_dev, ms_e2e_max = float(t[0]), float(t[1])
+    global_batch = args.per_gpu_batch * world
+    if rank == 0:
+        value = global_batch * args.steps / (ms_dev / 1e3)
+        rec = {
+            "metric": f"train samples/s, WALL-OSS-{args.mode.upper()}-size fine-tune (max over ranks, device-timed)",
+            "value": round(value, 3), "unit": "samples/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms_dev / args.steps, 3), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+            "config": {
+                "model": f"WALL-OSS-{args.mode.upper()} (Qwen2.5-VL-3B backbone, 36 layers, action expert FFN {args.action_ffn}, ViT 32 blocks)"
+                         + (f" DEBUG layers={args.layers}" if args.layers else ""),
+                "global_batch": global_batch, "per_gpu_batch": args.per_gpu_batch, "micro_batch": micro,
+                "grad_accum": accum, "seq_len": int(pool[0][0]["input_ids"].shape[1]),
+                "vit_patches_per_sample": 3 * 18 * 18, "params": n_params,
+                "parallelism": f"dp{world} (resident bf16 params; sharded fp32 master + Adam moments; transport={transport if world > 1 else 'local'})",
+                "optimizer": "fused AdamW, wd 0.1, clip 1.0, fp32 master",
+                "l2_policy": "inputs and weights (>8 GB) are far larger than L2; no explicit flush",
+                "loss": loss_val,
+            },
+            "clocks": clocks, "gpu_launches": int(launches),
+        }
+        if ms_e2e is not None:
+            rec["e2e"] = {"value": round(global_batch * args.steps / (ms_e2e_max / 1e3), 3), "unit": "samples/s",
+                          "h2d_bytes_per_step": int(bi), "d2h_bytes_per_step": int(bo),
+                          "ms_per_step": round(ms_e2e_max / args.steps, 3)}
+        print(json.dumps(rec), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

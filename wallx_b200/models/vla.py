@@ -174,26 +174,47 @@ class Qwen2_5_VLMoEForAction(nn.Module):
 
     @torch.no_grad()
     def init_weights(self, seed: Optional[int] = None):
-        """normal(0, initializer_range) weights, zero biases, unit RMSNorm weights, zero padding row."""
+        """normal(0, initializer_range) weights, zero biases, unit RMSNorm weights, zero padding row.
+
+        With ``seed`` the values come from a CPU generator (reproducible across devices); without it
+        they are drawn in place on whatever device the parameters live on (fast for large models)."""
         from .layers import FusedQKV, RMSNorm, SwiGLUFFN
 
         gen = torch.Generator().manual_seed(seed) if seed is not None else None
         std = self.config.initializer_range
+
+        def fill(t: torch.Tensor):
+            if gen is None:
+                t.normal_(0.0, std)
+            else:
+                t.copy_(torch.empty(t.shape, dtype=torch.float32).normal_(0.0, std, generator=gen))
+
         for mod in self.modules():
             if isinstance(mod, SwiGLUFFN):
-                mod.reset_parameters(std, gen)
+                if gen is None:
+                    fill(mod.gate_up_weight)
+                    fill(mod.down_weight)
+                    pad = mod.padded - mod.intermediate
+                    if pad:  # padding rows / columns must be zero
+                        g, u = mod.unpack_gate_up(mod.gate_up_weight.data)
+                        mod.gate_up_weight.copy_(mod.pack_gate_up(g, u))
+                        mod.down_weight[:, mod.intermediate:].zero_()
+                    if mod.gate_up_bias is not None:
+                        mod.gate_up_bias.zero_()
+                        mod.down_bias.zero_()
+                else:
+                    mod.reset_parameters(std, gen)
             elif isinstance(mod, (Linear, FusedQKV)):
-                mod.weight.copy_(torch.empty(mod.weight.shape).normal_(0.0, std, generator=gen))
+                fill(mod.weight)
                 if mod.bias is not None:
                     mod.bias.zero_()
             elif isinstance(mod, nn.Embedding):
-                mod.weight.copy_(torch.empty(mod.weight.shape).normal_(0.0, std, generator=gen))
+                fill(mod.weight)
                 if mod.padding_idx is not None:
                     mod.weight[mod.padding_idx].zero_()
             elif isinstance(mod, RMSNorm):
                 mod.weight.fill_(1.0)
-        w = self.visual.patch_embed.proj.weight
-        w.copy_(torch.empty(w.shape).normal_(0.0, std, generator=gen))
+        fill(self.visual.patch_embed.proj.weight)
 
     def define_action_token_id(self):
         tok = self.processor.tokenizer

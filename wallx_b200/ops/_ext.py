@@ -104,3 +104,46 @@ def get(required: bool = True):
 
 def available() -> bool:
     return get(required=False) is not None
+
+
+class LaunchCounter:
+    """Counts kernel launches issued through the extension (each binding knows how many kernels it
+    launches). Used by the benchmark to report how many of our kernels ran in the timed region."""
+
+    PER_CALL = {"rms_norm_bwd": 2, "column_sum": 2}
+
+    def __init__(self, mod):
+        self._mod = mod
+        self.total = 0
+        self.by_name = {}
+
+    def __getattr__(self, name):
+        fn = getattr(self._mod, name)
+        if not callable(fn):
+            return fn
+        base = self.PER_CALL.get(name, 1)
+
+        def wrapped(*a, **k):
+            n = base
+            if name == "attn_bwd":
+                n = 3 if a[11] == a[12] else 5
+            if name == "read_status":
+                n = 0
+            self.total += n
+            self.by_name[name] = self.by_name.get(name, 0) + n
+            return fn(*a, **k)
+
+        self.__dict__[name] = wrapped
+        return wrapped
+
+    @staticmethod
+    def install() -> "LaunchCounter":
+        global _mod
+        real = get()
+        c = LaunchCounter(real)
+        _mod = c
+        return c
+
+    def uninstall(self) -> None:
+        global _mod
+        _mod = self._mod

@@ -1,0 +1,106 @@
+"""Flat parameter / gradient storage and the sharded optimizer state that goes with it.
+
+B200-first memory plan: with 180 GB of HBM per GPU the bf16 parameters (a few GB) stay resident
+and whole on every rank; what is sharded across ranks is the expensive part -- fp32 master
+weights and both Adam moments (12 bytes per parameter). Each rank owns one contiguous shard of
+every flat buffer: gradients are reduce-scattered onto the owner, the owner runs the fused
+clip/scale + AdamW kernel on its shard and the new bf16 values are written back into every rank's
+resident copy.
+
+Compared with the reference (accelerate FSDP2, bf16 parameters *and* bf16 Adam states,
+qwen_vl_act_trainer.py:527,577-581,609-611) this keeps fp32 master weights and moments; set
+``master_dtype=torch.bfloat16`` to mimic the reference's numerics.
+"""
+from __future__ import annotations
+
+from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn as nn
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class ParamSegment:
+    """A contiguous run of parameters that share optimizer hyper-parameters."""
+
+    def __init__(self, start: int, end: int, lr_scale: float, weight_decay: float, name: str):
+        self.start, self.end, self.lr_scale, self.weight_decay, self.name = start, end, lr_scale, weight_decay, name
+
+
+class FlatBuffer:
+    """One flat bf16 (or fp32 on CPU) buffer holding a list of parameters, its gradient twin and
+    this rank's shard of the optimizer state."""
+
+    ALIGN = 1024  # elements; keeps every shard 2 KB aligned for vector and bulk accesses
+
+    def __init__(self, named_params: Sequence[Tuple[str, nn.Parameter]], world: int = 1, rank: int = 0,
+                 groups: Optional[Sequence[Tuple[str, float, float]]] = None, name: str = "",
+                 alloc=None, master_dtype=torch.float32):
+        """``groups``: per parameter ``(group_name, lr_scale, weight_decay)`` in the same order."""
+        assert len(named_params) > 0
+        self.name = name
+        self.world, self.rank = world, rank
+        p0 = named_params[0][1]
+        self.device, self.dtype = p0.device, p0.dtype
+        if groups is None:
+            groups = [("default", 1.0, 0.0)] * len(named_params)
+        # keep parameters with equal hyper-parameters adjacent
+        order = sorted(range(len(named_params)), key=lambda i: (groups[i][0], i))
+        self.names: List[str] = []
+        self.params: List[nn.Parameter] = []
+        self.offsets: List[int] = []
+        self.segments: List[ParamSegment] = []
+        off = 0
+        for i in order:
+            n, p = named_params[i]
+            g = groups[i]
+            if not self.segments or self.segments[-1].name != g[0]:
+                self.segments.append(ParamSegment(off, off, g[1], g[2], g[0]))
+            self.names.append(n)
+            self.params.append(p)
+            self.offsets.append(off)
+            off += p.numel()
+            self.segments[-1].end = off
+        self.numel = off
+        self.padded = _round_up(off, self.ALIGN * world)
+        self.shard_size = self.padded // world
+        alloc = alloc or (lambda n, dtype: torch.zeros(n, device=self.device, dtype=dtype))
+        self.param = alloc(self.padded, self.dtype)
+        self.grad = alloc(self.padded, self.dtype)
+        with torch.no_grad():
+            for p, o in zip(self.params, self.offsets):
+                self.param[o:o + p.numel()].copy_(p.data.reshape(-1))
+                p.data = self.param[o:o + p.numel()].view(p.shape)
+                p.grad = self.grad[o:o + p.numel()].view(p.shape)
+        s0 = rank * self.shard_size
+        self.shard_range = (s0, s0 + self.shard_size)
+        self.master = self.param[s0:s0 + self.shard_size].to(master_dtype).clone()
+        self.exp_avg = torch.zeros(self.shard_size, device=self.device, dtype=master_dtype)
+        self.exp_avg_sq = torch.zeros(self.shard_size, device=self.device, dtype=master_dtype)
+
+    def rebind_grads(self) -> None:
+        """Point every ``p.grad`` back at the flat gradient buffer (after ``zero_grad(set_to_none)``)."""
+        for p, o in zip(self.params, self.offsets):
+            p.grad = self.grad[o:o + p.numel()].view(p.shape)
+
+    def zero_grad(self) -> None:
+        self.grad.zero_()
+
+    def shard_segments(self) -> List[Tuple[int, int, ParamSegment]]:
+        """Intersections of the hyper-parameter segments with this rank's shard, in shard-local
+        coordinates (padding elements belong to the last segment; their gradient is zero)."""
+        s0, s1 = self.shard_range
+        out = []
+        for k, seg in enumerate(self.segments):
+            a = seg.start
+            b = seg.end if k + 1 < len(self.segments) else self.padded
+            lo, hi = max(a, s0), min(b, s1)
+            if hi > lo:
+                out.append((lo - s0, hi - s0, seg))
+        return out
+
+    def state_dict(self) -> Dict[str, torch.Tensor]:
+        return {"master": self.master, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq}
