@@ -1,0 +1,213 @@
+"""Trainer, engine, optimizer sharding, checkpoint resharding and failure handling on CPU (gloo)."""
+import copy
+import json
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from wallx_b200.config import tiny_config
+from wallx_b200.data.collator import add_pack_info
+from wallx_b200.data.synthetic import make_batch, make_processor
+from wallx_b200.models import Qwen2_5_VLMoEForAction
+from wallx_b200.parallel.engine import TrainEngine, default_units
+from wallx_b200.train.schedule import CosineWithMinLR
+
+
+def _model(seed=0):
+    cfg = tiny_config()
+    proc = make_processor(cfg, 16)
+    m = Qwen2_5_VLMoEForAction(cfg, processor=proc)
+    m.init_weights(seed=seed)
+    return cfg, proc, m
+
+
+def _batches(cfg, proc, n, B=2, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for _ in range(n):
+        b = add_pack_info(make_batch(cfg, proc, B, views=1, image_hw=(112, 112), prompt_len=16, horizon=16, generator=g), cfg)
+        b["flow_noise"] = torch.randn(b["action_chunk"].shape, generator=g)
+        b["flow_time"] = torch.rand(B, generator=g)
+        out.append(b)
+    return out
+
+
+def test_schedule_matches_closed_form():
+    s = CosineWithMinLR(1e-3, 10, 110, min_lr=1e-4)
+    assert s.get_lr() == 0.0
+    for _ in range(10):
+        s.step()
+    assert abs(s.get_lr() - 1e-3) < 1e-12
+    for _ in range(50):
+        s.step()
+    assert abs(s.get_lr() - (1e-4 + (1e-3 - 1e-4) * 0.5)) < 1e-9
+    for _ in range(50):
+        s.step()
+    assert abs(s.get_lr() - 1e-4) < 1e-9
+
+
+def test_units_cover_every_trainable_parameter_once():
+    _, _, m = _model()
+    units = default_units(m)
+    names = [n for _, ps in units for n, _ in ps]
+    assert len(names) == len(set(names))
+    assert sum(p.numel() for _, ps in units for _, p in ps) == sum(p.numel() for p in m.parameters() if p.requires_grad)
+    assert [u for u, _ in units][:2] == ["visual.blocks.0", "visual.blocks.1"] and units[-1][0] == "root"
+
+
+def test_engine_step_matches_torch_adamw_with_clipping():
+    cfg, proc, m = _model()
+    ref_m = copy.deepcopy(m)
+    eng = TrainEngine(m, lr=1e-3, weight_decay=0.1, max_grad_norm=0.5, grad_accum=2)
+    opt = torch.optim.AdamW([p for p in ref_m.parameters() if p.requires_grad], lr=1e-3, weight_decay=0.1)
+    for step in range(2):
+        bs = _batches(cfg, proc, 2, seed=step)
+        for b in bs:
+            eng.backward(m(mode="train", **b).loss)
+            (ref_m(mode="train", **b).loss / 2).backward()
+        torch.nn.utils.clip_grad_norm_([p for p in ref_m.parameters() if p.requires_grad], 0.5)
+        opt.step()
+        opt.zero_grad()
+        eng.optimizer_step(1e-3)
+    for (n, a), (_, b) in zip(m.named_parameters(), ref_m.named_parameters()):
+        assert torch.allclose(a, b, atol=2e-6), n
+    assert eng.grad_norm().item() > 0
+
+
+def test_nonfinite_gradient_skips_the_update_everywhere():
+    cfg, proc, m = _model()
+    eng = TrainEngine(m, lr=1e-3, grad_accum=1)
+    before = eng.buffers[0].param.clone()
+    eng.backward(m(mode="train", **_batches(cfg, proc, 1)[0]).loss)
+    eng.buffers[3].grad[5] = float("nan")
+    eng.optimizer_step(1e-3)
+    assert torch.equal(eng.buffers[0].param, before)  # no buffer moved, not just the poisoned one
+    assert eng.buffers[3].grad.abs().sum() == 0  # gradients were still cleared
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _dist_worker(rank, world, port, tmp, mode):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.distributed.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    cfg, proc, m = _model()
+    eng = TrainEngine(m, lr=1e-3, weight_decay=0.1, max_grad_norm=1.0, grad_accum=1, world=world, rank=rank, transport="dist")
+    all_b = _batches(cfg, proc, 2 * world, seed=3)
+    if mode == "peer_never_joins" and rank == 1:
+        torch.distributed.destroy_process_group()
+        return
+    for step in range(2):
+        b = all_b[step * world + rank]
+        eng.backward(m(mode="train", **b).loss)
+        if mode == "rank_raises" and step == 1 and rank == 1:
+            raise RuntimeError("injected failure on rank 1")
+        eng.optimizer_step(1e-3)
+    torch.save({n: p.detach().clone() for n, p in m.named_parameters()}, os.path.join(tmp, f"params_{rank}.pt"))
+    torch.save(eng.optimizer_state(), os.path.join(tmp, f"optim_rank{rank:05d}_of_{world:05d}.pt"))
+    torch.distributed.barrier()
+    torch.distributed.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_two_rank_gloo_training_equals_single_rank_large_batch(tmp_path):
+    world = 2
+    mp.spawn(_dist_worker, args=(world, _free_port(), str(tmp_path), "ok"), nprocs=world, join=True)
+    p0 = torch.load(tmp_path / "params_0.pt")
+    p1 = torch.load(tmp_path / "params_1.pt")
+    for k in p0:
+        assert torch.equal(p0[k], p1[k]), k  # replicas stay identical
+    # single process, both micro-batches per step (== data parallel average)
+    cfg, proc, m = _model()
+    eng = TrainEngine(m, lr=1e-3, weight_decay=0.1, max_grad_norm=1.0, grad_accum=2)
+    all_b = _batches(cfg, proc, 4, seed=3)
+    for step in range(2):
+        for r in range(2):
+            eng.backward(m(mode="train", **all_b[step * 2 + r]).loss)
+        eng.optimizer_step(1e-3)
+    for n, p in m.named_parameters():
+        assert torch.allclose(p, p0[n], atol=3e-5), n  # 3% of one lr-sized Adam step: rounding only
+    # reshard the 2-rank optimizer state onto 1 rank and compare with the single-rank state
+    from wallx_b200.parallel.reshard import load_optimizer_shards
+
+    cfg, proc, m2 = _model()
+    eng2 = TrainEngine(m2, lr=1e-3, grad_accum=1)
+    load_optimizer_shards(eng2, str(tmp_path), 2)
+    assert eng2.optimizer.step_count == 2
+    for a, b in zip(eng.buffers, eng2.buffers):
+        assert torch.allclose(a.exp_avg[: a.numel], b.exp_avg[: b.numel], atol=1e-6)
+        assert torch.allclose(a.master[: a.numel], b.master[: b.numel], atol=3e-5)
+
+
+@pytest.mark.timeout(300)
+def test_rank_failure_is_reported_not_hung(tmp_path):
+    """A rank that raises between steps takes the job down with an error instead of a hang."""
+    with pytest.raises(Exception):
+        mp.spawn(_dist_worker, args=(2, _free_port(), str(tmp_path), "rank_raises"), nprocs=2, join=True)
+
+
+def test_watchdog_raises_after_timeout():
+    import time
+
+    from wallx_b200.train.trainer import StepWatchdog
+
+    w = StepWatchdog(0.05)
+    w.check()
+    time.sleep(0.1)
+    with pytest.raises(TimeoutError):
+        w.check()
+    w.kick()
+    w.check()
+
+
+def test_trainer_fit_save_resume(tmp_path):
+    from wallx_b200.train.trainer import QwenVlAct_Trainer
+
+    config = {
+        "model": {"preset": "tiny"}, "save_path": str(tmp_path / "run"), "learning_rate": 1e-3, "min_lr": 1e-4,
+        "num_warmup_steps": 1, "num_training_steps": 10, "num_epoch": 1, "gradient_accumulation_steps": 2,
+        "batch_size_per_gpu": 2, "num_workers": 0, "epoch_save_interval": 1, "max_steps": 3,
+        "data": {"synthetic": True, "action_horizon": 16, "synthetic_config": {"num_samples": 20, "image_hw": [112, 112]},
+                 "resolution": {"face_view": 112, "left_wrist_view": 112, "right_wrist_view": 112}},
+    }
+    tr = QwenVlAct_Trainer(config, seed=1)
+    tr.fit()
+    assert tr.global_step == 3
+    ck = tmp_path / "run" / "0"
+    assert (ck / "config.json").exists() and (ck / "model.safetensors").exists() and (ck / "trainer_state.json").exists()
+    lines = [json.loads(l) for l in open(tmp_path / "run" / "metrics.jsonl")]
+    assert any("train_loss" in l and "flow_loss" in l and "total_norm" in l and "lr" in l for l in lines)
+    assert any("val_loss" in l for l in lines)
+    config2 = dict(config, resume={"ckpt": str(ck)}, num_epoch=2, max_steps=4)
+    tr2 = QwenVlAct_Trainer(config2, seed=1)
+    assert tr2.global_step == 3 and tr2.epoch == 1 and tr2.lr_scheduler.step_count == 3
+    for a, b in zip(tr.engine.buffers, tr2.engine.buffers):
+        assert torch.equal(a.exp_avg, b.exp_avg) and torch.allclose(a.master, b.master, atol=1e-6)
+    sd1, sd2 = tr.model.state_dict(), tr2.model.state_dict()
+    assert all(torch.equal(sd1[k], sd2[k]) for k in sd1)
+
+
+def test_timers_accumulate_and_log(capsys):
+    import time
+
+    from wallx_b200.utils.timers import Timers
+
+    t = Timers(log_level=0, log_option="minmax")
+    t("fwd", 0).start()
+    time.sleep(0.02)
+    t("fwd", 0).stop()
+    t("skipped", 2).start()  # above the log level: a no-op dummy
+    t.log(["fwd"])
+    out = capsys.readouterr().out
+    assert "fwd" in out and "(min, max)" in out
+    assert t("fwd", 0).elapsed() == 0.0

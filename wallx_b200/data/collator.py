@@ -63,3 +63,98 @@ def to_device(batch: Dict[str, object], device, dtype=None, non_blocking: bool =
 
 def pin_batch(batch: Dict[str, object]) -> Dict[str, object]:
     return {k: (v.pin_memory() if isinstance(v, torch.Tensor) and not v.is_pinned() else v) for k, v in batch.items()}
+
+
+# ------------------------------------------------------------------------------------ DataCollator
+ACTION_PAD_DIM = 20  # actions and proprio are zero-padded to 20 dims (load_lerobot_dataset.py:317,349)
+
+
+def minmax_normalize(x: torch.Tensor, min_stat, max_stat) -> torch.Tensor:
+    """``(x - min) / delta * 2 - 1`` clamped to [-1, 1]; a zero range counts as 1."""
+    mn = torch.as_tensor(min_stat, dtype=x.dtype)
+    delta = torch.as_tensor(max_stat, dtype=x.dtype) - mn
+    delta = torch.where(delta == 0, torch.ones_like(delta), delta)
+    return torch.clamp((x - mn) / delta * 2 - 1, -1, 1)
+
+
+def _pad_last(x: torch.Tensor, width: int) -> torch.Tensor:
+    if x.shape[-1] >= width:
+        return x
+    return torch.cat([x, x.new_zeros(x.shape[:-1] + (width - x.shape[-1],))], dim=-1)
+
+
+class DataCollator:
+    """List of samples ``{image_inputs, text, action, agent_pos, frame_index}`` -> model batch.
+
+    Follows the reference collator (load_lerobot_dataset.py:239-415): NaN entries become mask 0,
+    min-max normalisation with the dataset statistics, zero-padding to 20 dims, FAST token
+    substitution (or removal of the FAST slot in flow mode), placeholder expansion + tokenisation +
+    assistant labels, ``moe_token_types = (input_ids == <|action|>)``, ``dataset_names``.
+    On top of that the batch gets its host-side packing info (:func:`add_pack_info`).
+    """
+
+    def __init__(self, config: Dict, dataload_config: Dict, stats: Dict, processor=None, action_tokenizer=None,
+                 model_config=None):
+        from . import text as T
+
+        self.T = T
+        self.config = config
+        self.dataload_config = dataload_config
+        self.min_stat = stats["action"]["min"]
+        self.max_stat = stats["action"]["max"]
+        self.use_fast_tokenizer = bool(config.get("use_fast_tokenizer", False))
+        if processor is None:
+            from transformers import AutoProcessor
+
+            processor = AutoProcessor.from_pretrained(config["pretrained_wallx_path"], use_fast=True)
+        if config.get("padding_side", "left") == "left":
+            processor.tokenizer.padding_side = "left"
+        self.processor = processor
+        if self.use_fast_tokenizer and action_tokenizer is None:
+            from transformers import AutoProcessor
+
+            action_tokenizer = AutoProcessor.from_pretrained(config["action_tokenizer_path"], trust_remote_code=True)
+        self.train_action_tokenizer = action_tokenizer if self.use_fast_tokenizer else None
+        self.action_mapper = None
+        if self.train_action_tokenizer is not None:
+            tok = processor.tokenizer
+            self.action_mapper = {tok.convert_tokens_to_ids(f"<|action_token_{i}|>"): i
+                                  for i in range(self.train_action_tokenizer.vocab_size)}
+        self.model_config = model_config
+        self.max_length = dataload_config.get("max_length", 768)
+
+    def _vector(self, items, key):
+        x = torch.stack([torch.as_tensor(it[key], dtype=torch.float32) for it in items])
+        if x.dim() == 2:
+            x = x.unsqueeze(1)
+        mask = (~torch.isnan(x)).float()
+        x = minmax_normalize(torch.nan_to_num(x, nan=0.0), self.min_stat, self.max_stat)
+        return _pad_last(x, ACTION_PAD_DIM), _pad_last(mask, ACTION_PAD_DIM)
+
+    def __call__(self, items):
+        known = {"agent_pos", "action", "image_inputs", "text", "frame_index"}
+        for k in items[0].keys():
+            if k not in known:
+                raise NotImplementedError(f"{k} input not implemented in preprocesser")
+        out: Dict[str, object] = {}
+        if "agent_pos" in items[0]:
+            out["proprioception"], out["agent_pos_mask"] = self._vector(items, "agent_pos")
+        if "action" in items[0]:
+            out["action_chunk"], out["dof_mask"] = self._vector(items, "action")
+        if "frame_index" in items[0]:
+            out["frame_index"] = torch.stack([torch.as_tensor(it["frame_index"]) for it in items])
+        names = ["x2_normal"] * len(items)
+        text = self.T.replace_action_token([it["text"] for it in items], out.get("action_chunk"),
+                                           self.train_action_tokenizer, names, out.get("dof_mask"))
+        images = [im for it in items for im in it["image_inputs"]]
+        enc = self.T.preprocesser_call(self.processor, images=images, text=text, videos=None, padding=True,
+                                       truncation=True, max_length=self.max_length, return_tensors="pt")
+        out.update(enc)
+        action_id = self.processor.tokenizer.convert_tokens_to_ids("<|action|>")
+        out["moe_token_types"] = out["input_ids"] == action_id
+        out["dataset_names"] = names
+        if out.get("labels") is None:
+            out.pop("labels", None)
+        if self.model_config is not None:
+            add_pack_info(out, self.model_config)
+        return out

@@ -98,6 +98,66 @@ class SyntheticTokenizer:
             return self.action_start + int(token[len("<|action_token_"):-2])
         raise KeyError(token)
 
+    # ---- string tokenisation (special tokens are atoms; other text is hashed word by word)
+    _SPLIT = None
+
+    def _encode(self, text: str):
+        import re
+        import zlib
+
+        if SyntheticTokenizer._SPLIT is None:
+            SyntheticTokenizer._SPLIT = re.compile(r"(<\|[^|<>]*\|>)")
+        ids = []
+        for piece in SyntheticTokenizer._SPLIT.split(text):
+            if not piece:
+                continue
+            if piece.startswith("<|") and piece.endswith("|>"):
+                if piece in self.special:
+                    ids.append(self.special[piece])
+                    continue
+                if piece.startswith("<|action_token_"):
+                    ids.append(self.action_start + int(piece[len("<|action_token_"):-2]))
+                    continue
+                if piece == "<|endoftext|>":
+                    ids.append(self.pad_token_id)
+                    continue
+            for word in re.findall(r"\n|[A-Za-z0-9_]+|[^\sA-Za-z0-9_]", piece):
+                if word == "assistant":
+                    ids.append(self.special["assistant"])
+                elif word == "\n":
+                    ids.append(5)
+                else:
+                    ids.append(6 + zlib.crc32(word.encode()) % max(1, self.text_hi - 6))
+        return ids
+
+    @property
+    def text_hi(self):
+        lows = [v for v in self.special.values() if v > 6]
+        return min(min(lows), self.base_vocab) if lows else self.base_vocab
+
+    def encode(self, text, add_special_tokens=False):
+        return self._encode(text)
+
+    def __call__(self, text, return_tensors=None, padding=False, truncation=None, max_length=None,
+                 add_special_tokens=False):
+        single = isinstance(text, str)
+        rows = [self._encode(t) for t in ([text] if single else text)]
+        if truncation and max_length:
+            rows = [r[:max_length] for r in rows]
+        if single and return_tensors is None:
+            return type("Enc", (), {"input_ids": rows[0]})()
+        width = max(len(r) for r in rows)
+        ids = torch.full((len(rows), width), self.pad_token_id, dtype=torch.long)
+        am = torch.zeros((len(rows), width), dtype=torch.long)
+        for i, r in enumerate(rows):
+            if self.padding_side == "left":
+                ids[i, width - len(r):] = torch.tensor(r, dtype=torch.long)
+                am[i, width - len(r):] = 1
+            else:
+                ids[i, : len(r)] = torch.tensor(r, dtype=torch.long)
+                am[i, : len(r)] = 1
+        return {"input_ids": ids, "attention_mask": am}
+
     def decode(self, ids, **kw):
         inv = {v: k for k, v in self.special.items()}
         out = []
@@ -114,9 +174,33 @@ class SyntheticTokenizer:
         return [self.decode(row) for row in batch]
 
 
+class SyntheticImageProcessor:
+    """uint8 HWC arrays / PIL images -> Qwen2-VL style patches (see :func:`images_to_patches`)."""
+
+    def __init__(self, patch_size=14, temporal_patch_size=2, merge_size=2):
+        self.patch_size, self.temporal_patch_size, self.merge_size = patch_size, temporal_patch_size, merge_size
+
+    def __call__(self, images=None, videos=None, return_tensors="pt"):
+        import numpy as np
+
+        pvs, grids = [], []
+        for im in images or []:
+            arr = torch.as_tensor(np.array(im))
+            if arr.dim() == 3 and arr.shape[0] == 3 and arr.shape[-1] != 3:
+                arr = arr.permute(1, 2, 0)
+            if arr.dtype != torch.uint8:
+                arr = (arr.float().clamp(0, 1) * 255).to(torch.uint8) if arr.is_floating_point() else arr.to(torch.uint8)
+            pv, g = images_to_patches(arr.unsqueeze(0), self.patch_size, self.temporal_patch_size, self.merge_size)
+            pvs.append(pv)
+            grids.extend(g)
+        return {"pixel_values": torch.cat(pvs) if pvs else None,
+                "image_grid_thw": torch.tensor(grids, dtype=torch.long) if grids else None}
+
+
 class SyntheticProcessor:
-    def __init__(self, tokenizer: SyntheticTokenizer):
+    def __init__(self, tokenizer: SyntheticTokenizer, image_processor=None):
         self.tokenizer = tokenizer
+        self.image_processor = image_processor or SyntheticImageProcessor()
         self.action_processor = None
 
     def batch_decode(self, batch, **kw):

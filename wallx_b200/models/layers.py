@@ -59,7 +59,6 @@ class FusedQKV(nn.Module):
         self.weight = nn.Parameter(torch.empty(q_out + 2 * kv_out, hidden))
         self.bias = nn.Parameter(torch.zeros(q_out + 2 * kv_out)) if bias else None
         self._register_state_dict_hook(FusedQKV._split_hook)
-        self._register_load_state_dict_pre_hook(self._merge_hook)
 
     def forward(self, x):
         return F_.linear(x, self.weight, self.bias)
@@ -79,14 +78,18 @@ class FusedQKV(nn.Module):
             for name, part in zip(("q_proj", "k_proj", "v_proj"), parts):
                 state_dict[f"{parent}{name}.{kind}"] = part.clone()
 
-    def _merge_hook(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs):
-        if not prefix.endswith("qkv_proj."):
-            return
-        parent = prefix[: -len("qkv_proj.")]
-        for kind in ("weight", "bias"):
-            keys = [f"{parent}{n}.{kind}" for n in ("q_proj", "k_proj", "v_proj")]
-            if all(k in state_dict for k in keys):
-                state_dict[prefix + kind] = torch.cat([state_dict.pop(k) for k in keys], dim=0)
+    @staticmethod
+    def merge_hook_for_parent(name: str = "qkv_proj"):
+        """Load-time hook to register on the *parent* module: torch hands a child only the keys
+        under the child's own prefix, and q_proj/k_proj/v_proj live beside it, not under it."""
+
+        def hook(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs):
+            for kind in ("weight", "bias"):
+                keys = [f"{prefix}{n}.{kind}" for n in ("q_proj", "k_proj", "v_proj")]
+                if all(k in state_dict for k in keys):
+                    state_dict[f"{prefix}{name}.{kind}"] = torch.cat([state_dict.pop(k) for k in keys], dim=0)
+
+        return hook
 
 
 class SwiGLUFFN(nn.Module):

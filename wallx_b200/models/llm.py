@@ -73,6 +73,7 @@ class Attention(nn.Module):
         self.head_dim = config.head_dim
         self.qkv_proj = FusedQKV(self.hidden_size, self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim, bias=True)
         self.o_proj = Linear(self.num_heads * self.head_dim, self.hidden_size, bias=False)
+        self._register_load_state_dict_pre_hook(FusedQKV.merge_hook_for_parent("qkv_proj"))
 
     def forward(self, x: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> torch.Tensor:
         hq, hkv, d = self.num_heads, self.num_kv_heads, self.head_dim

@@ -382,19 +382,30 @@ class AttnMeta:
 
     def __init__(self, cu_q: Sequence[int], device, causal: bool, bidir_q: Optional[torch.Tensor] = None,
                  cu_k: Optional[Sequence[int]] = None, bidir_k: Optional[torch.Tensor] = None,
-                 cache_rows: Optional[torch.Tensor] = None):
+                 cache_rows: Optional[torch.Tensor] = None, k_starts: Optional[Sequence[int]] = None,
+                 k_lens: Optional[Sequence[int]] = None, k_rows: Optional[int] = None):
+        """Key ranges are either ``cu_k`` (adjacent segments), or ``k_starts``/``k_lens`` (one
+        range per sequence inside a larger buffer of ``k_rows`` rows, e.g. KV-cache slots), or
+        absent (self-attention: keys are the queries' own rows)."""
         self.cu_q_host = [int(c) for c in cu_q]
-        self.cu_k_host = [int(c) for c in cu_k] if cu_k is not None else self.cu_q_host
-        self.self_attn = cu_k is None
+        nseq = len(self.cu_q_host) - 1
+        self.self_attn = cu_k is None and k_starts is None
+        if k_starts is not None:
+            self.k_ranges = [(int(s0), int(s0) + int(l)) for s0, l in zip(k_starts, k_lens)]
+            self.k_rows = int(k_rows) if k_rows is not None else max(e for _, e in self.k_ranges)
+        else:
+            ck = [int(c) for c in cu_k] if cu_k is not None else self.cu_q_host
+            self.k_ranges = [(ck[i], ck[i + 1]) for i in range(nseq)]
+            self.k_rows = ck[-1]
+        self.cu_k_host = [r[0] for r in self.k_ranges] + [self.k_ranges[-1][1] if self.k_ranges else 0]
         self.cu_q = torch.tensor(self.cu_q_host, dtype=torch.int32, device=device)
-        self.cu_k = self.cu_q if cu_k is None else torch.tensor(self.cu_k_host, dtype=torch.int32, device=device)
-        lq = [self.cu_q_host[i + 1] - self.cu_q_host[i] for i in range(len(self.cu_q_host) - 1)]
-        lk = [self.cu_k_host[i + 1] - self.cu_k_host[i] for i in range(len(self.cu_k_host) - 1)]
+        lq = [self.cu_q_host[i + 1] - self.cu_q_host[i] for i in range(nseq)]
+        lk = [e - s0 for s0, e in self.k_ranges]
         self.max_q = max(lq) if lq else 0
         self.max_k = max(lk) if lk else 0
         self.causal = bool(causal)
         self.bidir_q = bidir_q
-        self.bidir_k = bidir_k if bidir_k is not None else (bidir_q if cu_k is None else None)
+        self.bidir_k = bidir_k if bidir_k is not None else (bidir_q if self.self_attn else None)
         self.cache_rows = cache_rows
         self._dev = {}
 
@@ -407,15 +418,15 @@ class AttnMeta:
         """Per-token tables for the kernels: for every query row its key range and causal limit."""
         t = self._dev.get("tables")
         if t is None:
-            nq, nk = self.cu_q_host[-1], self.cu_k_host[-1]
-            k_lo = torch.empty(nq, dtype=torch.int32)
-            k_hi = torch.empty(nq, dtype=torch.int32)
-            k_lim = torch.empty(nq, dtype=torch.int32)  # last visible key (absolute row) under causality
-            q_lo = torch.empty(nk, dtype=torch.int32)
-            q_hi = torch.empty(nk, dtype=torch.int32)
+            nq, nk = self.cu_q_host[-1], self.k_rows
+            k_lo = torch.zeros(nq, dtype=torch.int32)
+            k_hi = torch.zeros(nq, dtype=torch.int32)
+            k_lim = torch.full((nq,), -1, dtype=torch.int32)  # last visible key (absolute row) under causality
+            q_lo = torch.zeros(nk, dtype=torch.int32)
+            q_hi = torch.zeros(nk, dtype=torch.int32)
             for b in range(len(self.cu_q_host) - 1):
                 q0, q1 = self.cu_q_host[b], self.cu_q_host[b + 1]
-                k0, k1 = self.cu_k_host[b], self.cu_k_host[b + 1]
+                k0, k1 = self.k_ranges[b]
                 k_lo[q0:q1] = k0
                 k_hi[q0:q1] = k1
                 off = (k1 - k0) - (q1 - q0)
@@ -424,10 +435,15 @@ class AttnMeta:
                 q_hi[k0:k1] = q1
             if not self.causal:
                 k_lim = k_hi - 1
-            fq = self.bidir_q.to(torch.int32).cpu() if self.bidir_q is not None else torch.zeros(nq, dtype=torch.int32)
-            fk = self.bidir_k.to(torch.int32).cpu() if self.bidir_k is not None else torch.zeros(nk, dtype=torch.int32)
-            qtab = torch.stack([k_lo, k_hi, k_lim, fq], dim=1).contiguous().to(device)
-            ktab = torch.stack([q_lo, q_hi, fk, torch.zeros_like(fk)], dim=1).contiguous().to(device)
+            # flags stay on their device (no host round trip); host-built columns are uploaded once
+            qh = torch.stack([k_lo, k_hi, k_lim], dim=1).to(device, non_blocking=True)
+            kh = torch.stack([q_lo, q_hi], dim=1).to(device, non_blocking=True)
+            fq = (self.bidir_q.to(device=device, dtype=torch.int32) if self.bidir_q is not None
+                  else torch.zeros(nq, dtype=torch.int32, device=device))
+            fk = (self.bidir_k.to(device=device, dtype=torch.int32) if self.bidir_k is not None
+                  else torch.zeros(nk, dtype=torch.int32, device=device))
+            qtab = torch.cat([qh, fq.reshape(-1, 1)], dim=1).contiguous()
+            ktab = torch.cat([kh, fk.reshape(-1, 1), torch.zeros_like(fk).reshape(-1, 1)], dim=1).contiguous()
             t = (qtab, ktab)
             self._dev["tables"] = t
         return t
@@ -439,7 +455,7 @@ def _attention_torch(q, k, v, meta: AttnMeta, hq, hkv, d, scale):
     rep = hq // hkv
     for b in range(len(meta.cu_q_host) - 1):
         q0, q1 = meta.cu_q_host[b], meta.cu_q_host[b + 1]
-        k0, k1 = meta.cu_k_host[b], meta.cu_k_host[b + 1]
+        k0, k1 = meta.k_ranges[b]
         lq, lk = q1 - q0, k1 - k0
         qb = q[q0:q1].reshape(lq, hq, d).float()
         kb = k[k0:k1].reshape(lk, hkv, d).float()

@@ -73,6 +73,9 @@ class TrainEngine:
         self.optimizer = FlatAdamW(self.buffers, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
                                    max_grad_norm=max_grad_norm, grad_accum=grad_accum * world)
         self.last_norm_sq: Optional[torch.Tensor] = None
+        # ranks agree on which parameters were used unless batches differ in modality; the merge
+        # costs one host read per step, so it can be switched off for homogeneous data
+        self.check_touched = True
         if self.transport == "symm":
             symm.register_buffers(self.buffers)
 
@@ -113,6 +116,27 @@ class TrainEngine:
                 dist.all_gather(parts, b.param[s0:s1].clone(), group=self.group)
                 b.param.copy_(torch.cat(parts))
 
+    def _merge_touched(self) -> None:
+        """A parameter counts as used if any rank produced a gradient for it (ranks can differ when a
+        batch lacks a modality); one small all-reduce, only when some parameter was left untouched."""
+        flags = [t for b in self.buffers for t in b.touched]
+        if self.world == 1:
+            return
+        import torch.distributed as dist
+
+        dev = self.buffers[0].device
+        t = torch.tensor(flags, dtype=torch.float32).to(dev)
+        if self.transport == "symm":
+            t = self.symm.all_reduce_vector(t)
+        else:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+        merged = (t > 0).cpu().tolist()
+        k = 0
+        for b in self.buffers:
+            n = len(b.touched)
+            b.touched = merged[k:k + n]
+            k += n
+
     def _global_norm_sq(self, shards: Optional[List[torch.Tensor]]) -> torch.Tensor:
         opt = self.optimizer
         if shards is None:
@@ -139,6 +163,8 @@ class TrainEngine:
     def optimizer_step(self, lr: float) -> torch.Tensor:
         """Reduce gradients, clip by global norm, update shards, refresh parameters, clear grads.
         Returns the squared global gradient norm *before* scaling by 1/(accum*world) (device)."""
+        if self.check_touched:
+            self._merge_touched()
         shards = self._reduce_scatter()
         norm_sq = self._global_norm_sq(shards)
         self.optimizer.step(lr=lr, norm_sq=norm_sq, grad_shards=shards)

@@ -75,11 +75,50 @@ class FlatBuffer:
                 self.param[o:o + p.numel()].copy_(p.data.reshape(-1))
                 p.data = self.param[o:o + p.numel()].view(p.shape)
                 p.grad = self.grad[o:o + p.numel()].view(p.shape)
+        # which parameters received a gradient since the last step (torch's AdamW leaves parameters
+        # whose grad is None untouched -- no decay, no moment update -- e.g. the LM head in flow-only
+        # training); filled by post-accumulate hooks, merged across ranks by the engine
+        self.touched = [False] * len(self.params)
+        for i, p in enumerate(self.params):
+            p.register_post_accumulate_grad_hook(self._make_hook(i))
+        self.seg_of_param = []
+        for o in self.offsets:
+            self.seg_of_param.append(next(k for k, sg in enumerate(self.segments) if sg.start <= o < sg.end))
         s0 = rank * self.shard_size
         self.shard_range = (s0, s0 + self.shard_size)
         self.master = self.param[s0:s0 + self.shard_size].to(master_dtype).clone()
         self.exp_avg = torch.zeros(self.shard_size, device=self.device, dtype=master_dtype)
         self.exp_avg_sq = torch.zeros(self.shard_size, device=self.device, dtype=master_dtype)
+
+    def _make_hook(self, i: int):
+        def hook(_p):
+            self.touched[i] = True
+
+        return hook
+
+    def clear_touched(self) -> None:
+        self.touched = [False] * len(self.params)
+
+    def update_ranges(self, touched=None) -> List[Tuple[int, int, ParamSegment]]:
+        """Shard-local ``(lo, hi, segment)`` ranges to update: touched parameters only, adjacent
+        ones with equal hyper-parameters merged."""
+        touched = self.touched if touched is None else touched
+        if all(touched):
+            return self.shard_segments()
+        s0, s1 = self.shard_range
+        out: List[Tuple[int, int, ParamSegment]] = []
+        for i, (p, o) in enumerate(zip(self.params, self.offsets)):
+            if not touched[i]:
+                continue
+            lo, hi = max(o, s0), min(o + p.numel(), s1)
+            if hi <= lo:
+                continue
+            seg = self.segments[self.seg_of_param[i]]
+            if out and out[-1][1] == lo - s0 and out[-1][2] is seg:
+                out[-1] = (out[-1][0], hi - s0, seg)
+            else:
+                out.append((lo - s0, hi - s0, seg))
+        return out
 
     def rebind_grads(self) -> None:
         """Point every ``p.grad`` back at the flat gradient buffer (after ``zero_grad(set_to_none)``)."""

@@ -67,7 +67,7 @@ class FlatAdamW:
             s0, s1 = b.shard_range
             g_all = grad_shards[i] if grad_shards is not None else b.grad[s0:s1]
             p16 = b.param[s0:s1]
-            for lo, hi, seg in b.shard_segments():
+            for lo, hi, seg in b.update_ranges():
                 wd = seg.weight_decay
                 seg_lr = lr * seg.lr_scale
                 if b.param.is_cuda:
@@ -95,6 +95,7 @@ class FlatAdamW:
     def zero_grad(self) -> None:
         for b in self.buffers:
             b.zero_grad()
+            b.clear_touched()
 
     def state_dict(self):
         return {"step": self.step_count, "buffers": [b.state_dict() for b in self.buffers]}
