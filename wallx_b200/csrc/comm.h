@@ -1,0 +1,44 @@
+// Peer-memory collectives for the sharded optimizer (raw pointers + stream). All kernels read or
+// write other GPUs' memory through plain peer pointers over NVLink / NVSwitch; no NCCL call.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace wx {
+
+constexpr int kMaxPeers = 8;
+
+struct PeerPtrs {
+  void* p[kMaxPeers];
+};
+
+// Table entry: one flat buffer's shard. `arena_off` is the element offset of this rank's shard in
+// every rank's bf16 arena, `n` its length, `out_off` the offset in the local fp32 shard buffer.
+struct ShardDesc {
+  long arena_off;
+  long n;
+  long out_off;
+};
+
+// Every rank signals every peer and waits (bounded) until all peers signalled `epoch`.
+// flags.p[r] points at rank r's int[kMaxPeers] flag array. Sets *status non-zero on time-out.
+int symm_barrier(const PeerPtrs& flags, int rank, int world, int epoch, int* status, cudaStream_t s);
+
+// out[out_off + i] = sum_r bf16(grads.p[r][arena_off + i]) in fp32, for every table entry; adds the
+// sum of squares of the results into *sumsq.
+int rs_reduce(const PeerPtrs& grads, const ShardDesc* table_dev, int nbuf, int world, float* out, float* sumsq,
+              cudaStream_t s);
+
+// Copies this rank's bf16 shards (table entries) from its own arena into every peer's arena.
+int ag_push(const PeerPtrs& params, const ShardDesc* table_dev, int nbuf, int rank, int world, cudaStream_t s);
+
+// All-reduce (sum) of a small fp32 vector: each rank writes its values into slot `rank` of every
+// peer's scratch [world][n]; after the barrier every rank sums the `world` slots into out.
+int small_allreduce_write(const PeerPtrs& scratch, const float* vals, int n, int rank, int world, cudaStream_t s);
+int small_allreduce_sum(const float* my_scratch, float* out, int n, int world, cudaStream_t s);
+
+// AdamW on fp32 gradients (see adamw_step in kernels.h for the hyper-parameter layout).
+int adamw_step_f32g(void* p16, float* p32, float* m, float* v, const float* g, long n, const float* hyper,
+                    const float* norm_sq, cudaStream_t s);
+
+}  // namespace wx

@@ -3,6 +3,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include "comm.h"
 #include "kernels.h"
 
 namespace {
@@ -159,6 +160,58 @@ void adamw_step(at::Tensor& p16, at::Tensor& p32, at::Tensor& m, at::Tensor& v, 
               "adamw_step");
 }
 
+wx::PeerPtrs peer_ptrs(const std::vector<int64_t>& ptrs) {
+  TORCH_CHECK(ptrs.size() >= 1 && ptrs.size() <= wx::kMaxPeers, "1..8 peers");
+  wx::PeerPtrs pp{};
+  for (size_t i = 0; i < ptrs.size(); ++i) pp.p[i] = reinterpret_cast<void*>(ptrs[i]);
+  return pp;
+}
+
+void symm_barrier(const std::vector<int64_t>& flag_ptrs, int64_t rank, int64_t epoch, at::Tensor& status) {
+  WX_CHECK_RC(wx::symm_barrier(peer_ptrs(flag_ptrs), rank, flag_ptrs.size(), epoch, status.data_ptr<int>(), cur_stream()),
+              "symm_barrier");
+}
+
+void rs_reduce(const std::vector<int64_t>& grad_ptrs, const at::Tensor& table, at::Tensor& out, at::Tensor& sumsq) {
+  TORCH_CHECK(table.is_cuda() && table.scalar_type() == at::kLong && table.dim() == 2 && table.size(1) == 3 && table.is_contiguous());
+  TORCH_CHECK(out.scalar_type() == at::kFloat && sumsq.scalar_type() == at::kFloat);
+  WX_CHECK_RC(wx::rs_reduce(peer_ptrs(grad_ptrs), reinterpret_cast<const wx::ShardDesc*>(table.data_ptr<int64_t>()),
+                            table.size(0), grad_ptrs.size(), out.data_ptr<float>(), sumsq.data_ptr<float>(), cur_stream()),
+              "rs_reduce");
+}
+
+void ag_push(const std::vector<int64_t>& param_ptrs, const at::Tensor& table, int64_t rank) {
+  TORCH_CHECK(table.is_cuda() && table.scalar_type() == at::kLong && table.size(1) == 3 && table.is_contiguous());
+  WX_CHECK_RC(wx::ag_push(peer_ptrs(param_ptrs), reinterpret_cast<const wx::ShardDesc*>(table.data_ptr<int64_t>()),
+                          table.size(0), rank, param_ptrs.size(), cur_stream()),
+              "ag_push");
+}
+
+void small_allreduce_write(const std::vector<int64_t>& scratch_ptrs, const at::Tensor& vals, int64_t rank) {
+  TORCH_CHECK(vals.is_cuda() && vals.scalar_type() == at::kFloat && vals.is_contiguous());
+  WX_CHECK_RC(wx::small_allreduce_write(peer_ptrs(scratch_ptrs), vals.data_ptr<float>(), vals.numel(), rank,
+                                        scratch_ptrs.size(), cur_stream()),
+              "small_allreduce_write");
+}
+
+void small_allreduce_sum(const at::Tensor& my_scratch, at::Tensor& out, int64_t world) {
+  WX_CHECK_RC(wx::small_allreduce_sum(my_scratch.data_ptr<float>(), out.data_ptr<float>(), out.numel(), world, cur_stream()),
+              "small_allreduce_sum");
+}
+
+void adamw_step_f32g(at::Tensor& p16, at::Tensor& p32, at::Tensor& m, at::Tensor& v, const at::Tensor& g,
+                     const at::Tensor& hyper, const OptT& norm_sq) {
+  TORCH_CHECK(p16.scalar_type() == at::kBFloat16 && g.scalar_type() == at::kFloat && p32.scalar_type() == at::kFloat);
+  TORCH_CHECK(p16.is_contiguous() && p32.is_contiguous() && m.is_contiguous() && v.is_contiguous() && g.is_contiguous());
+  const int64_t n = p16.numel();
+  TORCH_CHECK(p32.numel() == n && m.numel() == n && v.numel() == n && g.numel() == n, "adamw: size mismatch");
+  c10::cuda::CUDAGuard guard(p16.device());
+  const float* ns = (norm_sq.has_value() && norm_sq->defined()) ? norm_sq->data_ptr<float>() : nullptr;
+  WX_CHECK_RC(wx::adamw_step_f32g(p16.data_ptr(), p32.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
+                                  g.data_ptr<float>(), n, hyper.data_ptr<float>(), ns, cur_stream()),
+              "adamw_step_f32g");
+}
+
 }  // namespace
 
 void register_kernel_bindings(pybind11::module_& m) {
@@ -174,4 +227,10 @@ void register_kernel_bindings(pybind11::module_& m) {
   m.def("ce_bwd", &ce_bwd);
   m.def("sumsq_bf16", &sumsq_bf16);
   m.def("adamw_step", &adamw_step);
+  m.def("adamw_step_f32g", &adamw_step_f32g);
+  m.def("symm_barrier", &symm_barrier);
+  m.def("rs_reduce", &rs_reduce);
+  m.def("ag_push", &ag_push);
+  m.def("small_allreduce_write", &small_allreduce_write);
+  m.def("small_allreduce_sum", &small_allreduce_sum);
 }

@@ -23,6 +23,7 @@ SOURCES = [
     "gemm.cu",
     "kernels.cu",
     "attention.cu",
+    "comm.cu",
 ]
 
 NVCC_FLAGS = [

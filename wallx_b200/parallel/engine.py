@@ -66,8 +66,14 @@ class TrainEngine:
         self.grad_accum = grad_accum
         pg = param_group_fn or (lambda name: ("default", 1.0, weight_decay))
         self.buffers: List[FlatBuffer] = []
-        alloc = symm.alloc if (self.transport == "symm" and symm is not None) else None
-        for uname, ps in default_units(model):
+        units = default_units(model)
+        alloc = None
+        if self.transport == "symm" and symm is not None:
+            align = FlatBuffer.ALIGN * world
+            total = sum((sum(p.numel() for _, p in ps) + align - 1) // align * align for _, ps in units)
+            symm.reserve(total, dtype=units[0][1][0][1].dtype)
+            alloc = (symm.alloc_param, symm.alloc_grad)
+        for uname, ps in units:
             groups = [pg(n) for n, _ in ps]
             self.buffers.append(FlatBuffer(ps, world, rank, groups, name=uname, alloc=alloc, master_dtype=master_dtype))
         self.optimizer = FlatAdamW(self.buffers, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
@@ -141,6 +147,9 @@ class TrainEngine:
         opt = self.optimizer
         if shards is None:
             return opt.local_grad_sumsq(shard_only=False)
+        if self.transport == "symm":  # the reduce-scatter kernel already summed the squares of its shard
+            opt.norm_sq.copy_(self.symm.local_sumsq)
+            return self.symm.all_reduce_scalar(opt.norm_sq)
         opt.norm_sq.zero_()
         for g in shards:
             if g.is_cuda and g.dtype == torch.bfloat16:
@@ -149,8 +158,6 @@ class TrainEngine:
                 _ext.get().sumsq_bf16(g, opt.norm_sq)
             else:
                 opt.norm_sq += (g.float() ** 2).sum()
-        if self.transport == "symm":
-            return self.symm.all_reduce_scalar(opt.norm_sq)
         import torch.distributed as dist
 
         dist.all_reduce(opt.norm_sq, op=dist.ReduceOp.SUM, group=self.group)

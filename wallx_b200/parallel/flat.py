@@ -67,9 +67,10 @@ class FlatBuffer:
         self.numel = off
         self.padded = _round_up(off, self.ALIGN * world)
         self.shard_size = self.padded // world
-        alloc = alloc or (lambda n, dtype: torch.zeros(n, device=self.device, dtype=dtype))
-        self.param = alloc(self.padded, self.dtype)
-        self.grad = alloc(self.padded, self.dtype)
+        default = lambda n, dtype: torch.zeros(n, device=self.device, dtype=dtype)
+        alloc_param, alloc_grad = alloc if alloc is not None else (default, default)
+        self.param = alloc_param(self.padded, self.dtype)
+        self.grad = alloc_grad(self.padded, self.dtype)
         with torch.no_grad():
             for p, o in zip(self.params, self.offsets):
                 self.param[o:o + p.numel()].copy_(p.data.reshape(-1))

@@ -1,0 +1,135 @@
+"""Symmetric-memory transport: peer pointers over NVLink / NVSwitch + hand-written collectives.
+
+Bootstrap (allocation, handle exchange, peer pointer tables) uses
+``torch.distributed._symmetric_memory``; the data plane is this package's kernels
+(``csrc/comm.cu``): a flag barrier with bounded waits, a one-shot reduce-scatter that pulls every
+peer's gradient shard and sums in fp32, a one-shot all-gather that pushes the updated bf16 shard
+into every peer's resident parameters, and a small-vector all-reduce for the gradient norm and
+logged scalars. No NCCL call is made on these paths (NCCL only serves the bootstrap rendezvous).
+
+Two bf16 arenas (parameters, gradients) are allocated once; every :class:`FlatBuffer` is a view, so
+one rendezvous covers the whole model.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from ..ops import _ext
+from ..ops import gemm as G
+
+MAX_VEC = 4096  # floats per rank in the small all-reduce scratch
+
+
+class SymmComm:
+    def __init__(self, group, device):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.symm_mem = symm_mem
+        self.group = group
+        self.device = device
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        if self.world > 8:
+            raise ValueError("symmetric transport supports up to 8 ranks of one NVSwitch domain")
+        try:
+            symm_mem.enable_symm_mem_for_group(group.group_name)
+        except Exception:
+            pass
+        # control block: [0, 32) int32 flags (8 used) | then world * MAX_VEC floats of scratch
+        self.ctrl = symm_mem.empty(32 + self.world * MAX_VEC, dtype=torch.float32, device=device)
+        self.ctrl.zero_()
+        self.ctrl_hdl = symm_mem.rendezvous(self.ctrl, group)
+        base = [int(p) for p in self.ctrl_hdl.buffer_ptrs]
+        self.flag_ptrs = base
+        self.scratch_ptrs = [p + 32 * 4 for p in base]
+        self.scratch = self.ctrl[32:]
+        self.epoch = 0
+        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.param_arena = self.grad_arena = None
+        self._cursor = {"param": 0, "grad": 0}
+        self.local_sumsq = torch.zeros(1, dtype=torch.float32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+    # ------------------------------------------------------------------ allocation
+    def reserve(self, total_elems: int, dtype=torch.bfloat16) -> None:
+        sm = self.symm_mem
+        self.param_arena = sm.empty(total_elems, dtype=dtype, device=self.device)
+        self.grad_arena = sm.empty(total_elems, dtype=dtype, device=self.device)
+        self.param_arena.zero_()
+        self.grad_arena.zero_()
+        self.param_ptrs = [int(p) for p in sm.rendezvous(self.param_arena, self.group).buffer_ptrs]
+        self.grad_ptrs = [int(p) for p in sm.rendezvous(self.grad_arena, self.group).buffer_ptrs]
+        self._cursor = {"param": 0, "grad": 0}
+
+    def _take(self, which: str, n: int, dtype) -> torch.Tensor:
+        arena = self.param_arena if which == "param" else self.grad_arena
+        if arena is None:
+            raise RuntimeError("SymmComm.reserve() must be called before allocating flat buffers")
+        assert arena.dtype == dtype, "arena dtype mismatch"
+        c = self._cursor[which]
+        if c + n > arena.numel():
+            raise RuntimeError("symmetric arena exhausted")
+        self._cursor[which] = c + n
+        return arena[c:c + n]
+
+    def alloc_param(self, n: int, dtype) -> torch.Tensor:
+        return self._take("param", n, dtype)
+
+    def alloc_grad(self, n: int, dtype) -> torch.Tensor:
+        return self._take("grad", n, dtype)
+
+    def register_buffers(self, buffers) -> None:
+        rows, out_off = [], 0
+        elem = self.param_arena.element_size()
+        base = self.param_arena.data_ptr()
+        self.views = []
+        for b in buffers:
+            arena_off = (b.param.data_ptr() - base) // elem + self.rank * b.shard_size
+            rows.append([arena_off, b.shard_size, out_off])
+            self.views.append((out_off, b.shard_size))
+            out_off += b.shard_size
+        self.table = torch.tensor(rows, dtype=torch.int64, device=self.device)
+        self.gshard = torch.zeros(out_off, dtype=torch.float32, device=self.device)
+
+    # ------------------------------------------------------------------ collectives
+    def barrier(self) -> None:
+        self.epoch += 1
+        _ext.get().symm_barrier(self.flag_ptrs, self.rank, self.epoch, self.status)
+
+    def check(self) -> None:
+        """Raise if a barrier wait ran out (a peer died or stalled); synchronises."""
+        st = int(self.status[0].item())
+        if st != 0:
+            self.status.zero_()
+            raise RuntimeError(f"symmetric barrier timed out waiting for rank {st - 16}")
+
+    def reduce_scatter_grads(self, buffers) -> List[torch.Tensor]:
+        C = _ext.get()
+        self.barrier()  # every rank has finished writing its gradients
+        self.local_sumsq.zero_()
+        C.rs_reduce(self.grad_ptrs, self.table, self.gshard, self.local_sumsq)
+        return [self.gshard[o:o + n] for o, n in self.views]
+
+    def all_reduce_vector(self, t: torch.Tensor) -> torch.Tensor:
+        C = _ext.get()
+        v = t.detach().float().contiguous().reshape(-1)
+        if v.numel() > MAX_VEC:
+            raise ValueError(f"small all-reduce handles at most {MAX_VEC} floats")
+        C.small_allreduce_write(self.scratch_ptrs, v, self.rank)
+        self.barrier()
+        out = torch.empty_like(v)
+        C.small_allreduce_sum(self.scratch, out, self.world)
+        self.barrier()  # nobody overwrites the scratch before everyone has read it
+        return out.reshape(t.shape)
+
+    def all_reduce_scalar(self, t: torch.Tensor) -> torch.Tensor:
+        t.copy_(self.all_reduce_vector(t))
+        return t
+
+    def all_gather_params(self, buffers) -> None:
+        _ext.get().ag_push(self.param_ptrs, self.table, self.rank)
+        self.barrier()  # all pushes have landed before anyone reads the parameters

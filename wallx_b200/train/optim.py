@@ -72,8 +72,8 @@ class FlatAdamW:
                 seg_lr = lr * seg.lr_scale
                 if b.param.is_cuda:
                     hyper = self._hyper(b.device, seg_lr, wd)
-                    _ext.get().adamw_step(p16[lo:hi], b.master[lo:hi], b.exp_avg[lo:hi], b.exp_avg_sq[lo:hi],
-                                          g_all[lo:hi], hyper, norm_sq)
+                    fn = _ext.get().adamw_step_f32g if g_all.dtype == torch.float32 else _ext.get().adamw_step
+                    fn(p16[lo:hi], b.master[lo:hi], b.exp_avg[lo:hi], b.exp_avg_sq[lo:hi], g_all[lo:hi], hyper, norm_sq)
                 else:
                     self._cpu_step(b, lo, hi, g_all, seg_lr, wd, norm_sq)
 
