@@ -76,8 +76,11 @@ def test_symm_transport_matches_nccl(tmp_path):
     for k in s0["params"]:
         assert torch.equal(s0["params"][k], s1["params"][k]), k  # replicas identical
         assert torch.equal(d0["params"][k], d1["params"][k]), k
-        # fp32 peer sum vs NCCL's bf16 reduction: same up to bf16 rounding of one Adam step
-        assert torch.allclose(s0["params"][k], d0["params"][k], atol=2.5e-3), k
+        # fp32 peer sum vs NCCL's bf16 reduction: equal up to one bf16 ulp of the stored parameter
+        # (0.0039 at 1.0) plus a fraction of an lr-sized Adam step
+        a, b = s0["params"][k], d0["params"][k]
+        assert torch.allclose(a, b, atol=8e-3, rtol=8e-3), k
+        assert ((a - b).abs() > 2.5e-3).float().mean() < 0.2, k
     assert abs(s0["norms"][0] - d0["norms"][0]) / d0["norms"][0] < 2e-2
 
 

@@ -34,10 +34,6 @@ class SymmComm:
         self.world = dist.get_world_size(group)
         if self.world > 8:
             raise ValueError("symmetric transport supports up to 8 ranks of one NVSwitch domain")
-        try:
-            symm_mem.enable_symm_mem_for_group(group.group_name)
-        except Exception:
-            pass
         # control block: [0, 32) int32 flags (8 used) | then world * MAX_VEC floats of scratch
         self.ctrl = symm_mem.empty(32 + self.world * MAX_VEC, dtype=torch.float32, device=device)
         self.ctrl.zero_()
