@@ -267,3 +267,36 @@ def test_adamw_matches_torch():
     nsq = torch.zeros(1, device="cuda")
     C.sumsq_bf16(_bf(g), nsq)
     assert abs(nsq.item() - (_bf(g).float() ** 2).sum().item()) / nsq.item() < 1e-3
+
+
+def test_index_kernels_match_python_originals():
+    from wallx_b200.ops import index as IX, ref
+
+    IMG, VID, VS = 900, 901, 902
+    torch.manual_seed(8)
+    grids = [[1, 18, 18], [1, 8, 12], [1, 4, 4], [2, 6, 8]]
+    vgrids = [[3, 4, 6]]
+    n = lambda g: g[0] * (g[1] // 2) * (g[2] // 2)
+    rows = [
+        [5, 6, VS] + [IMG] * n(grids[0]) + [7] * 5 + [VS] + [IMG] * n(grids[1]) + [9, 9],
+        [11] * 9,
+        [VS] + [IMG] * n(grids[2]) + [8, 8, VS] + [VID] * n(vgrids[0]) + [3] + [VS] + [IMG] * n(grids[3]) + [4] * 7,
+    ]
+    S = max(len(r) for r in rows)
+    ids = torch.zeros((3, S), dtype=torch.long)
+    am = torch.zeros((3, S), dtype=torch.long)
+    for i, r in enumerate(rows):  # left padding
+        ids[i, S - len(r):] = torch.tensor(r)
+        am[i, S - len(r):] = 1
+    ig, vg = torch.tensor(grids), torch.tensor(vgrids)
+    spg = torch.tensor([0.5])
+    pos_r, d_r = ref.rope_index(ids, ig, vg, spg, am, 2, IMG, VID, VS, 2.0)
+    pos_c, d_c = IX.get_rope_index(ids.cuda(), ig.cuda(), vg.cuda(), spg.cuda(), am.cuda(), 2, IMG, VID, VS, 2.0)
+    assert torch.equal(pos_c.cpu(), pos_r) and torch.equal(d_c.cpu(), d_r)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, 40, 2).float() / 40))
+    a_r = ref.rot_pos_emb(inv, grids, 2)
+    a_c = IX.rot_pos_emb(inv.cuda(), ig.cuda(), 2)
+    assert torch.allclose(a_c.cpu(), a_r, atol=1e-6)
+    w_r, cu_r = ref.window_index(grids + [[1, 16, 16]], 112, 2, 14)
+    w_c, cu_c = IX.get_window_index(torch.tensor(grids + [[1, 16, 16]]).cuda(), 112, 2, 14)
+    assert torch.equal(w_c.cpu(), w_r) and cu_c.cpu().tolist() == cu_r

@@ -36,7 +36,7 @@ struct AttnArgs {
   CUtensorMap tmV;
   CUtensorMap tmDO;   // like tmQ
   const int4* qtab;   // [Tq] (k_lo, k_hi, k_lim, flag)
-  const int4* ktab;   // [Tk] (q_lo, q_hi, flag, 0)
+  const int4* ktab;   // [Tk] (q_lo, q_hi, first causal viewer row, flag | first viewer row << 1)
   __nv_bfloat16* out;   // fwd: O; dq: dQ
   long ld_out;
   __nv_bfloat16* out2;  // dkdv: dV (bf16, rep == 1)
@@ -58,33 +58,78 @@ struct SmemCtl {
   int kmin, kmax;
 };
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Bits c (0..63) with lo <= c <= hi.
+__device__ __forceinline__ uint64_t bits_between(int lo, int hi) {
+  lo = max(lo, 0);
+  hi = min(hi, 63);
+  if (hi < lo) return 0ull;
+  return (~0ull >> (63 - (hi - lo))) << lo;
+}
+// Which of the 64 keys starting at kbase a query row may see: its causal interval, plus (for a
+// flagged row) the flagged keys of its own sequence. `kflags` has bit c set when key kbase+c is flagged.
+__device__ __forceinline__ uint64_t row_key_mask(const int4& qi, int kbase, uint64_t kflags) {
+  uint64_t m = bits_between(qi.x - kbase, min(qi.z, qi.y - 1) - kbase);
+  if (qi.w != 0) m |= kflags & bits_between(qi.x - kbase, qi.y - 1 - kbase);
+  return m;
+}
+// 64-bit ballot over a shared int[64] of 0/1 flags (all 32 lanes of the warp take part).
+__device__ __forceinline__ uint64_t flags_to_mask(const int* flags64) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t lo = __ballot_sync(0xffffffffu, flags64[lane] != 0);
+  const uint32_t hi = __ballot_sync(0xffffffffu, flags64[32 + lane] != 0);
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+
 __device__ __forceinline__ bool key_allowed(int kk, const int4& qi, int kflag) {
   return kk >= qi.x && kk < qi.y && (kk <= qi.z || (qi.w != 0 && kflag != 0));
 }
 
+// Optional stage timestamps of one CTA (debug builds with -DWX_ATTN_TRACE only).
+#ifdef WX_ATTN_TRACE
+__device__ long long g_attn_trace[16 * 16];
+#define TRACE_AS(t, slot) do { if (blockIdx.x == 3 && blockIdx.y == 0 && tid == (t) && j < 16) g_attn_trace[j * 16 + (slot)] = clock64(); } while (0)
+#else
+#define TRACE_AS(t, slot) do {} while (0)
+#endif
+
 // ================================================================================ forward
+// 160 threads: warps 0..3 own one query row per thread (softmax, O rescale, epilogue); warp 4 is
+// the issue warp (one lane drives TMA loads and tcgen05.mma). The two roles talk through mbarriers
+// only, so the issuing lane never shares a warp with threads that wait.
 // smem: Q 2x[128][64] (32 KB) | stage s in {0,1}: K 2x[64][64] (16 KB) | V 2x[64][64] (16 KB).
 // P (16 KB, [128][64] K-major) overwrites the K stage once S has been read.
-__global__ void __launch_bounds__(AT_THREADS, 2)
+// Barriers: kv_full[2] (TMA), q_full (TMA), s_bar (QK done), s_free (S copied to registers, 128
+// arrivals), p_ready (P in smem and O rescaled, 128 arrivals), pv_bar (PV done).
+constexpr int FWD_THREADS = 160;
+__global__ void __launch_bounds__(FWD_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ AttnArgs a, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sKV = smem + 32768;  // stage s: K at sKV + s*32768, V at + 16384
   __shared__ SmemCtl ctl;
-  __shared__ int s_kflag[64];
+  __shared__ int s_kflag[2][64];
   uint64_t* kv_full = &ctl.bar[0];  // [2]
   uint64_t* q_full = &ctl.bar[2];
   uint64_t* s_bar = &ctl.bar[3];
   uint64_t* pv_bar = &ctl.bar[4];
+  uint64_t* s_free = &ctl.bar[5];
+  uint64_t* p_ready = &ctl.bar[6];
   volatile int* abort_flag = &ctl.abort_flag;
 
   const int tid = threadIdx.x, warp = tid >> 5;
+  const bool is_row = warp < 4;
   const int h = blockIdx.y;
   const int g = h / (a.hq / a.hkv);
   const int r0 = blockIdx.x * 128;
   const int row = r0 + tid;
-  const bool row_ok = row < a.Tq;
+  const bool row_ok = is_row && row < a.Tq;
   const int D = a.D;
   const int nbox = (D + 63) / 64;
 
@@ -92,6 +137,8 @@ attn_fwd_kernel(const __grid_constant__ AttnArgs a, int* __restrict__ status) {
   if (row_ok) qi = a.qtab[row];
   if (tid == 0) {
     for (int i = 0; i < 5; ++i) mbar_init(&ctl.bar[i], 1);
+    mbar_init(s_free, 128);
+    mbar_init(p_ready, 128);
     ctl.abort_flag = 0;
     ctl.kmin = 0x7fffffff;
     ctl.kmax = 0;
@@ -112,161 +159,191 @@ attn_fwd_kernel(const __grid_constant__ AttnArgs a, int* __restrict__ status) {
   __syncthreads();
   const uint32_t tmem = ctl.tmem_slot;
   const uint32_t tS = tmem;        // 64 columns
-  const uint32_t tO = tmem + 64;   // D columns
+  const uint32_t tO = tmem + 128;  // D columns
   const int kmin = ctl.kmin, kmax = ctl.kmax;
   const int nblk = (kmax > kmin) ? (kmax - kmin + 63) / 64 : 0;
-  const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-  const uint32_t kv_bytes = static_cast<uint32_t>(nbox) * 8192u * 2u;
-
-  auto load_kv = [&](int j) {
-    const int st = j & 1;
-    uint8_t* sK = sKV + st * 32768;
-    uint8_t* sV = sK + 16384;
-    mbar_arrive_expect_tx(&kv_full[st], kv_bytes);
-    for (int b = 0; b < nbox; ++b) {
-      tma_load_2d(sK + b * 8192, &a.tmK, &kv_full[st], g * D + b * 64, kmin + j * 64);
-      tma_load_2d(sV + b * 8192, &a.tmV, &kv_full[st], g * D + b * 64, kmin + j * 64);
-    }
-  };
-
-  if (tid == 0 && nblk > 0) {
-    mbar_arrive_expect_tx(q_full, static_cast<uint32_t>(nbox) * 16384u);
-    for (int b = 0; b < nbox; ++b) tma_load_2d(sQ + b * 16384, &a.tmQ, q_full, h * D + b * 64, r0);
-    load_kv(0);
-    if (nblk > 1) load_kv(1);
-  }
-
   const float scale_log2 = a.scale * LOG2E;
   float m_run = -INFINITY, l_run = 0.f;
-  const uint32_t idesc_s = make_idesc_bf16(128, 64, false, false);
-  const uint32_t idesc_o = make_idesc_bf16(128, D, false, true);
   bool ok = nblk > 0;
-  if (ok) ok = mbar_wait(q_full, 0, abort_flag);
 
-  for (int j = 0; j < nblk; ++j) {
-    const int st = j & 1;
-    uint8_t* sK = sKV + st * 32768;
-    uint8_t* sV = sK + 16384;
-    uint8_t* sP = sK;
-    if (ok) ok = mbar_wait(&kv_full[st], (j >> 1) & 1, abort_flag);
-    if (a.has_bidir && tid < 64) {
-      const int kk = kmin + j * 64 + tid;
-      s_kflag[tid] = (kk < a.Tk) ? a.ktab[kk].z : 0;
-    }
-    if (tid == 0 && ok) {
-      tc_fence_after();
-      const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK);
-      for (int k = 0; k < D / 16; ++k) {
-        const uint64_t da = make_smem_desc_sw128(qa + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
-        const uint64_t db = make_smem_desc_sw128(ka + (k >> 2) * 8192 + (k & 3) * 32, 16, 1024);
-        tc_mma_bf16(tS, da, db, idesc_s, k != 0);
-      }
-      tc_commit(s_bar);
-    }
-    if (a.has_bidir) __syncthreads();
-    if (ok) ok = mbar_wait(s_bar, j & 1, abort_flag);
-    tc_fence_after();
-
-    // ---- softmax on this thread's row
-    uint32_t pk[32];
-    float m_new = m_run;
-    float sc[64];
-    {
-      uint32_t r[32];
-      tmem_ld_32x32(tS + lane_off, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int c = 0; c < 32; ++c) sc[c] = __uint_as_float(r[c]);
-      tmem_ld_32x32(tS + lane_off + 32, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int c = 0; c < 32; ++c) sc[32 + c] = __uint_as_float(r[c]);
-    }
-    const int kbase = kmin + j * 64;
-#pragma unroll
-    for (int c = 0; c < 64; ++c) {
-      const bool al = key_allowed(kbase + c, qi, a.has_bidir ? s_kflag[c] : 0);
-      sc[c] = al ? sc[c] * scale_log2 : -INFINITY;
-      m_new = fmaxf(m_new, sc[c]);
-    }
-    const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-    const float alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_use);
-    float psum = 0.f;
-#pragma unroll
-    for (int c = 0; c < 64; c += 2) {
-      const float p0 = exp2f(sc[c] - m_use), p1 = exp2f(sc[c + 1] - m_use);
-      psum += p0 + p1;
-      pk[c >> 1] = pack_bf16x2(p0, p1);
-    }
-    l_run = l_run * alpha + psum;
-    const bool changed = m_new > m_run;
-    m_run = m_new;
-
-    // ---- previous P V must be done before P smem / O are touched
-    if (j > 0) {
-      if (ok) ok = mbar_wait(pv_bar, (j - 1) & 1, abort_flag);
-      tc_fence_after();
-      if (tid == 0 && ok && j + 1 < nblk) load_kv(j + 1);
-      if (__any_sync(0xffffffffu, changed)) {
-        for (int c = 0; c < D; c += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32(tO + lane_off + c, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
-          tmem_st_32x32(tO + lane_off + c, r);
+  if (!is_row) {
+    // ------------------------------------------------------------------ issue warp
+    if (tid == 128 && nblk > 0) {
+      const uint32_t kv_bytes = static_cast<uint32_t>(nbox) * 8192u * 2u;
+      const uint32_t idesc_s = make_idesc_bf16(128, 64, false, false);
+      const uint32_t idesc_o = make_idesc_bf16(128, D, false, true);
+      auto load_kv = [&](int j) {
+        const int st = j & 1;
+        uint8_t* sK = sKV + st * 32768;
+        uint8_t* sV = sK + 16384;
+        mbar_arrive_expect_tx(&kv_full[st], kv_bytes);
+        for (int b = 0; b < nbox; ++b) {
+          tma_load_2d(sK + b * 8192, &a.tmK, &kv_full[st], g * D + b * 64, kmin + j * 64);
+          tma_load_2d(sV + b * 8192, &a.tmV, &kv_full[st], g * D + b * 64, kmin + j * 64);
         }
-        tmem_st_wait();
+      };
+      mbar_arrive_expect_tx(q_full, static_cast<uint32_t>(nbox) * 16384u);
+      for (int b = 0; b < nbox; ++b) tma_load_2d(sQ + b * 16384, &a.tmQ, q_full, h * D + b * 64, r0);
+      load_kv(0);
+      if (nblk > 1) load_kv(1);
+      ok = mbar_wait(q_full, 0, abort_flag);
+      const uint32_t qa = smem_u32(sQ);
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ka = smem_u32(sKV + st * 32768), va = ka + 16384;
+        TRACE_AS(128, 0);
+        ok = mbar_wait(&kv_full[st], (j >> 1) & 1, abort_flag);
+        TRACE_AS(128, 1);
+        if (ok && j > 0) ok = mbar_wait(s_free, (j - 1) & 1, abort_flag);  // S(j-1) is in registers
+        if (!ok) break;
+        TRACE_AS(128, 2);
+        tc_fence_after();
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t da = make_smem_desc_sw128(qa + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(ka + (k >> 2) * 8192 + (k & 3) * 32, 16, 1024);
+          tc_mma_bf16(tS, da, db, idesc_s, k != 0);
+        }
+        tc_commit(s_bar);
+        TRACE_AS(128, 3);
+        // stage (j+1)&1 was last read by PV(j-1): refill it once that is done
+        if (j > 0 && j + 1 < nblk) {
+          ok = mbar_wait(pv_bar, (j - 1) & 1, abort_flag);
+          if (!ok) break;
+          load_kv(j + 1);
+        }
+        TRACE_AS(128, 4);
+        ok = mbar_wait(p_ready, j & 1, abort_flag);
+        if (!ok) break;
+        TRACE_AS(128, 5);
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint64_t da = make_smem_desc_sw128(ka + k * 32, 16, 1024);          // P lives in the K stage
+          const uint64_t db = make_smem_desc_sw128(va + k * 2048, 8192, 1024);
+          tc_mma_bf16(tO, da, db, idesc_o, (j | k) != 0);
+        }
+        tc_commit(pv_bar);
+        TRACE_AS(128, 6);
       }
     }
-#pragma unroll
-    for (int c16 = 0; c16 < 8; ++c16)
-      *reinterpret_cast<uint4*>(sP + sw128_offset(tid, c16)) =
-          make_uint4(pk[4 * c16], pk[4 * c16 + 1], pk[4 * c16 + 2], pk[4 * c16 + 3]);
-    fence_proxy_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0 && ok) {
+  } else {
+    // ------------------------------------------------------------------ softmax warps
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    for (int j = 0; j < nblk; ++j) {
+      const int st = j & 1;
+      uint8_t* sP = sKV + st * 32768;
+      const int kbase = kmin + j * 64;
+      if (a.has_bidir && tid < 64) {
+        const int kk = kbase + tid;
+        s_kflag[st][tid] = (kk < a.Tk) ? (a.ktab[kk].w & 1) : 0;
+      }
+      if (a.has_bidir) asm volatile("bar.sync 1, 128;" ::: "memory");  // flags visible to the 4 row warps
+      TRACE_AS(0, 8);
+      if (ok) ok = mbar_wait(s_bar, j & 1, abort_flag);
       tc_fence_after();
-      const uint32_t pa = smem_u32(sP), va = smem_u32(sV);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const uint64_t da = make_smem_desc_sw128(pa + k * 32, 16, 1024);
-        const uint64_t db = make_smem_desc_sw128(va + k * 2048, 8192, 1024);
-        tc_mma_bf16(tO, da, db, idesc_o, (j | k) != 0);
-      }
-      tc_commit(pv_bar);
-    }
-  }
-
-  if (ok && nblk > 0) ok = mbar_wait(pv_bar, (nblk - 1) & 1, abort_flag);
-  tc_fence_after();
-  {
-    // TMEM loads are warp-collective: every lane runs them, only the stores are predicated.
-    const bool have = __all_sync(0xffffffffu, ok) && nblk > 0;
-    const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
-    __nv_bfloat16* orow = a.out + static_cast<long>(row) * a.ld_out + h * D;
-    for (int c = 0; c < D; c += 16) {
-      uint32_t r[16];
-      if (have) {
-        tmem_ld_32x16(tO + lane_off + c, r);
+      TRACE_AS(0, 9);
+      float sc[64];
+      {
+        uint32_t r[32];
+        tmem_ld_32x32(tS + lane_off, r);
         tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) sc[c] = __uint_as_float(r[c]);
+        tmem_ld_32x32(tS + lane_off + 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) sc[32 + c] = __uint_as_float(r[c]);
+      }
+      tc_fence_before();
+      mbar_arrive(s_free);  // the issue warp may overwrite S with the next block's scores
+      TRACE_AS(0, 10);
+      // Interior blocks (every key visible to every row of the warp) skip the per-element mask.
+      const bool fast = __all_sync(0xffffffffu, kbase >= qi.x && kbase + 63 <= qi.z && kbase + 63 < qi.y);
+      float raw_max = -INFINITY;
+      if (fast) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) raw_max = fmaxf(raw_max, sc[c]);
       } else {
+        const uint64_t km = row_key_mask(qi, kbase, a.has_bidir ? flags_to_mask(s_kflag[st]) : 0ull);
+        const uint32_t km_lo = static_cast<uint32_t>(km), km_hi = static_cast<uint32_t>(km >> 32);
 #pragma unroll
-        for (int e = 0; e < 16; ++e) r[e] = 0u;
+        for (int c = 0; c < 32; ++c) {
+          sc[c] = (km_lo & (1u << c)) ? sc[c] : -INFINITY;
+          sc[32 + c] = (km_hi & (1u << c)) ? sc[32 + c] : -INFINITY;
+          raw_max = fmaxf(raw_max, fmaxf(sc[c], sc[32 + c]));
+        }
       }
-      if (row_ok) {
+      const float m_new = fmaxf(m_run, raw_max * scale_log2);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = (m_run == -INFINITY) ? 0.f : ex2_approx(m_run - m_use);
+      float psum = 0.f;
+      uint32_t pk[32];
 #pragma unroll
-        for (int q2 = 0; q2 < 2; ++q2)
-          reinterpret_cast<uint4*>(orow + c)[q2] = make_uint4(
-              pack_bf16x2(__uint_as_float(r[8 * q2 + 0]) * inv_l, __uint_as_float(r[8 * q2 + 1]) * inv_l),
-              pack_bf16x2(__uint_as_float(r[8 * q2 + 2]) * inv_l, __uint_as_float(r[8 * q2 + 3]) * inv_l),
-              pack_bf16x2(__uint_as_float(r[8 * q2 + 4]) * inv_l, __uint_as_float(r[8 * q2 + 5]) * inv_l),
-              pack_bf16x2(__uint_as_float(r[8 * q2 + 6]) * inv_l, __uint_as_float(r[8 * q2 + 7]) * inv_l));
+      for (int c = 0; c < 64; c += 2) {
+        const float p0 = ex2_approx(fmaf(sc[c], scale_log2, -m_use));
+        const float p1 = ex2_approx(fmaf(sc[c + 1], scale_log2, -m_use));
+        psum += p0 + p1;
+        pk[c >> 1] = pack_bf16x2(p0, p1);
       }
+      l_run = l_run * alpha + psum;
+      const bool changed = m_new > m_run;
+      m_run = m_new;
+      TRACE_AS(0, 11);
+      // PV(j-1) must be done before O is rescaled; P(j) goes to the other stage, which PV(j-2) freed
+      if (j > 0) {
+        if (ok) ok = mbar_wait(pv_bar, (j - 1) & 1, abort_flag);
+        tc_fence_after();
+        TRACE_AS(0, 12);
+        if (__any_sync(0xffffffffu, changed)) {
+          for (int c = 0; c < D; c += 32) {
+            uint32_t r[32];
+            tmem_ld_32x32(tO + lane_off + c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+            tmem_st_32x32(tO + lane_off + c, r);
+          }
+          tmem_st_wait();
+        }
+      }
+#pragma unroll
+      for (int c16 = 0; c16 < 8; ++c16)
+        *reinterpret_cast<uint4*>(sP + sw128_offset(tid, c16)) =
+            make_uint4(pk[4 * c16], pk[4 * c16 + 1], pk[4 * c16 + 2], pk[4 * c16 + 3]);
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_ready);
+      TRACE_AS(0, 13);
     }
-    if (row_ok)
-      a.lse[static_cast<long>(h) * a.Tq + row] = (have && l_run > 0.f) ? (m_run + log2f(l_run)) * LN2 : -INFINITY;
+    if (ok && nblk > 0) ok = mbar_wait(pv_bar, (nblk - 1) & 1, abort_flag);
+    tc_fence_after();
+    {
+      // TMEM loads are warp-collective: every lane runs them, only the stores are predicated.
+      const bool have = __all_sync(0xffffffffu, ok) && nblk > 0;
+      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* orow = a.out + static_cast<long>(row) * a.ld_out + h * D;
+      for (int c = 0; c < D; c += 16) {
+        uint32_t r[16];
+        if (have) {
+          tmem_ld_32x16(tO + lane_off + c, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) r[e] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int q2 = 0; q2 < 2; ++q2)
+            reinterpret_cast<uint4*>(orow + c)[q2] = make_uint4(
+                pack_bf16x2(__uint_as_float(r[8 * q2 + 0]) * inv_l, __uint_as_float(r[8 * q2 + 1]) * inv_l),
+                pack_bf16x2(__uint_as_float(r[8 * q2 + 2]) * inv_l, __uint_as_float(r[8 * q2 + 3]) * inv_l),
+                pack_bf16x2(__uint_as_float(r[8 * q2 + 4]) * inv_l, __uint_as_float(r[8 * q2 + 5]) * inv_l),
+                pack_bf16x2(__uint_as_float(r[8 * q2 + 6]) * inv_l, __uint_as_float(r[8 * q2 + 7]) * inv_l));
+        }
+      }
+      if (row_ok)
+        a.lse[static_cast<long>(h) * a.Tq + row] = (have && l_run > 0.f) ? (m_run + log2f(l_run)) * LN2 : -INFINITY;
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -299,9 +376,11 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, long ld_
 }
 
 // ================================================================================ dQ
+// 160 threads: warps 0..3 own one query row per thread, warp 4 issues TMA and tcgen05.mma.
 // smem: Q 2x[128][64] (32 KB) | dO 2x[128][64] (32 KB) | K 2x[64][64] (16 KB) | V 2x[64][64] (16 KB).
 // dS ([128][64] K-major, 16 KB) overwrites V once dP has been read.
-__global__ void __launch_bounds__(AT_THREADS, 2)
+constexpr int DQ_THREADS = 160;
+__global__ void __launch_bounds__(DQ_THREADS, 2)
 attn_dq_kernel(const __grid_constant__ AttnArgs a, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -310,31 +389,34 @@ attn_dq_kernel(const __grid_constant__ AttnArgs a, int* __restrict__ status) {
   uint8_t* sK = smem + 65536;
   uint8_t* sV = smem + 81920;
   __shared__ SmemCtl ctl;
-  __shared__ int s_kflag[64];
+  __shared__ int s_kflag[2][64];
   uint64_t* kv_full = &ctl.bar[0];
   uint64_t* q_full = &ctl.bar[1];
   uint64_t* s_bar = &ctl.bar[2];
   uint64_t* dq_bar = &ctl.bar[3];
+  uint64_t* ds_ready = &ctl.bar[4];
   volatile int* abort_flag = &ctl.abort_flag;
 
   const int tid = threadIdx.x, warp = tid >> 5;
+  const bool is_row = warp < 4;
   const int h = blockIdx.y;
   const int g = h / (a.hq / a.hkv);
   const int r0 = blockIdx.x * 128;
   const int row = r0 + tid;
-  const bool row_ok = row < a.Tq;
+  const bool row_ok = is_row && row < a.Tq;
   const int D = a.D;
   const int nbox = (D + 63) / 64;
 
   int4 qi = make_int4(0, 0, -1, 0);
-  float lse2 = 0.f, dlt = 0.f;
+  float lse2 = 0.f, dlt_s = 0.f;
   if (row_ok) {
     qi = a.qtab[row];
     lse2 = a.lse[static_cast<long>(h) * a.Tq + row] * LOG2E;
-    dlt = a.delta[static_cast<long>(h) * a.Tq + row];
+    dlt_s = a.delta[static_cast<long>(h) * a.Tq + row] * a.scale;
   }
   if (tid == 0) {
     for (int i = 0; i < 4; ++i) mbar_init(&ctl.bar[i], 1);
+    mbar_init(ds_ready, 128);
     ctl.abort_flag = 0;
     ctl.kmin = 0x7fffffff;
     ctl.kmax = 0;
@@ -357,114 +439,125 @@ attn_dq_kernel(const __grid_constant__ AttnArgs a, int* __restrict__ status) {
   const uint32_t tS = tmem, tDP = tmem + 64, tDQ = tmem + 128;
   const int kmin = ctl.kmin, kmax = ctl.kmax;
   const int nblk = (kmax > kmin) ? (kmax - kmin + 63) / 64 : 0;
-  const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-  const uint32_t kv_bytes = static_cast<uint32_t>(nbox) * 8192u * 2u;
-
-  auto load_kv = [&](int j) {
-    mbar_arrive_expect_tx(kv_full, kv_bytes);
-    for (int b = 0; b < nbox; ++b) {
-      tma_load_2d(sK + b * 8192, &a.tmK, kv_full, g * D + b * 64, kmin + j * 64);
-      tma_load_2d(sV + b * 8192, &a.tmV, kv_full, g * D + b * 64, kmin + j * 64);
-    }
-  };
-  if (tid == 0 && nblk > 0) {
-    mbar_arrive_expect_tx(q_full, static_cast<uint32_t>(nbox) * 16384u * 2u);
-    for (int b = 0; b < nbox; ++b) {
-      tma_load_2d(sQ + b * 16384, &a.tmQ, q_full, h * D + b * 64, r0);
-      tma_load_2d(sDO + b * 16384, &a.tmDO, q_full, h * D + b * 64, r0);
-    }
-    load_kv(0);
-  }
   const float scale_log2 = a.scale * LOG2E;
-  const uint32_t idesc_s = make_idesc_bf16(128, 64, false, false);
-  const uint32_t idesc_dq = make_idesc_bf16(128, D, false, true);
   bool ok = nblk > 0;
-  if (ok) ok = mbar_wait(q_full, 0, abort_flag);
 
-  for (int j = 0; j < nblk; ++j) {
-    if (ok) ok = mbar_wait(kv_full, j & 1, abort_flag);
-    if (a.has_bidir && tid < 64) {
-      const int kk = kmin + j * 64 + tid;
-      s_kflag[tid] = (kk < a.Tk) ? a.ktab[kk].z : 0;
-    }
-    if (tid == 0 && ok) {
-      tc_fence_after();
-      const uint32_t qa = smem_u32(sQ), da_ = smem_u32(sDO), ka = smem_u32(sK), va = smem_u32(sV);
-      for (int k = 0; k < D / 16; ++k) {
-        const uint32_t ao = (k >> 2) * 16384 + (k & 3) * 32, bo = (k >> 2) * 8192 + (k & 3) * 32;
-        tc_mma_bf16(tS, make_smem_desc_sw128(qa + ao, 16, 1024), make_smem_desc_sw128(ka + bo, 16, 1024), idesc_s, k != 0);
-      }
-      for (int k = 0; k < D / 16; ++k) {
-        const uint32_t ao = (k >> 2) * 16384 + (k & 3) * 32, bo = (k >> 2) * 8192 + (k & 3) * 32;
-        tc_mma_bf16(tDP, make_smem_desc_sw128(da_ + ao, 16, 1024), make_smem_desc_sw128(va + bo, 16, 1024), idesc_s, k != 0);
-      }
-      tc_commit(s_bar);
-    }
-    if (a.has_bidir) __syncthreads();
-    if (ok) ok = mbar_wait(s_bar, j & 1, abort_flag);
-    tc_fence_after();
-    const int kbase = kmin + j * 64;
-    uint32_t pk[32];
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      uint32_t rs[32], rp[32];
-      tmem_ld_32x32(tS + lane_off + half * 32, rs);
-      tmem_ld_32x32(tDP + lane_off + half * 32, rp);
-      tmem_ld_wait();
-#pragma unroll
-      for (int c = 0; c < 32; c += 2) {
-        float ds[2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int cc = half * 32 + c + e;
-          const bool al = key_allowed(kbase + cc, qi, a.has_bidir ? s_kflag[cc] : 0);
-          const float p = al ? exp2f(__uint_as_float(rs[c + e]) * scale_log2 - lse2) : 0.f;
-          ds[e] = p * (__uint_as_float(rp[c + e]) - dlt) * a.scale;
+  if (!is_row) {
+    if (tid == 128 && nblk > 0) {
+      const uint32_t kv_bytes = static_cast<uint32_t>(nbox) * 8192u * 2u;
+      const uint32_t idesc_s = make_idesc_bf16(128, 64, false, false);
+      const uint32_t idesc_dq = make_idesc_bf16(128, D, false, true);
+      auto load_kv = [&](int j) {
+        mbar_arrive_expect_tx(kv_full, kv_bytes);
+        for (int b = 0; b < nbox; ++b) {
+          tma_load_2d(sK + b * 8192, &a.tmK, kv_full, g * D + b * 64, kmin + j * 64);
+          tma_load_2d(sV + b * 8192, &a.tmV, kv_full, g * D + b * 64, kmin + j * 64);
         }
-        pk[(half * 32 + c) >> 1] = pack_bf16x2(ds[0], ds[1]);
+      };
+      mbar_arrive_expect_tx(q_full, static_cast<uint32_t>(nbox) * 16384u * 2u);
+      for (int b = 0; b < nbox; ++b) {
+        tma_load_2d(sQ + b * 16384, &a.tmQ, q_full, h * D + b * 64, r0);
+        tma_load_2d(sDO + b * 16384, &a.tmDO, q_full, h * D + b * 64, r0);
+      }
+      load_kv(0);
+      ok = mbar_wait(q_full, 0, abort_flag);
+      const uint32_t qa = smem_u32(sQ), da_ = smem_u32(sDO), ka = smem_u32(sK), va = smem_u32(sV);
+      for (int j = 0; j < nblk && ok; ++j) {
+        ok = mbar_wait(kv_full, j & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t ao = (k >> 2) * 16384 + (k & 3) * 32, bo = (k >> 2) * 8192 + (k & 3) * 32;
+          tc_mma_bf16(tS, make_smem_desc_sw128(qa + ao, 16, 1024), make_smem_desc_sw128(ka + bo, 16, 1024), idesc_s, k != 0);
+        }
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t ao = (k >> 2) * 16384 + (k & 3) * 32, bo = (k >> 2) * 8192 + (k & 3) * 32;
+          tc_mma_bf16(tDP, make_smem_desc_sw128(da_ + ao, 16, 1024), make_smem_desc_sw128(va + bo, 16, 1024), idesc_s, k != 0);
+        }
+        tc_commit(s_bar);
+        ok = mbar_wait(ds_ready, j & 1, abort_flag);  // dS is in smem (over V)
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma_bf16(tDQ, make_smem_desc_sw128(va + k * 32, 16, 1024), make_smem_desc_sw128(ka + k * 2048, 8192, 1024),
+                      idesc_dq, (j | k) != 0);
+        tc_commit(dq_bar);
+        if (j + 1 < nblk) {  // K and dS are read by the MMA just issued: refill when it is done
+          ok = mbar_wait(dq_bar, j & 1, abort_flag);
+          if (!ok) break;
+          load_kv(j + 1);
+        }
       }
     }
-    uint8_t* sDS = sV;
-#pragma unroll
-    for (int c16 = 0; c16 < 8; ++c16)
-      *reinterpret_cast<uint4*>(sDS + sw128_offset(tid, c16)) =
-          make_uint4(pk[4 * c16], pk[4 * c16 + 1], pk[4 * c16 + 2], pk[4 * c16 + 3]);
-    fence_proxy_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0 && ok) {
+  } else {
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    for (int j = 0; j < nblk; ++j) {
+      const int st = j & 1;
+      const int kbase = kmin + j * 64;
+      if (a.has_bidir) {
+        if (tid < 64) {
+          const int kk = kbase + tid;
+          s_kflag[st][tid] = (kk < a.Tk) ? (a.ktab[kk].w & 1) : 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      if (ok) ok = mbar_wait(s_bar, j & 1, abort_flag);
       tc_fence_after();
-      const uint32_t sa = smem_u32(sDS), ka = smem_u32(sK);
+      const bool fast = __all_sync(0xffffffffu, kbase >= qi.x && kbase + 63 <= qi.z && kbase + 63 < qi.y);
+      uint64_t km = ~0ull;
+      if (!fast) km = row_key_mask(qi, kbase, a.has_bidir ? flags_to_mask(s_kflag[st]) : 0ull);
+      uint32_t pk[32];
 #pragma unroll
-      for (int k = 0; k < 4; ++k)
-        tc_mma_bf16(tDQ, make_smem_desc_sw128(sa + k * 32, 16, 1024), make_smem_desc_sw128(ka + k * 2048, 8192, 1024),
-                    idesc_dq, (j | k) != 0);
-      tc_commit(dq_bar);
-    }
-    if (ok) ok = mbar_wait(dq_bar, j & 1, abort_flag);
-    if (tid == 0 && ok && j + 1 < nblk) load_kv(j + 1);
-  }
-  tc_fence_after();
-  {
-    const bool have = __all_sync(0xffffffffu, ok) && nblk > 0;
-    __nv_bfloat16* orow = a.out + static_cast<long>(row) * a.ld_out + h * D;
-    for (int c = 0; c < D; c += 16) {
-      uint32_t r[16];
-      if (have) {
-        tmem_ld_32x16(tDQ + lane_off + c, r);
+      for (int half = 0; half < 2; ++half) {
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32(tS + lane_off + half * 32, rs);
+        tmem_ld_32x32(tDP + lane_off + half * 32, rp);
         tmem_ld_wait();
-      } else {
+        const uint32_t kmh = static_cast<uint32_t>(km >> (32 * half));
 #pragma unroll
-        for (int e = 0; e < 16; ++e) r[e] = 0u;
+        for (int c = 0; c < 32; c += 2) {
+          float p0 = ex2_approx(fmaf(__uint_as_float(rs[c]), scale_log2, -lse2));
+          float p1 = ex2_approx(fmaf(__uint_as_float(rs[c + 1]), scale_log2, -lse2));
+          if (!fast) {
+            p0 = (kmh & (1u << c)) ? p0 : 0.f;
+            p1 = (kmh & (2u << c)) ? p1 : 0.f;
+          }
+          pk[(half * 32 + c) >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[c]), a.scale, -dlt_s),
+                                                 p1 * fmaf(__uint_as_float(rp[c + 1]), a.scale, -dlt_s));
+        }
       }
-      if (row_ok) {
 #pragma unroll
-        for (int q2 = 0; q2 < 2; ++q2)
-          reinterpret_cast<uint4*>(orow + c)[q2] =
-              make_uint4(pack_bf16x2(__uint_as_float(r[8 * q2 + 0]), __uint_as_float(r[8 * q2 + 1])),
-                         pack_bf16x2(__uint_as_float(r[8 * q2 + 2]), __uint_as_float(r[8 * q2 + 3])),
-                         pack_bf16x2(__uint_as_float(r[8 * q2 + 4]), __uint_as_float(r[8 * q2 + 5])),
-                         pack_bf16x2(__uint_as_float(r[8 * q2 + 6]), __uint_as_float(r[8 * q2 + 7])));
+      for (int c16 = 0; c16 < 8; ++c16)
+        *reinterpret_cast<uint4*>(sV + sw128_offset(tid, c16)) =
+            make_uint4(pk[4 * c16], pk[4 * c16 + 1], pk[4 * c16 + 2], pk[4 * c16 + 3]);
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(ds_ready);
+    }
+    if (ok && nblk > 0) ok = mbar_wait(dq_bar, (nblk - 1) & 1, abort_flag);
+    tc_fence_after();
+    {
+      const bool have = __all_sync(0xffffffffu, ok) && nblk > 0;
+      __nv_bfloat16* orow = a.out + static_cast<long>(row) * a.ld_out + h * D;
+      for (int c = 0; c < D; c += 16) {
+        uint32_t r[16];
+        if (have) {
+          tmem_ld_32x16(tDQ + lane_off + c, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) r[e] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int q2 = 0; q2 < 2; ++q2)
+            reinterpret_cast<uint4*>(orow + c)[q2] =
+                make_uint4(pack_bf16x2(__uint_as_float(r[8 * q2 + 0]), __uint_as_float(r[8 * q2 + 1])),
+                           pack_bf16x2(__uint_as_float(r[8 * q2 + 2]), __uint_as_float(r[8 * q2 + 3])),
+                           pack_bf16x2(__uint_as_float(r[8 * q2 + 4]), __uint_as_float(r[8 * q2 + 5])),
+                           pack_bf16x2(__uint_as_float(r[8 * q2 + 6]), __uint_as_float(r[8 * q2 + 7])));
+        }
       }
     }
   }
@@ -478,13 +571,14 @@ attn_dq_kernel(const __grid_constant__ AttnArgs a, int* __restrict__ status) {
 }
 
 // ================================================================================ dK / dV
-// One CTA: 128 keys of kv head g, one query head h. smem: K 2x[128][64] (32 KB) | V (32 KB) |
-// stage s in {0,1}: Q_i 2x[64][64] (16 KB) + dO_i (16 KB) | P^T [128][64] (16 KB) | dS^T (16 KB).
-struct QCol {
-  int4 qi;
-  float lse2, delta;
-};
-__global__ void __launch_bounds__(AT_THREADS, 1)
+// One CTA: 128 keys of kv head g, one query head h. 160 threads: warps 0..3 own one key row per
+// thread, warp 4 issues TMA and tcgen05.mma. smem: K 2x[128][64] (32 KB) | V (32 KB) | stage s in
+// {0,1}: Q_i 2x[64][64] (16 KB) + dO_i (16 KB) | P^T [128][64] (16 KB) | dS^T (16 KB).
+// Which query columns a key row may be seen by is an interval of rows (from the first causal
+// viewer to the end of the sequence) plus, for a flagged key, the flagged queries of the sequence:
+// one 64-bit mask per thread and block, no per-element table look-ups.
+constexpr int DKDV_THREADS = 160;
+__global__ void __launch_bounds__(DKDV_THREADS, 1)
 attn_dkdv_kernel(const __grid_constant__ AttnArgs a, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -494,28 +588,35 @@ attn_dkdv_kernel(const __grid_constant__ AttnArgs a, int* __restrict__ status) {
   uint8_t* sPT = smem + 65536 + 65536;
   uint8_t* sDST = sPT + 16384;
   __shared__ SmemCtl ctl;
-  __shared__ QCol s_q[64];
+  __shared__ __align__(16) float2 s_ld[2][64];  // (lse * log2e, delta * scale) per query column
+  __shared__ int s_qflag[2][64];
   uint64_t* qd_full = &ctl.bar[0];  // [2]
   uint64_t* kv_full = &ctl.bar[2];
   uint64_t* s_bar = &ctl.bar[3];
   uint64_t* acc_bar = &ctl.bar[4];
+  uint64_t* sp_free = &ctl.bar[5];
+  uint64_t* pt_ready = &ctl.bar[6];
   volatile int* abort_flag = &ctl.abort_flag;
 
   const int tid = threadIdx.x, warp = tid >> 5;
+  const bool is_row = warp < 4;
   const int rep = a.hq / a.hkv;
   const int g = blockIdx.y / rep;
   const int hsub = blockIdx.y - g * rep;
   const int h = g * rep + hsub;
   const int c0 = blockIdx.x * 128;
   const int key = c0 + tid;
-  const bool key_ok = key < a.Tk;
+  const bool key_ok = is_row && key < a.Tk;
   const int D = a.D;
   const int nbox = (D + 63) / 64;
 
-  int4 ki = make_int4(0, 0, 0, 0);
+  int4 ki = make_int4(0, 0, 0x7fffffff, 0);  // (q_lo, q_hi, first causal viewer, flag | first viewer << 1)
   if (key_ok) ki = a.ktab[key];
+  const int kflag = ki.w & 1;
   if (tid == 0) {
     for (int i = 0; i < 5; ++i) mbar_init(&ctl.bar[i], 1);
+    mbar_init(sp_free, 128);
+    mbar_init(pt_ready, 128);
     ctl.abort_flag = 0;
     ctl.kmin = 0x7fffffff;
     ctl.kmax = 0;
@@ -529,172 +630,187 @@ attn_dkdv_kernel(const __grid_constant__ AttnArgs a, int* __restrict__ status) {
   __syncthreads();
   tc_fence_after();
   if (key_ok) {
-    atomicMin(&ctl.kmin, ki.x);
+    atomicMin(&ctl.kmin, ki.w >> 1);  // first query row that can see this key
     atomicMax(&ctl.kmax, ki.y);
   }
   __syncthreads();
   const uint32_t tmem = ctl.tmem_slot;
   const uint32_t tS = tmem, tDP = tmem + 64, tDV = tmem + 128, tDK = tmem + 256;
-  int qmin = ctl.kmin;
+  const int qmin = ctl.kmin;
   const int qmax = ctl.kmax;
-  if (a.causal_self && qmin < c0) qmin = c0;  // query r sees key k only if r >= k
   const int nblk = (qmax > qmin) ? (qmax - qmin + 63) / 64 : 0;
-  const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-  const uint32_t qd_bytes = static_cast<uint32_t>(nbox) * 8192u * 2u;
-
-  auto load_qd = [&](int i) {
-    const int st = i & 1;
-    uint8_t* q = sQD + st * 32768;
-    uint8_t* d = q + 16384;
-    mbar_arrive_expect_tx(&qd_full[st], qd_bytes);
-    for (int b = 0; b < nbox; ++b) {
-      tma_load_2d(q + b * 8192, &a.tmQ, &qd_full[st], h * D + b * 64, qmin + i * 64);
-      tma_load_2d(d + b * 8192, &a.tmDO, &qd_full[st], h * D + b * 64, qmin + i * 64);
-    }
-  };
-  if (tid == 0 && nblk > 0) {
-    mbar_arrive_expect_tx(kv_full, static_cast<uint32_t>(nbox) * 16384u * 2u);
-    for (int b = 0; b < nbox; ++b) {
-      tma_load_2d(sK + b * 16384, &a.tmK, kv_full, g * D + b * 64, c0);
-      tma_load_2d(sV + b * 16384, &a.tmV, kv_full, g * D + b * 64, c0);
-    }
-    load_qd(0);
-    if (nblk > 1) load_qd(1);
-  }
   const float scale_log2 = a.scale * LOG2E;
-  const uint32_t idesc_s = make_idesc_bf16(128, 64, false, false);
-  const uint32_t idesc_acc = make_idesc_bf16(128, D, false, true);
   bool ok = nblk > 0;
-  if (ok) ok = mbar_wait(kv_full, 0, abort_flag);
 
-  for (int i = 0; i < nblk; ++i) {
-    const int st = i & 1;
-    uint8_t* q = sQD + st * 32768;
-    uint8_t* d = q + 16384;
-    if (ok) ok = mbar_wait(&qd_full[st], (i >> 1) & 1, abort_flag);
-    if (tid < 64) {
-      const int qr = qmin + i * 64 + tid;
-      QCol qc;
-      qc.qi = make_int4(0, 0, -1, 0);
-      qc.lse2 = 0.f;
-      qc.delta = 0.f;
-      if (qr < a.Tq) {
-        qc.qi = a.qtab[qr];
-        qc.lse2 = a.lse[static_cast<long>(h) * a.Tq + qr] * LOG2E;
-        qc.delta = a.delta[static_cast<long>(h) * a.Tq + qr];
-      }
-      s_q[tid] = qc;
-    }
-    if (tid == 0 && ok) {
-      tc_fence_after();
-      const uint32_t ka = smem_u32(sK), va = smem_u32(sV), qa = smem_u32(q), da_ = smem_u32(d);
-      for (int k = 0; k < D / 16; ++k) {
-        const uint32_t ao = (k >> 2) * 16384 + (k & 3) * 32, bo = (k >> 2) * 8192 + (k & 3) * 32;
-        tc_mma_bf16(tS, make_smem_desc_sw128(ka + ao, 16, 1024), make_smem_desc_sw128(qa + bo, 16, 1024), idesc_s, k != 0);
-      }
-      for (int k = 0; k < D / 16; ++k) {
-        const uint32_t ao = (k >> 2) * 16384 + (k & 3) * 32, bo = (k >> 2) * 8192 + (k & 3) * 32;
-        tc_mma_bf16(tDP, make_smem_desc_sw128(va + ao, 16, 1024), make_smem_desc_sw128(da_ + bo, 16, 1024), idesc_s, k != 0);
-      }
-      tc_commit(s_bar);
-    }
-    __syncthreads();  // s_q visible
-    if (ok) ok = mbar_wait(s_bar, i & 1, abort_flag);
-    tc_fence_after();
-    uint32_t pp[32], pd[32];
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      uint32_t rs[32], rp[32];
-      tmem_ld_32x32(tS + lane_off + half * 32, rs);
-      tmem_ld_32x32(tDP + lane_off + half * 32, rp);
-      tmem_ld_wait();
-#pragma unroll
-      for (int c = 0; c < 32; c += 2) {
-        float pv[2], dsv[2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const QCol& qc = s_q[half * 32 + c + e];
-          const bool al = key_ok && key_allowed(key, qc.qi, ki.z);
-          const float p = al ? exp2f(__uint_as_float(rs[c + e]) * scale_log2 - qc.lse2) : 0.f;
-          pv[e] = p;
-          dsv[e] = p * (__uint_as_float(rp[c + e]) - qc.delta) * a.scale;
+  if (!is_row) {
+    if (tid == 128 && nblk > 0) {
+      const uint32_t qd_bytes = static_cast<uint32_t>(nbox) * 8192u * 2u;
+      const uint32_t idesc_s = make_idesc_bf16(128, 64, false, false);
+      const uint32_t idesc_acc = make_idesc_bf16(128, D, false, true);
+      auto load_qd = [&](int i) {
+        const int st = i & 1;
+        uint8_t* q = sQD + st * 32768;
+        uint8_t* d = q + 16384;
+        mbar_arrive_expect_tx(&qd_full[st], qd_bytes);
+        for (int b = 0; b < nbox; ++b) {
+          tma_load_2d(q + b * 8192, &a.tmQ, &qd_full[st], h * D + b * 64, qmin + i * 64);
+          tma_load_2d(d + b * 8192, &a.tmDO, &qd_full[st], h * D + b * 64, qmin + i * 64);
         }
-        pp[(half * 32 + c) >> 1] = pack_bf16x2(pv[0], pv[1]);
-        pd[(half * 32 + c) >> 1] = pack_bf16x2(dsv[0], dsv[1]);
+      };
+      mbar_arrive_expect_tx(kv_full, static_cast<uint32_t>(nbox) * 16384u * 2u);
+      for (int b = 0; b < nbox; ++b) {
+        tma_load_2d(sK + b * 16384, &a.tmK, kv_full, g * D + b * 64, c0);
+        tma_load_2d(sV + b * 16384, &a.tmV, kv_full, g * D + b * 64, c0);
+      }
+      load_qd(0);
+      if (nblk > 1) load_qd(1);
+      ok = mbar_wait(kv_full, 0, abort_flag);
+      const uint32_t ka = smem_u32(sK), va = smem_u32(sV), pa = smem_u32(sPT), sa = smem_u32(sDST);
+      for (int i = 0; i < nblk && ok; ++i) {
+        const int st = i & 1;
+        const uint32_t qa = smem_u32(sQD + st * 32768), da_ = qa + 16384;
+        ok = mbar_wait(&qd_full[st], (i >> 1) & 1, abort_flag);
+        if (ok && i > 0) ok = mbar_wait(sp_free, (i - 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t ao = (k >> 2) * 16384 + (k & 3) * 32, bo = (k >> 2) * 8192 + (k & 3) * 32;
+          tc_mma_bf16(tS, make_smem_desc_sw128(ka + ao, 16, 1024), make_smem_desc_sw128(qa + bo, 16, 1024), idesc_s, k != 0);
+        }
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t ao = (k >> 2) * 16384 + (k & 3) * 32, bo = (k >> 2) * 8192 + (k & 3) * 32;
+          tc_mma_bf16(tDP, make_smem_desc_sw128(va + ao, 16, 1024), make_smem_desc_sw128(da_ + bo, 16, 1024), idesc_s, k != 0);
+        }
+        tc_commit(s_bar);
+        if (i > 0 && i + 1 < nblk) {  // stage (i+1)&1 was read by the accumulating MMAs of block i-1
+          ok = mbar_wait(acc_bar, (i - 1) & 1, abort_flag);
+          if (!ok) break;
+          load_qd(i + 1);
+        }
+        ok = mbar_wait(pt_ready, i & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma_bf16(tDV, make_smem_desc_sw128(pa + k * 32, 16, 1024), make_smem_desc_sw128(da_ + k * 2048, 8192, 1024),
+                      idesc_acc, (i | k) != 0);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma_bf16(tDK, make_smem_desc_sw128(sa + k * 32, 16, 1024), make_smem_desc_sw128(qa + k * 2048, 8192, 1024),
+                      idesc_acc, (i | k) != 0);
+        tc_commit(acc_bar);
       }
     }
-    // the accumulating MMAs of the previous block read sPT / sDST and stage st^1
-    if (i > 0) {
-      if (ok) ok = mbar_wait(acc_bar, (i - 1) & 1, abort_flag);
-      if (tid == 0 && ok && i + 1 < nblk) load_qd(i + 1);
-    }
-#pragma unroll
-    for (int c16 = 0; c16 < 8; ++c16) {
-      *reinterpret_cast<uint4*>(sPT + sw128_offset(tid, c16)) =
-          make_uint4(pp[4 * c16], pp[4 * c16 + 1], pp[4 * c16 + 2], pp[4 * c16 + 3]);
-      *reinterpret_cast<uint4*>(sDST + sw128_offset(tid, c16)) =
-          make_uint4(pd[4 * c16], pd[4 * c16 + 1], pd[4 * c16 + 2], pd[4 * c16 + 3]);
-    }
-    fence_proxy_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0 && ok) {
+  } else {
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    for (int i = 0; i < nblk; ++i) {
+      const int st = i & 1;
+      const int qbase = qmin + i * 64;
+      if (tid < 64) {
+        const int qr = qbase + tid;
+        float2 ld = make_float2(0.f, 0.f);
+        int fq = 0;
+        if (qr < a.Tq) {
+          ld.x = a.lse[static_cast<long>(h) * a.Tq + qr] * LOG2E;
+          ld.y = a.delta[static_cast<long>(h) * a.Tq + qr] * a.scale;
+          fq = a.has_bidir ? a.qtab[qr].w : 0;
+        }
+        s_ld[st][tid] = ld;
+        s_qflag[st][tid] = fq;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // per-query values visible to the 4 row warps
+      uint64_t qm = bits_between(ki.z - qbase, ki.y - 1 - qbase);
+      if (a.has_bidir) {
+        const uint64_t qfm = flags_to_mask(s_qflag[st]);
+        if (kflag) qm |= qfm & bits_between(ki.x - qbase, ki.y - 1 - qbase);
+      }
+      if (!key_ok) qm = 0ull;
+      const bool fast = __all_sync(0xffffffffu, qm == ~0ull);
+      if (ok) ok = mbar_wait(s_bar, i & 1, abort_flag);
       tc_fence_after();
-      const uint32_t pa = smem_u32(sPT), sa = smem_u32(sDST), qa = smem_u32(q), da_ = smem_u32(d);
+      uint32_t pp[32], pd[32];
 #pragma unroll
-      for (int k = 0; k < 4; ++k)
-        tc_mma_bf16(tDV, make_smem_desc_sw128(pa + k * 32, 16, 1024), make_smem_desc_sw128(da_ + k * 2048, 8192, 1024),
-                    idesc_acc, (i | k) != 0);
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-        tc_mma_bf16(tDK, make_smem_desc_sw128(sa + k * 32, 16, 1024), make_smem_desc_sw128(qa + k * 2048, 8192, 1024),
-                    idesc_acc, (i | k) != 0);
-      tc_commit(acc_bar);
-    }
-  }
-  if (ok && nblk > 0) ok = mbar_wait(acc_bar, (nblk - 1) & 1, abort_flag);
-  tc_fence_after();
-  {
-    const bool have = __all_sync(0xffffffffu, ok) && nblk > 0;
-    const long W = static_cast<long>(a.hkv) * D;
-    __nv_bfloat16* krow = a.out + static_cast<long>(key) * a.ld_out + g * D;
-    __nv_bfloat16* vrow = a.out2 + static_cast<long>(key) * a.ld_out2 + g * D;
-    float* pkrow = a.part_k + (static_cast<long>(hsub) * a.Tk + key) * W + g * D;
-    float* pvrow = a.part_v + (static_cast<long>(hsub) * a.Tk + key) * W + g * D;
-    for (int c = 0; c < D; c += 16) {
-      uint32_t rk[16], rv[16];
-      if (have) {
-        tmem_ld_32x16(tDK + lane_off + c, rk);
-        tmem_ld_32x16(tDV + lane_off + c, rv);
+      for (int half = 0; half < 2; ++half) {
+        uint32_t rs[32], rp[32];
+        tmem_ld_32x32(tS + lane_off + half * 32, rs);
+        tmem_ld_32x32(tDP + lane_off + half * 32, rp);
         tmem_ld_wait();
-      } else {
+        const uint32_t qmh = static_cast<uint32_t>(qm >> (32 * half));
 #pragma unroll
-        for (int e = 0; e < 16; ++e) rk[e] = rv[e] = 0u;
-      }
-      if (!key_ok) continue;
-      if (rep == 1) {
-#pragma unroll
-        for (int q2 = 0; q2 < 2; ++q2) {
-          reinterpret_cast<uint4*>(krow + c)[q2] = make_uint4(
-              pack_bf16x2(__uint_as_float(rk[8 * q2 + 0]), __uint_as_float(rk[8 * q2 + 1])),
-              pack_bf16x2(__uint_as_float(rk[8 * q2 + 2]), __uint_as_float(rk[8 * q2 + 3])),
-              pack_bf16x2(__uint_as_float(rk[8 * q2 + 4]), __uint_as_float(rk[8 * q2 + 5])),
-              pack_bf16x2(__uint_as_float(rk[8 * q2 + 6]), __uint_as_float(rk[8 * q2 + 7])));
-          reinterpret_cast<uint4*>(vrow + c)[q2] = make_uint4(
-              pack_bf16x2(__uint_as_float(rv[8 * q2 + 0]), __uint_as_float(rv[8 * q2 + 1])),
-              pack_bf16x2(__uint_as_float(rv[8 * q2 + 2]), __uint_as_float(rv[8 * q2 + 3])),
-              pack_bf16x2(__uint_as_float(rv[8 * q2 + 4]), __uint_as_float(rv[8 * q2 + 5])),
-              pack_bf16x2(__uint_as_float(rv[8 * q2 + 6]), __uint_as_float(rv[8 * q2 + 7])));
+        for (int c = 0; c < 32; c += 2) {
+          const float4 l2 = *reinterpret_cast<const float4*>(&s_ld[st][half * 32 + c]);
+          float p0 = ex2_approx(fmaf(__uint_as_float(rs[c]), scale_log2, -l2.x));
+          float p1 = ex2_approx(fmaf(__uint_as_float(rs[c + 1]), scale_log2, -l2.z));
+          if (!fast) {
+            p0 = (qmh & (1u << c)) ? p0 : 0.f;
+            p1 = (qmh & (2u << c)) ? p1 : 0.f;
+          }
+          pp[(half * 32 + c) >> 1] = pack_bf16x2(p0, p1);
+          pd[(half * 32 + c) >> 1] = pack_bf16x2(p0 * fmaf(__uint_as_float(rp[c]), a.scale, -l2.y),
+                                                 p1 * fmaf(__uint_as_float(rp[c + 1]), a.scale, -l2.w));
         }
-      } else {
+      }
+      tc_fence_before();
+      mbar_arrive(sp_free);  // S^T / dP^T are in registers: the next block's scores may overwrite them
+      // the accumulating MMAs of the previous block read sPT / sDST
+      if (i > 0) {
+        if (ok) ok = mbar_wait(acc_bar, (i - 1) & 1, abort_flag);
+      }
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          reinterpret_cast<float4*>(pkrow + c)[q4] =
-              make_float4(__uint_as_float(rk[4 * q4]), __uint_as_float(rk[4 * q4 + 1]), __uint_as_float(rk[4 * q4 + 2]),
-                          __uint_as_float(rk[4 * q4 + 3]));
-          reinterpret_cast<float4*>(pvrow + c)[q4] =
-              make_float4(__uint_as_float(rv[4 * q4]), __uint_as_float(rv[4 * q4 + 1]), __uint_as_float(rv[4 * q4 + 2]),
-                          __uint_as_float(rv[4 * q4 + 3]));
+      for (int c16 = 0; c16 < 8; ++c16) {
+        *reinterpret_cast<uint4*>(sPT + sw128_offset(tid, c16)) =
+            make_uint4(pp[4 * c16], pp[4 * c16 + 1], pp[4 * c16 + 2], pp[4 * c16 + 3]);
+        *reinterpret_cast<uint4*>(sDST + sw128_offset(tid, c16)) =
+            make_uint4(pd[4 * c16], pd[4 * c16 + 1], pd[4 * c16 + 2], pd[4 * c16 + 3]);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(pt_ready);
+    }
+    if (ok && nblk > 0) ok = mbar_wait(acc_bar, (nblk - 1) & 1, abort_flag);
+    tc_fence_after();
+    {
+      const bool have = __all_sync(0xffffffffu, ok) && nblk > 0;
+      const long W = static_cast<long>(a.hkv) * D;
+      __nv_bfloat16* krow = a.out + static_cast<long>(key) * a.ld_out + g * D;
+      __nv_bfloat16* vrow = a.out2 + static_cast<long>(key) * a.ld_out2 + g * D;
+      float* pkrow = a.part_k + (static_cast<long>(hsub) * a.Tk + key) * W + g * D;
+      float* pvrow = a.part_v + (static_cast<long>(hsub) * a.Tk + key) * W + g * D;
+      for (int c = 0; c < D; c += 16) {
+        uint32_t rk[16], rv[16];
+        if (have) {
+          tmem_ld_32x16(tDK + lane_off + c, rk);
+          tmem_ld_32x16(tDV + lane_off + c, rv);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) rk[e] = rv[e] = 0u;
+        }
+        if (!key_ok) continue;
+        if (rep == 1) {
+#pragma unroll
+          for (int q2 = 0; q2 < 2; ++q2) {
+            reinterpret_cast<uint4*>(krow + c)[q2] = make_uint4(
+                pack_bf16x2(__uint_as_float(rk[8 * q2 + 0]), __uint_as_float(rk[8 * q2 + 1])),
+                pack_bf16x2(__uint_as_float(rk[8 * q2 + 2]), __uint_as_float(rk[8 * q2 + 3])),
+                pack_bf16x2(__uint_as_float(rk[8 * q2 + 4]), __uint_as_float(rk[8 * q2 + 5])),
+                pack_bf16x2(__uint_as_float(rk[8 * q2 + 6]), __uint_as_float(rk[8 * q2 + 7])));
+            reinterpret_cast<uint4*>(vrow + c)[q2] = make_uint4(
+                pack_bf16x2(__uint_as_float(rv[8 * q2 + 0]), __uint_as_float(rv[8 * q2 + 1])),
+                pack_bf16x2(__uint_as_float(rv[8 * q2 + 2]), __uint_as_float(rv[8 * q2 + 3])),
+                pack_bf16x2(__uint_as_float(rv[8 * q2 + 4]), __uint_as_float(rv[8 * q2 + 5])),
+                pack_bf16x2(__uint_as_float(rv[8 * q2 + 6]), __uint_as_float(rv[8 * q2 + 7])));
+          }
+        } else {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            reinterpret_cast<float4*>(pkrow + c)[q4] =
+                make_float4(__uint_as_float(rk[4 * q4]), __uint_as_float(rk[4 * q4 + 1]), __uint_as_float(rk[4 * q4 + 2]),
+                            __uint_as_float(rk[4 * q4 + 3]));
+            reinterpret_cast<float4*>(pvrow + c)[q4] =
+                make_float4(__uint_as_float(rv[4 * q4]), __uint_as_float(rv[4 * q4 + 1]), __uint_as_float(rv[4 * q4 + 2]),
+                            __uint_as_float(rv[4 * q4 + 3]));
+          }
         }
       }
     }
@@ -768,6 +884,12 @@ bool shape_ok(const AttnShape& s) {
 
 }  // namespace
 
+#ifdef WX_ATTN_TRACE
+int attn_trace_read(long long* dst) {
+  return static_cast<int>(cudaMemcpyFromSymbol(dst, g_attn_trace, sizeof(long long) * 256));
+}
+#endif
+
 int attn_fwd(const AttnShape& s, const void* q, const void* k, const void* v, const void* qtab, const void* ktab,
              void* out, long ld_out, float* lse, cudaStream_t stream, int* status) {
   if (!shape_ok(s)) return -1;
@@ -791,7 +913,7 @@ int attn_fwd(const AttnShape& s, const void* q, const void* k, const void* v, co
     attr = true;
   }
   dim3 grid((s.Tq + 127) / 128, s.hq);
-  attn_fwd_kernel<<<grid, AT_THREADS, FWD_SMEM, stream>>>(a, status);
+  attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM, stream>>>(a, status);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -832,7 +954,7 @@ int attn_bwd(const AttnShape& s, const void* q, const void* k, const void* v, co
     if (e != cudaSuccess) return static_cast<int>(e);
     attr = true;
   }
-  attn_dq_kernel<<<dim3((s.Tq + 127) / 128, s.hq), AT_THREADS, DQ_SMEM, stream>>>(a, status);
+  attn_dq_kernel<<<dim3((s.Tq + 127) / 128, s.hq), DQ_THREADS, DQ_SMEM, stream>>>(a, status);
   // ---- dK / dV
   if (!tmap2d(&a.tmQ, q, static_cast<uint64_t>(s.hq) * s.D, s.Tq, s.ld_q, 64)) return -2;
   if (!tmap2d(&a.tmDO, dout, static_cast<uint64_t>(s.hq) * s.D, s.Tq, ld_do, 64)) return -2;
@@ -845,7 +967,7 @@ int attn_bwd(const AttnShape& s, const void* q, const void* k, const void* v, co
   a.part_k = part_k;
   a.part_v = part_v;
   if (rep > 1 && (part_k == nullptr || part_v == nullptr)) return -3;
-  attn_dkdv_kernel<<<dim3((s.Tk + 127) / 128, s.hq), AT_THREADS, DKDV_SMEM, stream>>>(a, status);
+  attn_dkdv_kernel<<<dim3((s.Tk + 127) / 128, s.hq), DKDV_THREADS, DKDV_SMEM, stream>>>(a, status);
   if (rep > 1) {
     const int W = s.hkv * s.D;
     const long total = static_cast<long>(s.Tk) * (W / 4);

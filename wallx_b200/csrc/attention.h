@@ -13,7 +13,9 @@ struct AttnShape {
   int causal_self;  // self-attention, causal, no bidirectional block: lets dK/dV skip query blocks
 };
 
-// qtab: int32 [Tq, 4] = (k_lo, k_hi, k_lim, flag); ktab: int32 [Tk, 4] = (q_lo, q_hi, flag, 0).
+// qtab: int32 [Tq, 4] = (k_lo, k_hi, k_lim, flag); ktab: int32 [Tk, 4] = (q_lo, q_hi, q_causal, flag | q_first << 1):
+// q_causal = first query row that sees the key under the causal rule (q_lo when not causal),
+// q_first = first query row that sees it at all (lets dK/dV skip earlier query blocks).
 // lse: fp32 [hq, Tq] (natural log). `status` is set non-zero when a bounded wait ran out.
 int attn_fwd(const AttnShape& s, const void* q, const void* k, const void* v, const void* qtab, const void* ktab,
              void* out, long ld_out, float* lse, cudaStream_t stream, int* status);

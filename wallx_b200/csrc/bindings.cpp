@@ -176,7 +176,19 @@ void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, 
 
 void register_kernel_bindings(pybind11::module_& m);
 
+#ifdef WX_ATTN_TRACE
+namespace wx { int attn_trace_read(long long* dst); }
+at::Tensor attn_trace() {
+  at::Tensor t = at::zeros({16, 16}, at::kLong);
+  wx::attn_trace_read(reinterpret_cast<long long*>(t.data_ptr<int64_t>()));
+  return t;
+}
+#endif
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+#ifdef WX_ATTN_TRACE
+  m.def("attn_trace", &attn_trace);
+#endif
   m.def("gemm_grouped", &gemm_grouped, "tcgen05 GEMM: one or two problems in one launch");
   m.def("read_status", &read_status, "read and clear the device-side wait-timeout status");
   m.def("attn_fwd", &attn_fwd);

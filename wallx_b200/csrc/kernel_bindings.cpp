@@ -212,6 +212,49 @@ void adamw_step_f32g(at::Tensor& p16, at::Tensor& p32, at::Tensor& m, at::Tensor
               "adamw_step_f32g");
 }
 
+std::tuple<at::Tensor, at::Tensor> rope_index(const at::Tensor& ids, const OptT& mask, const at::Tensor& img_grid,
+                                              const at::Tensor& vid_grid, const at::Tensor& sec_per_grid, int64_t merge,
+                                              int64_t image_id, int64_t video_id, int64_t vstart_id, double tps) {
+  TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.dim() == 2 && ids.is_contiguous(), "rope_index: ids");
+  TORCH_CHECK(img_grid.scalar_type() == at::kInt && vid_grid.scalar_type() == at::kInt && img_grid.is_contiguous() &&
+              vid_grid.is_contiguous() && sec_per_grid.scalar_type() == at::kFloat, "rope_index: grids");
+  c10::cuda::CUDAGuard g(ids.device());
+  const int B = ids.size(0), S = ids.size(1);
+  at::Tensor pos = at::empty({3, B, S}, ids.options());
+  at::Tensor deltas = at::empty({B, 1}, ids.options());
+  at::Tensor status = at::zeros({1}, ids.options().dtype(at::kInt));
+  WX_CHECK_RC(wx::rope_index(reinterpret_cast<const long*>(ids.data_ptr<int64_t>()), opt_int(mask), img_grid.data_ptr<int>(),
+                             img_grid.size(0), vid_grid.data_ptr<int>(), vid_grid.size(0),
+                             sec_per_grid.numel() ? sec_per_grid.data_ptr<float>() : nullptr, B, S, merge, image_id,
+                             video_id, vstart_id, static_cast<float>(tps), reinterpret_cast<long*>(pos.data_ptr<int64_t>()),
+                             reinterpret_cast<long*>(deltas.data_ptr<int64_t>()), status.data_ptr<int>(), cur_stream()),
+              "rope_index");
+  return {pos, deltas};
+}
+
+at::Tensor vit_rot_pos(const at::Tensor& inv_freq, const at::Tensor& grid, int64_t merge, int64_t total) {
+  TORCH_CHECK(inv_freq.is_cuda() && inv_freq.scalar_type() == at::kFloat && grid.is_cuda() && grid.scalar_type() == at::kInt);
+  c10::cuda::CUDAGuard g(grid.device());
+  const int F = inv_freq.numel();
+  at::Tensor out = at::empty({total, 2 * F}, inv_freq.options());
+  WX_CHECK_RC(wx::vit_rot_pos(inv_freq.data_ptr<float>(), F, grid.data_ptr<int>(), grid.size(0), merge,
+                              out.data_ptr<float>(), total, cur_stream()),
+              "vit_rot_pos");
+  return out;
+}
+
+std::tuple<at::Tensor, at::Tensor> vit_window_index(const at::Tensor& grid, int64_t vw, int64_t merge, int64_t n_merged,
+                                                    int64_t n_windows) {
+  TORCH_CHECK(grid.is_cuda() && grid.scalar_type() == at::kInt && grid.is_contiguous());
+  c10::cuda::CUDAGuard g(grid.device());
+  at::Tensor idx = at::empty({n_merged}, grid.options().dtype(at::kLong));
+  at::Tensor cu = at::empty({n_windows + 1}, grid.options());
+  WX_CHECK_RC(wx::vit_window_index(grid.data_ptr<int>(), grid.size(0), vw, merge, reinterpret_cast<long*>(idx.data_ptr<int64_t>()),
+                                   cu.data_ptr<int>(), cur_stream()),
+              "vit_window_index");
+  return {idx, cu};
+}
+
 }  // namespace
 
 void register_kernel_bindings(pybind11::module_& m) {
@@ -228,6 +271,9 @@ void register_kernel_bindings(pybind11::module_& m) {
   m.def("sumsq_bf16", &sumsq_bf16);
   m.def("adamw_step", &adamw_step);
   m.def("adamw_step_f32g", &adamw_step_f32g);
+  m.def("rope_index", &rope_index);
+  m.def("vit_rot_pos", &vit_rot_pos);
+  m.def("vit_window_index", &vit_window_index);
   m.def("symm_barrier", &symm_barrier);
   m.def("rs_reduce", &rs_reduce);
   m.def("ag_push", &ag_push);

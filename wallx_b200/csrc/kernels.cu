@@ -185,31 +185,33 @@ __global__ void reduce_partials_kernel(const float* __restrict__ partial, __nv_b
 }
 
 // ------------------------------------------------------------------------------ SwiGLU backward
-// gu is [R, ld_gu] with 32-column blocks [16 gate | 16 up]; dh is [R, ld_dh]; one thread per block.
-__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dh, const __nv_bfloat16* __restrict__ gu,
-                                  __nv_bfloat16* __restrict__ dgu, int R, int nblk, long ld_dh, long ld_gu) {
-  const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= static_cast<long>(R) * nblk) return;
-  const int r = static_cast<int>(idx / nblk);
-  const int b = static_cast<int>(idx - static_cast<long>(r) * nblk);
-  const BF8* gp = reinterpret_cast<const BF8*>(gu + r * ld_gu + b * 32);
-  const BF8* dp = reinterpret_cast<const BF8*>(dh + r * ld_dh + b * 16);
-  BF8* op = reinterpret_cast<BF8*>(dgu + r * ld_gu + b * 32);
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
+// gu is [R, ld_gu] with 32-column blocks [16 gate | 16 up]; dh is [R, ld_dh]. One thread handles 8
+// gate and the matching 8 up channels (three 16-byte loads, two 16-byte stores); neighbouring
+// threads take neighbouring 16-byte chunks, so every 32-byte sector is used whole.
+__global__ void __launch_bounds__(256)
+swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dh, const __nv_bfloat16* __restrict__ gu,
+                  __nv_bfloat16* __restrict__ dgu, int R, int nblk, long ld_dh, long ld_gu) {
+  const long per_row = static_cast<long>(nblk) * 2;
+  const long total = static_cast<long>(R) * per_row;
+  for (long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(idx / per_row);
+    const int rem = static_cast<int>(idx - static_cast<long>(r) * per_row);
+    const int b = rem >> 1, h = rem & 1;
+    const __nv_bfloat16* grow = gu + r * ld_gu + b * 32 + h * 8;
     float g[8], u[8], d[8], dg[8], du[8];
-    unpack8(gp[h], g);
-    unpack8(gp[2 + h], u);
-    unpack8(dp[h], d);
+    unpack8(*reinterpret_cast<const BF8*>(grow), g);
+    unpack8(*reinterpret_cast<const BF8*>(grow + 16), u);
+    unpack8(*reinterpret_cast<const BF8*>(dh + r * ld_dh + b * 16 + h * 8), d);
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       const float sg = 1.f / (1.f + __expf(-g[e]));
-      const float silu = g[e] * sg;
-      du[e] = d[e] * silu;
+      du[e] = d[e] * g[e] * sg;
       dg[e] = d[e] * u[e] * (sg * (1.f + g[e] * (1.f - sg)));
     }
-    op[h] = pack8(dg);
-    op[2 + h] = pack8(du);
+    __nv_bfloat16* orow = dgu + r * ld_gu + b * 32 + h * 8;
+    *reinterpret_cast<BF8*>(orow) = pack8(dg);
+    *reinterpret_cast<BF8*>(orow + 16) = pack8(du);
   }
 }
 
@@ -563,9 +565,9 @@ int swiglu_bwd(const void* dh, const void* gu, void* dgu, int R, int width_gu, l
                cudaStream_t s) {
   if (width_gu % 32 != 0 || ld_dh % 8 != 0 || ld_gu % 8 != 0) return -1;
   const int nblk = width_gu / 32;
-  const long total = static_cast<long>(R) * nblk;
+  const long total = static_cast<long>(R) * nblk * 2;
   if (total == 0) return 0;
-  swiglu_bwd_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(
+  swiglu_bwd_kernel<<<blocks_for(total, 256, 148 * 32), 256, 0, s>>>(
       reinterpret_cast<const __nv_bfloat16*>(dh), reinterpret_cast<const __nv_bfloat16*>(gu),
       reinterpret_cast<__nv_bfloat16*>(dgu), R, nblk, ld_dh, ld_gu);
   return static_cast<int>(cudaGetLastError());

@@ -27,4 +27,11 @@ int sumsq_bf16(const void* g, long n, float* out, cudaStream_t s);
 int adamw_step(void* p16, float* p32, float* m, float* v, const void* g, long n, const float* hyper,
                const float* norm_sq, cudaStream_t s);
 
+// index generation (index.cu)
+int rope_index(const long* ids, const int* mask, const int* img_grid, int n_img, const int* vid_grid, int n_vid,
+               const float* sec_per_grid, int B, int S, int merge, long image_id, long video_id, long vstart_id,
+               float tokens_per_second, long* pos, long* deltas, int* status, cudaStream_t s);
+int vit_rot_pos(const float* inv_freq, int F, const int* grid, int G, int merge, float* out, long N, cudaStream_t s);
+int vit_window_index(const int* grid, int G, int vw, int merge, long* window_index, int* cu_seqlens, cudaStream_t s);
+
 }  // namespace wx

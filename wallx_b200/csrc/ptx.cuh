@@ -74,15 +74,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait. `abort_flag` lives in shared memory and is shared by all roles of the CTA: the
 // first wait that runs out sets it, every other wait sees it within ~1k polls and returns false.
+// The limit is counted on the SM cycle counter (reading %globaltimer costs far more than a poll).
+#ifndef WX_WAIT_LIMIT_CYCLES
+#define WX_WAIT_LIMIT_CYCLES 4000000000ll  // about 2 s at 1.9 GHz
+#endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  long long t0 = 0;
   uint32_t it = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (((++it) & 255u) == 0u) {
+    if (((++it) & 1023u) == 0u) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > WX_WAIT_LIMIT_NS) {
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > WX_WAIT_LIMIT_CYCLES) {
         *abort_flag = 1;
         return false;
       }

@@ -24,6 +24,7 @@ SOURCES = [
     "kernels.cu",
     "attention.cu",
     "comm.cu",
+    "index.cu",
 ]
 
 NVCC_FLAGS = [

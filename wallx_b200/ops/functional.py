@@ -424,6 +424,9 @@ class AttnMeta:
             k_lim = torch.full((nq,), -1, dtype=torch.int32)  # last visible key (absolute row) under causality
             q_lo = torch.zeros(nk, dtype=torch.int32)
             q_hi = torch.zeros(nk, dtype=torch.int32)
+            q_first = torch.zeros(nk, dtype=torch.int32)  # first query row that sees the key (causal rule)
+            seq_of_q = torch.zeros(nq, dtype=torch.int64)
+            seq_of_k = torch.zeros(nk, dtype=torch.int64)
             for b in range(len(self.cu_q_host) - 1):
                 q0, q1 = self.cu_q_host[b], self.cu_q_host[b + 1]
                 k0, k1 = self.k_ranges[b]
@@ -433,17 +436,34 @@ class AttnMeta:
                 k_lim[q0:q1] = torch.arange(q1 - q0, dtype=torch.int32) + (k0 + off)
                 q_lo[k0:k1] = q0
                 q_hi[k0:k1] = q1
+                q_first[k0:k1] = (torch.arange(k1 - k0, dtype=torch.int32) - off).clamp_(min=0) + q0 if self.causal else q0
+                seq_of_q[q0:q1] = b
+                seq_of_k[k0:k1] = b
             if not self.causal:
                 k_lim = k_hi - 1
             # flags stay on their device (no host round trip); host-built columns are uploaded once
             qh = torch.stack([k_lo, k_hi, k_lim], dim=1).to(device, non_blocking=True)
             kh = torch.stack([q_lo, q_hi], dim=1).to(device, non_blocking=True)
+            qc = q_first.to(device, non_blocking=True)  # first viewer under the causal rule
+            qf = qc
             fq = (self.bidir_q.to(device=device, dtype=torch.int32) if self.bidir_q is not None
                   else torch.zeros(nq, dtype=torch.int32, device=device))
             fk = (self.bidir_k.to(device=device, dtype=torch.int32) if self.bidir_k is not None
                   else torch.zeros(nk, dtype=torch.int32, device=device))
+            if self.causal and self.bidir_q is not None and self.bidir_k is not None:
+                # a flagged key is also seen by every flagged query of its sequence: the first one
+                nseq = len(self.cu_q_host) - 1
+                rows = torch.arange(nq, dtype=torch.int32, device=device)
+                cand = torch.where(fq > 0, rows, torch.full_like(rows, nq))
+                first = torch.full((nseq,), nq, dtype=torch.int32, device=device)
+                first = first.scatter_reduce(0, seq_of_q.to(device), cand, reduce="amin", include_self=True)
+                per_key = first.index_select(0, seq_of_k.to(device))
+                qf = torch.where(fk > 0, torch.minimum(qc, per_key), qc)
+            else:
+                fq = torch.zeros_like(fq)
+                fk = torch.zeros_like(fk)
             qtab = torch.cat([qh, fq.reshape(-1, 1)], dim=1).contiguous()
-            ktab = torch.cat([kh, fk.reshape(-1, 1), torch.zeros_like(fk).reshape(-1, 1)], dim=1).contiguous()
+            ktab = torch.cat([kh, qc.reshape(-1, 1), (fk + 2 * qf).reshape(-1, 1)], dim=1).contiguous()
             t = (qtab, ktab)
             self._dev["tables"] = t
         return t
