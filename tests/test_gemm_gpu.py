@@ -121,3 +121,108 @@ def test_k_offset_segment_reduction():
     ref = dy[k0:k0 + K].float().t() @ x[k0:k0 + K].float()
     _check(out, ref, K)
     G.check_status()
+
+
+# --------------------------------------------------------------------------- gathered-weight mode
+# The shards of the "ranks" are separate tensors on one GPU: the puller CTAs only copy and publish
+# flags, so the whole mechanism (bulk copies, flags, rotated tile order, bounded waits) runs in one
+# kernel on one device.
+def _ag_call(x, shards, transpose_w, flags=0, rank=0, n_pullers=0, epoch_flags=None, epoch=1, out=None):
+    from wallx_b200.ops import _ext
+    from wallx_b200.ops import gemm as G
+
+    world = len(shards)
+    rpr, cols = shards[0].shape
+    rows = rpr * world
+    staging = torch.full((rows, cols), float("nan"), dtype=torch.bfloat16, device=x.device)
+    fl = epoch_flags if epoch_flags is not None else torch.zeros((rows + 255) // 256, dtype=torch.int32, device=x.device)
+    N = cols if transpose_w else rows
+    if out is None:
+        out = torch.empty(x.shape[0], N // 2 if flags & G.ACT_SWIGLU else N, dtype=torch.bfloat16, device=x.device)
+    spec = G.GemmSpec(x, staging, out, b_mn=transpose_w, flags=flags)
+    _ext.get().gemm_ag([spec.as_tuple()], [[s.data_ptr() for s in shards]], [fl], rank, [rpr], n_pullers, [epoch])
+    return out, staging, fl
+
+
+@pytest.mark.parametrize("world,rows,cols,M,rank,n_pullers", [
+    (1, 512, 256, 300, 0, 0),
+    (2, 2560, 2048, 1000, 1, 0),     # fused QKV of the 2048-wide decoder
+    (4, 1280, 1024, 4000, 2, 5),     # 320 rows per rank: shards straddle 256-row tiles
+    (8, 2048, 11008, 700, 7, 3),     # down-projection shape: 22 KB rows, 16-byte-multiple chunks
+    (2, 768, 136, 129, 0, 40),       # more pullers than chunks per tile
+])
+def test_gemm_gathered_weight_forward(world, rows, cols, M, rank, n_pullers):
+    from wallx_b200.ops import gemm as G
+
+    torch.manual_seed(0)
+    dev = torch.device("cuda")
+    w = (torch.randn(rows, cols, device=dev) * 0.05).to(torch.bfloat16)
+    shards = [w[r * (rows // world):(r + 1) * (rows // world)].clone() for r in range(world)]
+    x = torch.randn(M, cols, device=dev).to(torch.bfloat16)
+    y, staging, fl = _ag_call(x, shards, False, rank=rank, n_pullers=n_pullers)
+    torch.cuda.synchronize()
+    G.check_status()
+    assert torch.equal(staging, w)
+    assert int(fl.min()) == int(fl.max()) and int(fl.min()) > 0
+    ref = x.float() @ w.float().t()
+    torch.testing.assert_close(y.float(), ref, atol=2e-2 * ref.abs().max().item(), rtol=2e-2)
+    # second call on the same flags (epoch 2) with changed shards must see the new weights
+    shards2 = [s * 0.5 for s in shards]
+    y2, staging2, _ = _ag_call(x, shards2, False, rank=rank, n_pullers=n_pullers, epoch_flags=fl, epoch=2)
+    torch.cuda.synchronize()
+    G.check_status()
+    assert torch.equal(staging2, w * 0.5)
+    torch.testing.assert_close(y2.float(), ref * 0.5, atol=2e-2 * ref.abs().max().item(), rtol=2e-2)
+
+
+@pytest.mark.parametrize("world,rows,cols,M", [(2, 2560, 2048, 1000), (4, 1280, 1024, 515), (1, 256, 512, 128)])
+def test_gemm_gathered_weight_dgrad(world, rows, cols, M):
+    from wallx_b200.ops import gemm as G
+
+    torch.manual_seed(1)
+    dev = torch.device("cuda")
+    w = (torch.randn(rows, cols, device=dev) * 0.05).to(torch.bfloat16)
+    shards = [w[r * (rows // world):(r + 1) * (rows // world)].clone() for r in range(world)]
+    dy = torch.randn(M, rows, device=dev).to(torch.bfloat16)
+    dx, staging, _ = _ag_call(dy, shards, True)
+    torch.cuda.synchronize()
+    G.check_status()
+    assert torch.equal(staging, w)
+    ref = dy.float() @ w.float()
+    torch.testing.assert_close(dx.float(), ref, atol=2e-2 * ref.abs().max().item(), rtol=2e-2)
+
+
+def test_gemm_gathered_dual_gate_up():
+    """Two experts' interleaved gate/up weights gathered and multiplied in one launch, SwiGLU epilogue."""
+    from wallx_b200.ops import _ext
+    from wallx_b200.ops import gemm as G
+    from wallx_b200.ops import ref as R
+
+    torch.manual_seed(2)
+    dev = torch.device("cuda")
+    world, hidden = 2, 1024
+    widths = (2816, 512)  # FFN widths of the two experts
+    rows_tok = (900, 260)
+    specs, peers, flags, rprs, outs, refs = [], [], [], [], [], []
+    for e in range(2):
+        wgu = (torch.randn(2 * widths[e], hidden, device=dev) * 0.05).to(torch.bfloat16)
+        rpr = 2 * widths[e] // world
+        shards = [wgu[r * rpr:(r + 1) * rpr].clone() for r in range(world)]
+        x = torch.randn(rows_tok[e], hidden, device=dev).to(torch.bfloat16)
+        staging = torch.empty_like(wgu)
+        out = torch.empty(rows_tok[e], widths[e], dtype=torch.bfloat16, device=dev)
+        specs.append(G.GemmSpec(x, staging, out, flags=G.ACT_SWIGLU))
+        peers.append([s.data_ptr() for s in shards])
+        flags.append(torch.zeros((2 * widths[e] + 255) // 256, dtype=torch.int32, device=dev))
+        rprs.append(rpr)
+        outs.append(out)
+        refs.append((x, wgu, shards))
+    _ext.get().gemm_ag([s.as_tuple() for s in specs], peers, flags, 1, rprs, 0, [1, 1])
+    torch.cuda.synchronize()
+    G.check_status()
+    for e in range(2):
+        x, wgu, _ = refs[e]
+        z = (x.float() @ wgu.float().t()).to(torch.bfloat16).float().view(x.shape[0], -1, 2, 16)
+        ref = torch.nn.functional.silu(z[:, :, 0]) * z[:, :, 1]
+        ref = ref.reshape(x.shape[0], widths[e])
+        torch.testing.assert_close(outs[e].float(), ref, atol=2e-2 * ref.abs().max().item(), rtol=3e-2)

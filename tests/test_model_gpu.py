@@ -60,3 +60,40 @@ def test_tiny_model_gpu_matches_cpu(mode):
         assert cos > 0.95, (name, cos.item())
         checked += 1
     assert checked > 10
+
+
+def test_engine_step_with_gradient_sinks_matches_cpu():
+    """Two optimizer steps through the training engine (flat buffers, weight gradients accumulated
+    by the GEMM epilogue, fused AdamW) against the same engine on the CPU oracle path."""
+    from wallx_b200.data.collator import to_device
+    from wallx_b200.ops import gemm as G
+    from wallx_b200.parallel.engine import TrainEngine
+
+    cfg, model, batch = _build("flow")
+    model_g = copy.deepcopy(model).to(torch.bfloat16).cuda()
+    model_c = copy.deepcopy(model_g).float().cpu()
+    gen = torch.Generator().manual_seed(2)
+    extra = {"flow_noise": torch.randn(batch["action_chunk"].shape, generator=gen),
+             "flow_time": torch.rand(batch["action_chunk"].shape[0], generator=gen) * 0.9}
+    eng_g = TrainEngine(model_g, lr=1e-3, grad_accum=2)
+    eng_c = TrainEngine(model_c, lr=1e-3, grad_accum=2)
+    bg = to_device(batch, "cuda", torch.bfloat16)
+    eg = {k: v.cuda() for k, v in extra.items()}
+    for _ in range(2):
+        for _mb in range(2):
+            eng_c.backward(model_c(mode="train", **batch, **extra).loss)
+            eng_g.backward(model_g(mode="train", **bg, **eg).loss)
+        eng_c.optimizer_step(1e-3)
+        eng_g.optimizer_step(1e-3)
+    torch.cuda.synchronize()
+    G.check_status()
+    assert abs(eng_g.grad_norm().item() - eng_c.grad_norm().item()) / eng_c.grad_norm().item() < 0.05
+    tot = agree = 0
+    for bg_, bc_ in zip(eng_g.buffers, eng_c.buffers):
+        s0, s1 = bc_.shard_range
+        # the direction of the Adam update (sign of the first moment) agrees almost everywhere
+        mg, mc = bg_.exp_avg[: bg_.numel].float().cpu(), bc_.exp_avg[: bc_.numel]
+        big = mc.abs() > mc.abs().mean()
+        tot += int(big.sum())
+        agree += int((torch.sign(mg[big]) == torch.sign(mc[big])).sum())
+    assert agree / max(tot, 1) > 0.97, agree / max(tot, 1)

@@ -98,3 +98,62 @@ def test_barrier_wait_runs_out_and_reports_status():
     assert flags[0].item() == 1 and flags[32].item() == 1  # our own signals were delivered
     x = torch.ones(8, device="cuda") * 2  # context still works
     assert x.sum().item() == 16
+
+
+def _ag_worker(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    import torch.distributed as dist
+
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from wallx_b200.ops import gemm as G
+    from wallx_b200.parallel.ag_linear import AgLinear, GatherWorkspace
+
+    torch.manual_seed(0)  # same full weight on every rank; each keeps its rows
+    rows, cols, T = 2560, 2048, 1536
+    full = (torch.randn(rows, cols, device=dev) * 0.03).to(torch.bfloat16)
+    ws = GatherWorkspace(rows * cols, dev, slots=1)
+    lin = AgLinear(cols, rows, dist.group.WORLD, dev, workspace=ws)
+    lin.weight.load_full(full)
+    torch.cuda.synchronize()
+    dist.barrier()  # every shard is in place before any rank gathers
+    torch.manual_seed(10 + rank)
+    x = torch.randn(T, cols, device=dev).to(torch.bfloat16).requires_grad_(True)
+    dy = torch.randn(T, rows, device=dev).to(torch.bfloat16)
+    res = {}
+    for it in range(2):
+        x.grad = None
+        y = lin(x)
+        y.backward(dy)
+        gshard = lin.reduce_scatter_grad()
+    torch.cuda.synchronize()
+    G.check_status()
+    # reference: NCCL all-gather of the shards + fp32 matmuls
+    parts = [torch.empty_like(lin.weight.shard) for _ in range(world)]
+    dist.all_gather(parts, lin.weight.shard)
+    w = torch.cat(parts).float()
+    assert torch.equal(w.to(torch.bfloat16), full)
+    y_ref = x.detach().float() @ w.t()
+    dx_ref = dy.float() @ w
+    dw = dy.float().t() @ x.detach().float()
+    dist.all_reduce(dw, op=dist.ReduceOp.AVG)
+    r0 = rank * (rows // world)
+    res["y"] = (y.detach().float() - y_ref).abs().max().item() / y_ref.abs().max().item()
+    res["dx"] = (x.grad.float() - dx_ref).abs().max().item() / dx_ref.abs().max().item()
+    res["dw"] = (gshard - dw[r0:r0 + rows // world]).abs().max().item() / dw.abs().max().item()
+    torch.save(res, os.path.join(tmp, f"ag_{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(600)
+def test_gathered_weight_linear_two_gpus(tmp_path):
+    """Weight shards pulled from the peer GPU inside the GEMM: forward, dgrad and sharded wgrad."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    mp.spawn(_ag_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        res = torch.load(tmp_path / f"ag_{r}.pt")
+        assert res["y"] < 1e-2 and res["dx"] < 1e-2 and res["dw"] < 1e-2, res

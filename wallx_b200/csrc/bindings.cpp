@@ -105,6 +105,45 @@ void gemm_grouped(const std::vector<GemmTuple>& calls, int64_t force_bn) {
   TORCH_CHECK(rc == 0, "gemm_launch failed with code ", rc);
 }
 
+// One or two GEMMs whose weight operands (tuple element 2 = the local staging buffers) are gathered
+// from the ranks' shards while the kernel runs. peers[i] are the raw device addresses of problem
+// i's shards, one per rank.
+void gemm_ag(const std::vector<GemmTuple>& calls, const std::vector<std::vector<int64_t>>& peers,
+             const std::vector<at::Tensor>& flags, int64_t rank, const std::vector<int64_t>& rows_per_rank,
+             int64_t n_pullers, const std::vector<int64_t>& epoch) {
+  const size_t n = calls.size();
+  TORCH_CHECK(n >= 1 && n <= 2 && peers.size() == n && flags.size() == n && rows_per_rank.size() == n && epoch.size() == n,
+              "gemm_ag: one or two problems, one entry per problem in every list");
+  wx::GemmCall cs[2];
+  wx::AgInfo ags[2] = {};
+  for (size_t i = 0; i < n; ++i) {
+    fill_call(cs[i], calls[i]);
+    TORCH_CHECK(peers[i].size() >= 1 && peers[i].size() <= 8, "gemm_ag: 1..8 ranks");
+    TORCH_CHECK(flags[i].is_cuda() && flags[i].scalar_type() == at::kInt && flags[i].is_contiguous(), "gemm_ag: flags int32");
+    const at::Tensor& W = std::get<2>(calls[i]);
+    TORCH_CHECK(W.is_contiguous(), "gemm_ag: staging must be contiguous");
+    TORCH_CHECK(W.size(0) == static_cast<int64_t>(peers[i].size()) * rows_per_rank[i],
+                "gemm_ag: staging rows != world * rows_per_rank");
+    TORCH_CHECK(flags[i].numel() >= (W.size(0) + 255) / 256, "gemm_ag: one flag per 256 weight rows");
+    wx::AgInfo& ag = ags[i];
+    for (size_t r = 0; r < peers[i].size(); ++r)
+      ag.peer[r] = reinterpret_cast<const void*>(static_cast<uintptr_t>(peers[i][r]));
+    ag.staging = W.data_ptr();
+    ag.flags = flags[i].data_ptr<int>();
+    ag.world = static_cast<int>(peers[i].size());
+    ag.rank = static_cast<int>(rank);
+    ag.rows_per_rank = static_cast<int>(rows_per_rank[i]);
+    ag.n_pullers = static_cast<int>(n_pullers);
+    ag.epoch = static_cast<int>(epoch[i]);
+  }
+  const at::Tensor& W0 = std::get<2>(calls[0]);
+  c10::cuda::CUDAGuard guard(W0.device());
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream();
+  int* status = status_tensor(W0.device()).data_ptr<int>();
+  int rc = wx::gemm_ag_launch(cs, ags, static_cast<int>(n), stream, status);
+  TORCH_CHECK(rc == 0, "gemm_ag_launch failed with code ", rc);
+}
+
 bool view2d_ok(const at::Tensor& t) {
   return t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.dim() == 2 && t.stride(1) == 1 && (t.stride(0) % 8) == 0 &&
          (reinterpret_cast<uintptr_t>(t.data_ptr()) % 16) == 0;
@@ -189,6 +228,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
 #ifdef WX_ATTN_TRACE
   m.def("attn_trace", &attn_trace);
 #endif
+  m.def("gemm_ag", &gemm_ag, "GEMM with the weight all-gather fused in (peer loads over NVLink)");
   m.def("gemm_grouped", &gemm_grouped, "tcgen05 GEMM: one or two problems in one launch");
   m.def("read_status", &read_status, "read and clear the device-side wait-timeout status");
   m.def("attn_fwd", &attn_fwd);

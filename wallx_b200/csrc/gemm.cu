@@ -40,10 +40,26 @@ struct Problem {
   int M, N, K, m0, k0, flags;
 };
 
+// Device view of a fused weight gather (see AgInfo). The weight is one run of `total_bytes`
+// bytes cut into chunks of `chunk_bytes` (a divisor of both the shard size and the 256-row tile
+// size, so a chunk never straddles a rank or a tile).
+struct AgDev {
+  const uint8_t* peer[8];
+  uint8_t* staging;
+  int* flags;
+  long shard_bytes, tile_bytes, total_bytes;
+  int chunk_bytes, n_pullers, target, rot, ntiles;
+};
+
 struct GemmArgs {
   Problem p[2];
   int nprob;
+  AgDev ag[2];  // one per problem; used by the AG instantiations only
 };
+
+constexpr int kAgRing = 12;          // 16 KB buffers in the (otherwise unused) stage area of a puller CTA
+constexpr int kAgChunkMax = 16384;
+constexpr int kAgDepth = kAgRing - 2;  // loads in flight
 
 template <int BN>
 struct Cfg {
@@ -90,7 +106,7 @@ __device__ __forceinline__ void load_dims(const GemmArgs& args, Dims& d) {
   }
 }
 
-__device__ __forceinline__ TileInfo decode_tile(const Dims& d, int t) {
+__device__ __forceinline__ TileInfo decode_tile(const Dims& d, int t, int rot0 = 0, int rot1 = 0) {
   TileInfo ti;
   ti.prob = 0;
   if (t >= d.tiles[0]) {
@@ -101,16 +117,130 @@ __device__ __forceinline__ TileInfo decode_tile(const Dims& d, int t) {
   const int tm = d.tiles_m[ti.prob];
   ti.nt = t / tm;
   ti.mt = t - ti.nt * tm;
+  const int rot = ti.prob ? rot1 : rot0;
+  if (rot) {  // gathered weights: start with the tiles this rank owns
+    ti.nt += rot;
+    const int tn = d.tiles_n[ti.prob];
+    if (ti.nt >= tn) ti.nt -= tn;
+  }
   return ti;
 }
 
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
-template <int BN, bool A_MN, bool B_MN>
+// Copies the weight tiles from the ranks that own them into this GPU's staging buffer; run by one
+// thread of a puller CTA. Global -> shared by bulk copy (mbarrier completion), shared -> global by
+// bulk store (bulk-group completion), kAgDepth loads in flight. All pullers share every tile
+// (chunk i of a tile goes to puller i mod n_pullers), so the first tile arrives as early as the
+// links allow; each puller adds 1 to the tile's flag once its part is in memory.
+__device__ bool ag_pull(const AgDev& ag, int q, uint8_t* ring, uint64_t* bars, volatile int* abort_flag, int& seq) {
+  const int np = ag.n_pullers;
+  const int cb = ag.chunk_bytes;
+  int issued = seq, stored = seq;  // chunk sequence numbers of this puller (all stores up to seq are complete)
+  // (tile, chunk-in-tile) cursors for the load side and the store side
+  int lj = 0, li = q, sj = 0, si = q;
+  auto tile_chunks = [&](int nt) {
+    const long left = ag.total_bytes - static_cast<long>(nt) * ag.tile_bytes;
+    return static_cast<int>((left < ag.tile_bytes ? left : ag.tile_bytes) / cb);
+  };
+  auto phys = [&](int j) {
+    int nt = j + ag.rot;
+    return nt >= ag.ntiles ? nt - ag.ntiles : nt;
+  };
+  // skip to the first tile in which this puller has a chunk (load side)
+  auto advance = [&](int& j, int& i) {
+    while (j < ag.ntiles && i >= tile_chunks(phys(j))) {
+      i = q;
+      ++j;
+    }
+  };
+  bool ok = true;
+  while (ok) {
+    // ---- store side: chunk `stored` once kAgDepth loads are ahead of it or the loads ran out
+    advance(lj, li);
+    const bool loads_done = lj >= ag.ntiles;
+    if (stored < issued && (issued - stored >= kAgDepth || loads_done)) {
+      // tiles in which this puller has no chunk still get their arrival
+      while (si >= tile_chunks(phys(sj))) {
+        red_release_gpu_add(&ag.flags[phys(sj)], 1);
+        si = q;
+        ++sj;
+      }
+      const int b = stored % kAgRing;
+      if (!mbar_wait(&bars[b], (stored / kAgRing) & 1u, abort_flag)) {
+        ok = false;
+        break;
+      }
+      const int nt = phys(sj);
+      const long off = static_cast<long>(nt) * ag.tile_bytes + static_cast<long>(si) * cb;
+      bulk_store(ag.staging + off, ring + b * kAgChunkMax, cb);
+      tma_store_commit();
+      ++stored;
+      si += np;
+      if (si >= tile_chunks(nt)) {  // last chunk of this puller in the tile: publish
+        bulk_store_wait_all();
+        fence_proxy_async_global();
+        red_release_gpu_add(&ag.flags[nt], 1);
+        si = q;
+        ++sj;
+      }
+      continue;
+    }
+    if (loads_done) break;
+    // ---- load side
+    const int b = issued % kAgRing;
+    if (issued - seq >= kAgRing) bulk_store_wait_read<2>();  // the store that last read this buffer is 2+ groups back
+    const int nt = phys(lj);
+    const long off = static_cast<long>(nt) * ag.tile_bytes + static_cast<long>(li) * cb;
+    const int r = static_cast<int>(off / ag.shard_bytes);
+    const uint8_t* src = ag.peer[r] + (off - static_cast<long>(r) * ag.shard_bytes);
+    mbar_arrive_expect_tx(&bars[b], cb);
+    bulk_load(ring + b * kAgChunkMax, src, cb, &bars[b]);
+    ++issued;
+    li += np;
+  }
+  bulk_store_wait_all();
+  if (ok) {
+    while (sj < ag.ntiles) {  // trailing tiles without a chunk of this puller
+      red_release_gpu_add(&ag.flags[phys(sj)], 1);
+      ++sj;
+    }
+  }
+  seq = issued;
+  return ok;
+}
+
+// Bounded wait of a GEMM producer for a gathered tile.
+__device__ __forceinline__ bool ag_wait(const int* flag, int target, volatile int* abort_flag) {
+  if (ld_acquire_gpu(flag) < target) {
+    const long long t0 = clock64();
+    while (ld_acquire_gpu(flag) < target) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > WX_WAIT_LIMIT_CYCLES) {
+        *abort_flag = 1;
+        return false;
+      }
+      __nanosleep(64);
+    }
+  }
+  fence_proxy_async_global();
+  return true;
+}
+
+template <int BN, bool A_MN, bool B_MN, bool AG>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
   using C = Cfg<BN>;
+  static_assert(!AG || (BN == 256 && !A_MN), "gathered-weight mode: 256-wide tiles, K-major A");
+  static_assert(!AG || C::STAGES * C::STAGE_BYTES >= kAgRing * kAgChunkMax, "ring must fit in the stage area");
+  const int n_pull = AG ? args.ag[0].n_pullers : 0;
+  const bool puller = AG && static_cast<int>(blockIdx.x) < n_pull;
+  const int cta = static_cast<int>(blockIdx.x) - n_pull;
+  const int ncta = static_cast<int>(gridDim.x) - n_pull;
+  const int rot0 = (AG && !B_MN) ? args.ag[0].rot : 0;
+  const int rot1 = (AG && !B_MN) ? args.ag[1].rot : 0;
+
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
@@ -124,13 +254,19 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::STAGES; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
-    }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 4);
+    if (puller) {
+      // the 2 * STAGES + 4 barriers are contiguous; a puller uses the first kAgRing of them
+      static_assert(!AG || 2 * C::STAGES + 4 >= kAgRing, "not enough barriers for the ring");
+      for (int s = 0; s < kAgRing; ++s) mbar_init(&full_bar[s], 1);
+    } else {
+      for (int s = 0; s < C::STAGES; ++s) {
+        mbar_init(&full_bar[s], 1);
+        mbar_init(&empty_bar[s], 1);
+      }
+      for (int a = 0; a < 2; ++a) {
+        mbar_init(&tfull_bar[a], 1);
+        mbar_init(&tempty_bar[a], 4);
+      }
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -148,7 +284,13 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
   load_dims<BN>(args, d);
   const int total_tiles = d.tiles[0] + d.tiles[1];
 
-  if (warp == 0) {
+  if (puller) {
+    if (threadIdx.x == 0) {
+      int seq = 0;  // chunk sequence number carries over: the ring's barrier phases continue
+      for (int i = 0; i < args.nprob; ++i)
+        if (!ag_pull(args.ag[i], static_cast<int>(blockIdx.x), smem, full_bar, abort_flag, seq)) break;
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       for (int i = 0; i < args.nprob; ++i) {
@@ -158,14 +300,32 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const TileInfo ti = decode_tile(d, t);
+      int ag_ready[2] = {0, 0};  // MN-major B: 256-row blocks of the weight known to be in place
+      for (int t = cta; t < total_tiles && ok; t += ncta) {
+        const TileInfo ti = decode_tile(d, t, rot0, rot1);
         const Problem& p = args.p[ti.prob];
         const int m_base = d.m0[ti.prob] + ti.mt * BM;
         const int n_base = ti.nt * BN;
         const int k_base = d.k0[ti.prob];
         const int nkb = (d.K[ti.prob] + BK - 1) / BK;
         for (int kb = 0; kb < nkb; ++kb) {
+          if (AG) {
+            if (!B_MN) {
+              if (kb == 0 && !ag_wait(&args.ag[ti.prob].flags[ti.nt], args.ag[ti.prob].target, abort_flag)) {
+                ok = false;
+                break;
+              }
+            } else {
+              const int blk = (k_base + kb * BK + BK - 1) >> 8;
+              if (blk >= ag_ready[ti.prob]) {
+                if (!ag_wait(&args.ag[ti.prob].flags[blk], args.ag[ti.prob].target, abort_flag)) {
+                  ok = false;
+                  break;
+                }
+                ag_ready[ti.prob] = blk + 1;  // pullers finish tiles in order
+              }
+            }
+          }
           if (!mbar_wait(&empty_bar[s], phase ^ 1u, abort_flag)) {
             ok = false;
             break;
@@ -201,8 +361,8 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++it) {
-        const TileInfo ti = decode_tile(d, t);
+      for (int t = cta; t < total_tiles && ok; t += ncta, ++it) {
+        const TileInfo ti = decode_tile(d, t, rot0, rot1);
         const int nkb = (d.K[ti.prob] + BK - 1) / BK;
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
@@ -238,8 +398,8 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
     // ------------------------------------------------------------------ epilogue
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
     int it = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
-      const TileInfo ti = decode_tile(d, t);
+    for (int t = cta; t < total_tiles; t += ncta, ++it) {
+      const TileInfo ti = decode_tile(d, t, rot0, rot1);
       const Problem& p = args.p[ti.prob];
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
@@ -436,10 +596,10 @@ int num_sms() {
   return n;
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool AG = false>
 int launch_t(const GemmArgs& args, int grid, cudaStream_t stream, int* status) {
   using C = Cfg<BN>;
-  auto kern = gemm_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN, AG>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
@@ -458,40 +618,10 @@ int launch_bn(const GemmArgs& args, bool a_mn, bool b_mn, int grid, cudaStream_t
   return launch_t<BN, true, true>(args, grid, stream, status);
 }
 
-}  // namespace
-
-int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* status, int force_bn) {
-  if (ncalls < 1 || ncalls > 2) return -1;
-  const bool a_mn = calls[0].a_mn, b_mn = calls[0].b_mn;
-  for (int i = 1; i < ncalls; ++i)
-    if (calls[i].a_mn != a_mn || calls[i].b_mn != b_mn) return -2;
-
-  // Tile width: the widest BN that still gives every SM a tile.
-  const int sms = num_sms();
-  auto count_tiles = [&](int bn) {
-    long t = 0;
-    for (int i = 0; i < ncalls; ++i)
-      t += static_cast<long>((calls[i].M + BM - 1) / BM) * ((calls[i].N + bn - 1) / bn);
-    return t;
-  };
-  int bn = 64;
-  if (force_bn == 64 || force_bn == 128 || force_bn == 256) {
-    bn = force_bn;
-  } else {
-    int max_n = 0;
-    for (int i = 0; i < ncalls; ++i) max_n = calls[i].N > max_n ? calls[i].N : max_n;
-    if (max_n > 128 && count_tiles(256) >= sms * 3 / 4)
-      bn = 256;
-    else if (max_n > 64 && count_tiles(128) >= sms * 3 / 4)
-      bn = 128;
-    else
-      bn = (max_n > 64 && count_tiles(64) > 4L * sms) ? 128 : 64;
-  }
-  for (int i = 0; i < ncalls; ++i)
-    if ((calls[i].flags & GEMM_ACT_SWIGLU) && (calls[i].N % 32 != 0)) return -3;
-
-  GemmArgs args;
+int fill_args(GemmArgs& args, const GemmCall* calls, int ncalls, int bn) {
   args.nprob = ncalls;
+  args.ag[0] = AgDev{};
+  args.ag[1] = AgDev{};
   for (int i = 0; i < ncalls; ++i) {
     const GemmCall& c = calls[i];
     Problem& p = args.p[i];
@@ -522,12 +652,115 @@ int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* sta
     p.k0 = c.k0;
     p.flags = c.flags;
   }
+  return 0;
+}
+
+}  // namespace
+
+int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* status, int force_bn) {
+  if (ncalls < 1 || ncalls > 2) return -1;
+  const bool a_mn = calls[0].a_mn, b_mn = calls[0].b_mn;
+  for (int i = 1; i < ncalls; ++i)
+    if (calls[i].a_mn != a_mn || calls[i].b_mn != b_mn) return -2;
+
+  const int sms = num_sms();
+  auto count_tiles = [&](int bn) {
+    long t = 0;
+    for (int i = 0; i < ncalls; ++i)
+      t += static_cast<long>((calls[i].M + BM - 1) / BM) * ((calls[i].N + bn - 1) / bn);
+    return t;
+  };
+  // Tile width: minimise (number of waves) x (time of one tile); per-width MMA efficiency measured
+  // on B200 (BN 256 / 128 / 64 reach about 1260 / 970 / 525 TFLOP/s with every SM busy).
+  int bn = 64;
+  if (force_bn == 64 || force_bn == 128 || force_bn == 256) {
+    bn = force_bn;
+  } else {
+    int max_n = 0;
+    for (int i = 0; i < ncalls; ++i) max_n = calls[i].N > max_n ? calls[i].N : max_n;
+    const int widths[3] = {256, 128, 64};
+    const double eff[3] = {1260.0, 970.0, 525.0};
+    const double bias[3] = {1.0, 1.12, 1.25};  // wave counting is crude: prefer the wider tile on near ties
+    double best = 1e300;
+    for (int w = 0; w < 3; ++w) {
+      if (widths[w] > 64 && max_n <= widths[w] / 2) continue;  // mostly padding
+      const long t = count_tiles(widths[w]);
+      const long waves = (t + sms - 1) / sms;
+      const double cost = static_cast<double>(waves) * widths[w] / eff[w] * bias[w];
+      if (cost < best) {
+        best = cost;
+        bn = widths[w];
+      }
+    }
+  }
+  for (int i = 0; i < ncalls; ++i)
+    if ((calls[i].flags & GEMM_ACT_SWIGLU) && (calls[i].N % 32 != 0)) return -3;
+
+  GemmArgs args;
+  const int rc = fill_args(args, calls, ncalls, bn);
+  if (rc != 0) return rc;
   long tiles = count_tiles(bn);
   if (tiles <= 0) return 0;
   int grid = tiles < sms ? static_cast<int>(tiles) : sms;
   if (bn == 256) return launch_bn<256>(args, a_mn, b_mn, grid, stream, status);
   if (bn == 128) return launch_bn<128>(args, a_mn, b_mn, grid, stream, status);
   return launch_bn<64>(args, a_mn, b_mn, grid, stream, status);
+}
+
+int gemm_ag_launch(const GemmCall* calls, const AgInfo* ags, int ncalls, cudaStream_t stream, int* status) {
+  if (ncalls < 1 || ncalls > 2) return -1;
+  const bool b_mn = calls[0].b_mn;
+  for (int i = 0; i < ncalls; ++i)
+    if (calls[i].a_mn || calls[i].b_mn != b_mn) return -2;
+  for (int i = 0; i < ncalls; ++i)
+    if ((calls[i].flags & GEMM_ACT_SWIGLU) && (calls[i].N % 32 != 0)) return -3;
+  GemmArgs args;
+  const int rc = fill_args(args, calls, ncalls, 256);
+  if (rc != 0) return rc;
+  const int sms = num_sms();
+  int np = ags[0].n_pullers > 0 ? ags[0].n_pullers : 12;
+  if (np > sms / 2) np = sms / 2;
+  long tiles = 0;
+  for (int i = 0; i < ncalls; ++i) {
+    const GemmCall& call = calls[i];
+    const AgInfo& ag = ags[i];
+    if (ag.world < 1 || ag.world > 8 || ag.rows_per_rank < 1 || ag.epoch < 1) return -6;
+    if (call.B != ag.staging) return -7;
+    // rows of the weight in memory, and its row length
+    const long w_rows = static_cast<long>(ag.world) * ag.rows_per_rank;
+    const long w_cols = call.ldb;
+    if (!b_mn ? (w_rows != call.N || call.b_extent_mn != w_rows) : (call.b_extent_k != w_rows)) return -8;
+    if ((w_cols * 2) % 16 != 0) return -9;
+    for (int r = 0; r < ag.world; ++r)
+      if (ag.peer[r] == nullptr || (reinterpret_cast<uintptr_t>(ag.peer[r]) & 15) != 0) return -9;
+    if ((reinterpret_cast<uintptr_t>(ag.staging) & 15) != 0) return -9;
+    AgDev& a = args.ag[i];
+    for (int r = 0; r < ag.world; ++r) a.peer[r] = static_cast<const uint8_t*>(ag.peer[r]);
+    a.staging = static_cast<uint8_t*>(ag.staging);
+    a.flags = ag.flags;
+    a.shard_bytes = static_cast<long>(ag.rows_per_rank) * w_cols * 2;
+    a.tile_bytes = 256 * w_cols * 2;
+    a.total_bytes = w_rows * w_cols * 2;
+    a.ntiles = static_cast<int>((w_rows + 255) / 256);
+    // chunk: the largest multiple of 16 bytes, at most 16 KB, dividing both the shard and the tile
+    int chunk = 0;
+    for (int c = kAgChunkMax; c >= 16; c -= 16)
+      if (a.shard_bytes % c == 0 && a.tile_bytes % c == 0) {
+        chunk = c;
+        break;
+      }
+    if (chunk == 0) return -9;
+    a.chunk_bytes = chunk;
+    a.n_pullers = np;
+    a.target = np * ag.epoch;
+    a.rot = b_mn ? 0 : static_cast<int>((static_cast<long>(ag.rank) * ag.rows_per_rank) / 256) % a.ntiles;
+    tiles += static_cast<long>((call.M + BM - 1) / BM) * ((call.N + 255) / 256);
+  }
+  if (tiles <= 0) return 0;
+  const int workers = tiles < sms - np ? static_cast<int>(tiles) : sms - np;
+  const int grid = workers + np;
+  if (!b_mn) return launch_t<256, false, false, true>(args, grid, stream, status);
+  return launch_t<256, false, true, true>(args, grid, stream, status);
 }
 
 }  // namespace wx

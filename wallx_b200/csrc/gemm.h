@@ -51,8 +51,30 @@ struct GemmCall {
   int flags;
 };
 
+// Weight all-gather fused into the GEMM (ZeRO-3 style sharded weight): B's rows are split evenly
+// over `world` ranks, rank r holding rows [r * rows_per_rank, (r + 1) * rows_per_rank) at
+// peer[r] (peer-mapped memory over NVLink). A few CTAs of the persistent grid pull the shards
+// into `staging` (this GPU's memory, [N][K]) one 256-row tile at a time with bulk copies and
+// publish a flag per tile; the GEMM CTAs take the tiles in the same order and wait (bounded) on
+// the flag before loading a B tile from `staging` by TMA. No load uses cluster multicast.
+struct AgInfo {
+  const void* peer[8];  // peer[r]: rank r's shard, [rows_per_rank][K] bf16, pitch K
+  void* staging;        // this GPU's [N][K] bf16 buffer that the GEMM reads B from
+  int* flags;           // device int[ceil(N / 256)]; every puller adds 1 per tile per call
+  int world, rank, rows_per_rank;
+  int n_pullers;        // CTAs of the grid that copy instead of multiplying (0 = default)
+  int epoch;            // 1, 2, 3, ... per call on the same flags; a tile is ready at n_pullers * epoch
+};
+
 // Launches on `stream`. `status` is a device int that the kernel sets non-zero when one of its
 // bounded waits ran out (the kernel then returns normally). Returns a CUDA error code (0 = ok).
 int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* status, int force_bn);
+
+// One or two problems (A K-major; B K-major for the forward, MN-major for dgrad) whose B operand, the
+// weight [N][K] resp. [K][N], is gathered from `ag.peer` while the GEMM runs; call.B must be
+// ag.staging and call.ldb the weight's row length. Tile width is fixed at 256. Every rank's
+// shard must be complete before any rank launches (a barrier between the optimizer step and the
+// first gather is the caller's job).
+int gemm_ag_launch(const GemmCall* calls, const AgInfo* ags, int ncalls, cudaStream_t stream, int* status);
 
 }  // namespace wx

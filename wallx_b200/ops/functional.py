@@ -29,6 +29,46 @@ def _C():
     return _ext.get()
 
 
+# Gradient sinks: when a weight lives in a flat gradient buffer, its weight-gradient GEMM adds
+# straight into that buffer (GEMM epilogue with the accumulate flag) instead of producing a
+# temporary that autograd then adds: one kernel and one pass over the gradient less per weight.
+# Keyed by the weight's data pointer; the value is (gradient view, callback marking it as used).
+_GRAD_SINKS = {}
+
+
+def register_grad_sink(weight: torch.Tensor, grad_view: torch.Tensor, mark) -> None:
+    import weakref
+
+    _GRAD_SINKS[weight.data_ptr()] = (grad_view, mark, weakref.ref(weight))
+
+
+def _sink_of(w: torch.Tensor):
+    s = _GRAD_SINKS.get(w.data_ptr())
+    if s is None:
+        return None
+    owner = s[2]()
+    if owner is None or owner.data_ptr() != w.data_ptr() or s[0].shape != w.shape or not _pitch_ok(s[0]):
+        return None
+    return s
+
+
+def clear_grad_sinks() -> None:
+    _GRAD_SINKS.clear()
+
+
+def _wgrad(a: torch.Tensor, b: torch.Tensor, w: torch.Tensor, **spec_kw):
+    """dW[n, k] = sum_t a[t, n] b[t, k] (+ optional dyn/K overrides). Returns the gradient to hand
+    to autograd, or None when it was accumulated into the weight's sink."""
+    sink = _sink_of(w)
+    if sink is not None:
+        G.launch([G.GemmSpec(a, b, sink[0], a_mn=True, b_mn=True, flags=G.ACCUMULATE, **spec_kw)])
+        sink[1]()
+        return None
+    dw = torch.zeros_like(w) if "dyn" in spec_kw else torch.empty_like(w)
+    G.launch([G.GemmSpec(a, b, dw, a_mn=True, b_mn=True, **spec_kw)])
+    return dw
+
+
 def _pitch_ok(t: torch.Tensor) -> bool:
     return t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0
 
@@ -68,9 +108,8 @@ class _LinearFn(torch.autograd.Function):
             # dx[m, k] = sum_n dy[m, n] w[n, k]: B(n'=k, k'=n) is w read as MN-major
             G.launch([G.GemmSpec(dy2, _aligned2d(w), dx, b_mn=True)])
         if ctx.needs_input_grad[1]:
-            dw = torch.empty_like(w)
             # dw[n, k] = sum_m dy[m, n] x[m, k]: both operands MN-major over the token axis
-            G.launch([G.GemmSpec(dy2, _aligned2d(x), dw, a_mn=True, b_mn=True)])
+            dw = _wgrad(dy2, _aligned2d(x), w)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = column_sum(dy)
         if ctx.has_res and ctx.needs_input_grad[3]:
@@ -172,8 +211,7 @@ class _GateUpFn(torch.autograd.Function):
             dx = torch.empty_like(x)
             G.launch([G.GemmSpec(dgu, w_gu, dx, b_mn=True)])
         if ctx.needs_input_grad[1]:
-            dw = torch.empty_like(w_gu)
-            G.launch([G.GemmSpec(dgu, x, dw, a_mn=True, b_mn=True)])
+            dw = _wgrad(dgu, x, w_gu)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = column_sum(dgu)
         return dx, dw, db
@@ -281,10 +319,15 @@ class _MoeFfnFn(torch.autograd.Function):
         for e in range(n_exp):
             w_dn = weights[2 * e + 1]
             I = w_dn.shape[1]
-            dw = torch.zeros_like(w_dn)  # stays zero when the expert has no tokens
-            grads[2 * e + 1] = dw
+            sink = _sink_of(w_dn)
+            if sink is not None:  # accumulate straight into the flat gradient buffer
+                dw, fl = sink[0], G.ACCUMULATE
+                sink[1]()
+            else:
+                dw, fl = torch.zeros_like(w_dn), 0  # stays zero when the expert has no tokens
+                grads[2 * e + 1] = dw
             # dw[hid, i] = sum over the expert's (128-padded) token segment of dy[t, hid] h[t, i]
-            specs.append(G.GemmSpec(dyp, h[:, :I], dw, a_mn=True, b_mn=True, M=H, N=I, K=rows, dyn=segk[e]))
+            specs.append(G.GemmSpec(dyp, h[:, :I], dw, a_mn=True, b_mn=True, M=H, N=I, K=rows, dyn=segk[e], flags=fl))
         for i in range(0, n_exp, 2):
             G.launch(specs[i:i + 2])
         dgu = _C().swiglu_bwd(dh, gu)
@@ -299,9 +342,14 @@ class _MoeFfnFn(torch.autograd.Function):
         for e in range(n_exp):
             w_gu = weights[2 * e]
             W = w_gu.shape[0]
-            dw = torch.zeros_like(w_gu)
-            grads[2 * e] = dw
-            specs.append(G.GemmSpec(dgu[:, :W], xp, dw, a_mn=True, b_mn=True, M=W, N=H, K=rows, dyn=segk[e]))
+            sink = _sink_of(w_gu)
+            if sink is not None:
+                dw, fl = sink[0], G.ACCUMULATE
+                sink[1]()
+            else:
+                dw, fl = torch.zeros_like(w_gu), 0
+                grads[2 * e] = dw
+            specs.append(G.GemmSpec(dgu[:, :W], xp, dw, a_mn=True, b_mn=True, M=W, N=H, K=rows, dyn=segk[e], flags=fl))
         for i in range(0, n_exp, 2):
             G.launch(specs[i:i + 2])
         dres = dout if ctx.has_res else None

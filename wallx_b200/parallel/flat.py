@@ -82,6 +82,12 @@ class FlatBuffer:
         self.touched = [False] * len(self.params)
         for i, p in enumerate(self.params):
             p.register_post_accumulate_grad_hook(self._make_hook(i))
+        if self.param.is_cuda:  # weight-gradient GEMMs add straight into the flat gradient buffer
+            from ..ops import functional as F_
+
+            for i, (p, o) in enumerate(zip(self.params, self.offsets)):
+                if p.dim() == 2:
+                    F_.register_grad_sink(p, self.grad[o:o + p.numel()].view(p.shape), self._make_hook(i))
         self.seg_of_param = []
         for o in self.offsets:
             self.seg_of_param.append(next(k for k, sg in enumerate(self.segments) if sg.start <= o < sg.end))
@@ -92,7 +98,7 @@ class FlatBuffer:
         self.exp_avg_sq = torch.zeros(self.shard_size, device=self.device, dtype=master_dtype)
 
     def _make_hook(self, i: int):
-        def hook(_p):
+        def hook(_p=None):
             self.touched[i] = True
 
         return hook
