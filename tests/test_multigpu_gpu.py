@@ -101,6 +101,9 @@ def test_barrier_wait_runs_out_and_reports_status():
 
 
 def _ag_worker(rank, world, port, tmp):
+    import faulthandler
+
+    faulthandler.enable()
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)

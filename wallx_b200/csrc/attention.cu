@@ -864,6 +864,12 @@ EncodeTiledFn encode_fn() {
 bool tmap2d(CUtensorMap* out, const void* ptr, uint64_t width, uint64_t rows, uint64_t pitch, uint32_t box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
+  // the encode call is a driver call: make sure this thread has the primary context bound
+  thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
   cuuint64_t dims[2] = {width, rows};
   cuuint64_t strides[1] = {pitch * 2};
   cuuint32_t box[2] = {64, box_rows};

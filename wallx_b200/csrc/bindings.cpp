@@ -6,6 +6,8 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <cstdio>
+#include <stdexcept>
 #include <tuple>
 #include <vector>
 
@@ -16,6 +18,14 @@
 namespace {
 
 using OptT = c10::optional<at::Tensor>;
+
+// Launch-failure report formatted with snprintf (no iostream on the error path).
+[[noreturn]] void fail_code(const char* what, int rc) {
+  char buf[160];
+  snprintf(buf, sizeof(buf), "%s failed with code %d%s%s", what, rc, rc > 0 ? ": " : "",
+           rc > 0 ? cudaGetErrorString(static_cast<cudaError_t>(rc)) : "");
+  throw std::runtime_error(buf);
+}
 
 at::Tensor& status_tensor(const at::Device& dev) {
   static std::vector<at::Tensor> per_dev(64);
@@ -102,7 +112,7 @@ void gemm_grouped(const std::vector<GemmTuple>& calls, int64_t force_bn) {
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   int* status = status_tensor(A0.device()).data_ptr<int>();
   int rc = wx::gemm_launch(cs, static_cast<int>(calls.size()), stream, status, static_cast<int>(force_bn));
-  TORCH_CHECK(rc == 0, "gemm_launch failed with code ", rc);
+  if (rc != 0) fail_code("gemm_launch", rc);
 }
 
 // One or two GEMMs whose weight operands (tuple element 2 = the local staging buffers) are gathered
@@ -141,7 +151,7 @@ void gemm_ag(const std::vector<GemmTuple>& calls, const std::vector<std::vector<
   cudaStream_t stream = at::cuda::getCurrentCUDAStream();
   int* status = status_tensor(W0.device()).data_ptr<int>();
   int rc = wx::gemm_ag_launch(cs, ags, static_cast<int>(n), stream, status);
-  TORCH_CHECK(rc == 0, "gemm_ag_launch failed with code ", rc);
+  if (rc != 0) fail_code("gemm_ag_launch", rc);
 }
 
 bool view2d_ok(const at::Tensor& t) {

@@ -49,6 +49,7 @@ struct AgDev {
   int* flags;
   long shard_bytes, tile_bytes, total_bytes;
   int chunk_bytes, n_pullers, target, rot, ntiles;
+  int cpt, last_chunks, cps;  // chunks per full tile, in the last tile, per shard
 };
 
 struct GemmArgs {
@@ -133,78 +134,86 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)
 // thread of a puller CTA. Global -> shared by bulk copy (mbarrier completion), shared -> global by
 // bulk store (bulk-group completion), kAgDepth loads in flight. All pullers share every tile
 // (chunk i of a tile goes to puller i mod n_pullers), so the first tile arrives as early as the
-// links allow; each puller adds 1 to the tile's flag once its part is in memory.
+// links allow; each puller adds 1 to the tile's flag once its part is in memory. The loop is
+// scalar code on one thread, so it works in 32-bit chunk units and avoids 64-bit divisions.
+struct AgCursor {
+  int j, i, nt, n;  // logical tile, chunk in tile, physical tile, chunks in that tile
+};
+
+__device__ __forceinline__ void ag_enter(const AgDev& ag, AgCursor& c) {
+  int nt = c.j + ag.rot;
+  if (nt >= ag.ntiles) nt -= ag.ntiles;
+  c.nt = nt;
+  c.n = (nt == ag.ntiles - 1) ? ag.last_chunks : ag.cpt;
+}
+
 __device__ bool ag_pull(const AgDev& ag, int q, uint8_t* ring, uint64_t* bars, volatile int* abort_flag, int& seq) {
   const int np = ag.n_pullers;
-  const int cb = ag.chunk_bytes;
+  const uint32_t cb = static_cast<uint32_t>(ag.chunk_bytes);
   int issued = seq, stored = seq;  // chunk sequence numbers of this puller (all stores up to seq are complete)
-  // (tile, chunk-in-tile) cursors for the load side and the store side
-  int lj = 0, li = q, sj = 0, si = q;
-  auto tile_chunks = [&](int nt) {
-    const long left = ag.total_bytes - static_cast<long>(nt) * ag.tile_bytes;
-    return static_cast<int>((left < ag.tile_bytes ? left : ag.tile_bytes) / cb);
-  };
-  auto phys = [&](int j) {
-    int nt = j + ag.rot;
-    return nt >= ag.ntiles ? nt - ag.ntiles : nt;
-  };
-  // skip to the first tile in which this puller has a chunk (load side)
-  auto advance = [&](int& j, int& i) {
-    while (j < ag.ntiles && i >= tile_chunks(phys(j))) {
-      i = q;
-      ++j;
-    }
-  };
+  int lbuf = seq % kAgRing, sbuf = lbuf;
+  uint32_t sphase = (seq / kAgRing) & 1u;
+  AgCursor L{0, q, 0, 0}, S{0, q, 0, 0};
+  ag_enter(ag, L);
+  ag_enter(ag, S);
   bool ok = true;
-  while (ok) {
-    // ---- store side: chunk `stored` once kAgDepth loads are ahead of it or the loads ran out
-    advance(lj, li);
-    const bool loads_done = lj >= ag.ntiles;
+  while (true) {
+    // load cursor: skip tiles in which this puller has no (more) chunks
+    while (L.j < ag.ntiles && L.i >= L.n) {
+      L.i = q;
+      if (++L.j < ag.ntiles) ag_enter(ag, L);
+    }
+    const bool loads_done = L.j >= ag.ntiles;
     if (stored < issued && (issued - stored >= kAgDepth || loads_done)) {
-      // tiles in which this puller has no chunk still get their arrival
-      while (si >= tile_chunks(phys(sj))) {
-        red_release_gpu_add(&ag.flags[phys(sj)], 1);
-        si = q;
-        ++sj;
+      // ---- store side: tiles without a chunk of this puller still get their arrival
+      while (S.i >= S.n) {
+        red_release_gpu_add(&ag.flags[S.nt], 1);
+        S.i = q;
+        ++S.j;
+        ag_enter(ag, S);
       }
-      const int b = stored % kAgRing;
-      if (!mbar_wait(&bars[b], (stored / kAgRing) & 1u, abort_flag)) {
+      if (!mbar_wait(&bars[sbuf], sphase, abort_flag)) {
         ok = false;
         break;
       }
-      const int nt = phys(sj);
-      const long off = static_cast<long>(nt) * ag.tile_bytes + static_cast<long>(si) * cb;
-      bulk_store(ag.staging + off, ring + b * kAgChunkMax, cb);
+      const size_t off = (static_cast<size_t>(S.nt) * ag.cpt + S.i) * cb;
+      bulk_store(ag.staging + off, ring + sbuf * kAgChunkMax, cb);
       tma_store_commit();
       ++stored;
-      si += np;
-      if (si >= tile_chunks(nt)) {  // last chunk of this puller in the tile: publish
+      if (++sbuf == kAgRing) {
+        sbuf = 0;
+        sphase ^= 1u;
+      }
+      S.i += np;
+      if (S.i >= S.n) {  // last chunk of this puller in the tile: publish
         bulk_store_wait_all();
         fence_proxy_async_global();
-        red_release_gpu_add(&ag.flags[nt], 1);
-        si = q;
-        ++sj;
+        red_release_gpu_add(&ag.flags[S.nt], 1);
+        S.i = q;
+        if (++S.j < ag.ntiles) ag_enter(ag, S);
+        else S.n = 0x7fffffff;  // nothing left: the store side is only entered again with a loaded chunk
       }
       continue;
     }
     if (loads_done) break;
     // ---- load side
-    const int b = issued % kAgRing;
     if (issued - seq >= kAgRing) bulk_store_wait_read<2>();  // the store that last read this buffer is 2+ groups back
-    const int nt = phys(lj);
-    const long off = static_cast<long>(nt) * ag.tile_bytes + static_cast<long>(li) * cb;
-    const int r = static_cast<int>(off / ag.shard_bytes);
-    const uint8_t* src = ag.peer[r] + (off - static_cast<long>(r) * ag.shard_bytes);
-    mbar_arrive_expect_tx(&bars[b], cb);
-    bulk_load(ring + b * kAgChunkMax, src, cb, &bars[b]);
+    const uint32_t g = static_cast<uint32_t>(L.nt) * ag.cpt + L.i;  // chunk index in the whole weight
+    const uint32_t r = g / static_cast<uint32_t>(ag.cps);
+    const uint8_t* src = ag.peer[r] + static_cast<size_t>(g - r * ag.cps) * cb;
+    mbar_arrive_expect_tx(&bars[lbuf], cb);
+    bulk_load(ring + lbuf * kAgChunkMax, src, cb, &bars[lbuf]);
     ++issued;
-    li += np;
+    if (++lbuf == kAgRing) lbuf = 0;
+    L.i += np;
   }
   bulk_store_wait_all();
   if (ok) {
-    while (sj < ag.ntiles) {  // trailing tiles without a chunk of this puller
-      red_release_gpu_add(&ag.flags[phys(sj)], 1);
-      ++sj;
+    // trailing tiles without a chunk of this puller
+    while (S.j < ag.ntiles) {
+      if (S.n != 0x7fffffff) red_release_gpu_add(&ag.flags[S.nt], 1);
+      S.i = q;
+      if (++S.j < ag.ntiles) ag_enter(ag, S);
     }
   }
   seq = issued;
@@ -570,11 +579,24 @@ EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
+// cuTensorMapEncodeTiled is a driver call and needs a context bound to the calling thread. A
+// thread whose first CUDA work is one of these launches (an autograd worker on device 0, for
+// which torch skips cudaSetDevice) has none yet; cudaFree(nullptr) makes the runtime bind the
+// primary context.
+void bind_context_once() {
+  thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
 // 2-D bf16 tensor map with 128-byte swizzle; `inner` is the contiguous extent.
 bool make_tmap(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t pitch_elems,
                uint32_t box_inner, uint32_t box_outer) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return false;
+  bind_context_once();
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {pitch_elems * 2};
   cuuint32_t box[2] = {box_inner, box_outer};
@@ -751,6 +773,9 @@ int gemm_ag_launch(const GemmCall* calls, const AgInfo* ags, int ncalls, cudaStr
       }
     if (chunk == 0) return -9;
     a.chunk_bytes = chunk;
+    a.cpt = static_cast<int>(a.tile_bytes / chunk);
+    a.last_chunks = static_cast<int>((a.total_bytes - static_cast<long>(a.ntiles - 1) * a.tile_bytes) / chunk);
+    a.cps = static_cast<int>(a.shard_bytes / chunk);
     a.n_pullers = np;
     a.target = np * ag.epoch;
     a.rot = b_mn ? 0 : static_cast<int>((static_cast<long>(ag.rank) * ag.rows_per_rank) / 256) % a.ntiles;

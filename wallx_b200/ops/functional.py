@@ -195,10 +195,12 @@ class _GateUpFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w_gu, b_gu):
         M, N = x.shape[0], w_gu.shape[0]
-        gu = torch.empty((M, N), device=x.device, dtype=torch.bfloat16)
+        # the raw gate/up values are only needed by the backward pass
+        gu = torch.empty((M, N), device=x.device, dtype=torch.bfloat16) if any(ctx.needs_input_grad) else None
         h = torch.empty((M, N // 2), device=x.device, dtype=torch.bfloat16)
         G.launch([G.GemmSpec(x, w_gu, h, out2=gu, bias=b_gu, flags=G.ACT_SWIGLU)])
-        ctx.save_for_backward(x, w_gu, gu)
+        if gu is not None:
+            ctx.save_for_backward(x, w_gu, gu)
         ctx.has_bias = b_gu is not None
         return h
 
@@ -279,7 +281,8 @@ class _MoeFfnFn(torch.autograd.Function):
         rows, H = xp.shape
         T = dest.numel()
         wmax = max(weights[2 * e].shape[0] for e in range(n_exp))
-        gu = torch.empty((rows, wmax), device=xp.device, dtype=torch.bfloat16)
+        # the raw gate/up values are only needed by the backward pass
+        gu = torch.empty((rows, wmax), device=xp.device, dtype=torch.bfloat16) if any(ctx.needs_input_grad) else None
         h = torch.empty((rows, wmax // 2), device=xp.device, dtype=torch.bfloat16)
         out = torch.empty((T, H), device=xp.device, dtype=torch.bfloat16)
         specs = [G.GemmSpec(xp, weights[2 * e], h, out2=gu, M=rows, dyn=seg[e],
@@ -293,7 +296,8 @@ class _MoeFfnFn(torch.autograd.Function):
                                     residual=residual))
         for i in range(0, n_exp, 2):
             G.launch(specs[i:i + 2])
-        ctx.save_for_backward(xp, dest, seg, segk, gu, h, *weights)
+        if gu is not None:
+            ctx.save_for_backward(xp, dest, seg, segk, gu, h, *weights)
         ctx.n_exp = n_exp
         ctx.has_res = residual is not None
         return out

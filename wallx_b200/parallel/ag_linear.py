@@ -79,7 +79,8 @@ class ShardedWeight:
         return self.epoch
 
 
-def _launch(specs: Sequence[G.GemmSpec], weights: Sequence[ShardedWeight], n_pullers: int) -> None:
+def ag_launch(specs: Sequence[G.GemmSpec], weights: Sequence[ShardedWeight], n_pullers: int = 0) -> None:
+    """One launch of one or two problems; ``specs[i].b`` must be ``weights[i].staging(slot)`` (distinct slots)."""
     _ext.get().gemm_ag([s.as_tuple() for s in specs], [w.peer_ptrs for w in weights], [w.flags for w in weights],
                        weights[0].rank, [w.rows_per_rank for w in weights], int(n_pullers),
                        [w.next_epoch() for w in weights])
@@ -94,7 +95,7 @@ def ag_gemm(x: torch.Tensor, w: ShardedWeight, *, transpose_w: bool = False, bia
         width = N // 2 if (flags & G.ACT_SWIGLU) else N
         out = torch.empty(M, width, device=x.device, dtype=torch.float32 if (flags & G.OUT_FP32) else torch.bfloat16)
     spec = G.GemmSpec(x, w.staging(), out, b_mn=transpose_w, bias=bias, residual=residual, flags=flags)
-    _launch([spec], [w], n_pullers)
+    ag_launch([spec], [w], n_pullers)
     return out
 
 
@@ -162,5 +163,5 @@ def ag_dual_gate_up(xs: Sequence[torch.Tensor], ws: Sequence[ShardedWeight], *, 
         out = outs[i] if outs is not None else torch.empty(x.shape[0], w.rows // 2, dtype=torch.bfloat16, device=x.device)
         specs.append(G.GemmSpec(x, w.staging(slot=i), out, M=M, m0=m0[i], dyn=dyn[i], flags=G.ACT_SWIGLU))
         res.append(out)
-    _launch(specs, list(ws), n_pullers)
+    ag_launch(specs, list(ws), n_pullers)
     return res
