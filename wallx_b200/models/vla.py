@@ -444,7 +444,7 @@ class Qwen2_5_VLMoEForAction(nn.Module):
                 action_chunk=None, proprioception=None, rope_deltas=None, cache_position=None,
                 second_per_grid_ts=None, num_inference_timesteps=10, dataset_names=None, dof_mask=None,
                 agent_pos_mask=None, re_generate=False, image_grid_host=None, video_grid_host=None, noise=None,
-                **kwargs):
+                reference_grid=False, use_cuda_graph=False, **kwargs):
         from . import inference as INF
 
         if predict_mode == "diffusion":
@@ -456,7 +456,8 @@ class Qwen2_5_VLMoEForAction(nn.Module):
                                     proprioception=proprioception, second_per_grid_ts=second_per_grid_ts,
                                     num_inference_timesteps=num_inference_timesteps, dataset_names=dataset_names,
                                     dof_mask=dof_mask, agent_pos_mask=agent_pos_mask, image_grid_host=image_grid_host,
-                                    video_grid_host=video_grid_host, noise=noise)
+                                    video_grid_host=video_grid_host, noise=noise, reference_grid=reference_grid,
+                                    use_cuda_graph=use_cuda_graph)
         if predict_mode in ("text", "fast"):
             assert input_ids.shape[0] == 1, "predict only support batch size 1 for ar generation"
             return INF.predict_text(self, predict_mode, pred_horizon=pred_horizon, action_dim=action_dim,
