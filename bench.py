@@ -34,11 +34,12 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default="flow", choices=["flow", "fast"])
     ap.add_argument("--per-gpu-batch", type=int, default=32)
-    ap.add_argument("--micro-batch", type=int, default=16)
+    ap.add_argument("--micro-batch", type=int, default=32)
     ap.add_argument("--action-ffn", type=int, default=2048, help="action expert FFN width (not in the reference repo)")
     ap.add_argument("--transport", default="auto", choices=["auto", "dist", "symm"])
     ap.add_argument("--layers", type=int, default=0, help="debug only: override depth (invalidates the number)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--kernel-table", default="", help="after the timed runs, trace one more step and write per-kernel time shares here")
     return ap.parse_args()
 
 
@@ -267,8 +268,36 @@ def main():
                           "h2d_bytes_per_step": int(bi), "d2h_bytes_per_step": int(bo),
                           "ms_per_step": round(ms_e2e_max / args.steps, 3)}
         print(json.dumps(rec), flush=True)
+    if args.kernel_table and rank == 0:
+        write_kernel_table(args.kernel_table, lambda: train_step(resident[0]))
     if world > 1:
         dist.destroy_process_group()
+
+
+def write_kernel_table(path, step_fn):
+    """Trace ONE extra step (outside every timed region) and write each kernel's share of the
+    device time. Shares only: absolute times under the tracer are not benchmark numbers."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        step_fn()
+        torch.cuda.synchronize()
+    rows = []
+    for ev in prof.key_averages():
+        t = getattr(ev, "self_device_time_total", None)
+        if t is None:
+            t = getattr(ev, "self_cuda_time_total", 0.0)
+        if t > 0:
+            rows.append((ev.key, int(ev.count), float(t)))
+    rows.sort(key=lambda r: -r[2])
+    total = sum(r[2] for r in rows) or 1.0
+    os.makedirs(os.path.dirname(os.path.abspath(path)) or ".", exist_ok=True)
+    with open(path, "w") as f:
+        f.write(f"# one training step, kernel time shares (sum of kernel time {total / 1e3:.1f} ms under the tracer)\n")
+        f.write(f"# {'share':>6} {'ms':>9} {'calls':>6}  kernel\n")
+        for name, n, t in rows[:60]:
+            f.write(f"  {100 * t / total:6.2f} {t / 1e3:9.3f} {n:6d}  {name[:150]}\n")
 
 
 if __name__ == "__main__":

@@ -59,14 +59,21 @@ rs_reduce_kernel(PeerPtrs grads, const ShardDesc* __restrict__ table, int world,
   for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
        i += static_cast<long>(gridDim.x) * blockDim.x) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll 1
-    for (int r = 0; r < world; ++r) {
-      const BF8 x = reinterpret_cast<const BF8*>(reinterpret_cast<const __nv_bfloat16*>(grads.p[r]) + d.arena_off)[i];
+    // all ranks' loads are issued before the first add (peer loads have microseconds of latency)
+    BF8 x[kMaxPeers];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 f = __bfloat1622float2(x.v[e]);
-        acc[2 * e] += f.x;
-        acc[2 * e + 1] += f.y;
+    for (int r = 0; r < kMaxPeers; ++r)
+      if (r < world)
+        x[r] = reinterpret_cast<const BF8*>(reinterpret_cast<const __nv_bfloat16*>(grads.p[r]) + d.arena_off)[i];
+#pragma unroll
+    for (int r = 0; r < kMaxPeers; ++r) {
+      if (r < world) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(x[r].v[e]);
+          acc[2 * e] += f.x;
+          acc[2 * e + 1] += f.y;
+        }
       }
     }
     float4* o = reinterpret_cast<float4*>(out + d.out_off + i * 8);
@@ -156,13 +163,18 @@ int symm_barrier(const PeerPtrs& flags, int rank, int world, int epoch, int* sta
 int rs_reduce(const PeerPtrs& grads, const ShardDesc* table_dev, int nbuf, int world, float* out, float* sumsq,
               cudaStream_t s) {
   if (nbuf == 0) return 0;
-  rs_reduce_kernel<<<dim3(32, nbuf), 256, 0, s>>>(grads, table_dev, world, out, sumsq);
+  // about 16 resident blocks per SM in total, whatever the number of buffers
+  int gx = (148 * 16 + nbuf - 1) / nbuf;
+  gx = gx < 8 ? 8 : gx;
+  rs_reduce_kernel<<<dim3(gx, nbuf), 256, 0, s>>>(grads, table_dev, world, out, sumsq);
   return static_cast<int>(cudaGetLastError());
 }
 
 int ag_push(const PeerPtrs& params, const ShardDesc* table_dev, int nbuf, int rank, int world, cudaStream_t s) {
   if (nbuf == 0 || world == 1) return 0;
-  ag_push_kernel<<<dim3(32, nbuf), 256, 0, s>>>(params, table_dev, rank, world);
+  int gx = (148 * 16 + nbuf - 1) / nbuf;
+  gx = gx < 8 ? 8 : gx;
+  ag_push_kernel<<<dim3(gx, nbuf), 256, 0, s>>>(params, table_dev, rank, world);
   return static_cast<int>(cudaGetLastError());
 }
 
