@@ -111,9 +111,16 @@ class DataCollator:
             processor.tokenizer.padding_side = "left"
         self.processor = processor
         if self.use_fast_tokenizer and action_tokenizer is None:
-            from transformers import AutoProcessor
+            action_tokenizer = getattr(processor, "action_processor", None)
+        if self.use_fast_tokenizer and action_tokenizer is None:
+            if config.get("action_tokenizer_path"):
+                from transformers import AutoProcessor
 
-            action_tokenizer = AutoProcessor.from_pretrained(config["action_tokenizer_path"], trust_remote_code=True)
+                action_tokenizer = AutoProcessor.from_pretrained(config["action_tokenizer_path"], trust_remote_code=True)
+            else:  # no pretrained FAST tokenizer given: the built-in DCT tokenizer over the same id range
+                from .fast_tokenizer import DctActionTokenizer
+
+                action_tokenizer = DctActionTokenizer(int(processor.tokenizer.init_kwargs["action_token_vocab_size"]))
         self.train_action_tokenizer = action_tokenizer if self.use_fast_tokenizer else None
         self.action_mapper = None
         if self.train_action_tokenizer is not None:

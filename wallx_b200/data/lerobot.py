@@ -201,6 +201,10 @@ class TestDataset(PreprocessedDataset):
     def __init__(self, dataset, config, dataload_config, **kw):
         super().__init__(dataset, config, dataload_config, test_only=True, **kw)
 
+    def get_dataloader(self):
+        """Frames in order, batch size 1, no shuffling (reference: load_lerobot_dataset.py:564-620)."""
+        return DataLoader(self, batch_size=1, shuffle=False, num_workers=0, collate_fn=self._collator())
+
 
 def load_test_dataset(config: Dict, lerobot_config: Dict, seed: int = 42, dataset=None, **kw):
     dataload_config = get_data_configs(config["data"])

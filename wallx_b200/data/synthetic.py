@@ -89,6 +89,27 @@ class SyntheticTokenizer:
     def __len__(self):
         return self._len
 
+    def add_tokens(self, new_tokens) -> int:
+        """Append named tokens after the current vocabulary (consecutive ids); returns how many were new."""
+        added = 0
+        count = self._len - self.action_start if self._len > self.action_start else 0  # FAST ids already present
+        for t in new_tokens:
+            if t in self.special:
+                continue
+            if t.startswith("<|action_token_") and t.endswith("|>"):
+                if int(t[len("<|action_token_"):-2]) < count:
+                    continue
+                if count == 0:
+                    self.action_start = self._len
+                count += 1
+            else:
+                if count:
+                    raise ValueError("named tokens must be added before the FAST id range")
+                self.special[t] = self._len
+            self._len += 1
+            added += 1
+        return added
+
     def convert_tokens_to_ids(self, token):
         if isinstance(token, (list, tuple)):
             return [self.convert_tokens_to_ids(t) for t in token]
@@ -185,7 +206,7 @@ class SyntheticImageProcessor:
 
         pvs, grids = [], []
         for im in images or []:
-            arr = torch.as_tensor(np.array(im))
+            arr = im if torch.is_tensor(im) else torch.as_tensor(np.array(im))
             if arr.dim() == 3 and arr.shape[0] == 3 and arr.shape[-1] != 3:
                 arr = arr.permute(1, 2, 0)
             if arr.dtype != torch.uint8:
@@ -206,6 +227,56 @@ class SyntheticProcessor:
     def batch_decode(self, batch, **kw):
         return self.tokenizer.batch_decode(batch, **kw)
 
+    def apply_chat_template(self, messages, tokenize: bool = False, add_generation_prompt: bool = True) -> str:
+        """Qwen chat layout: ``<|im_start|>role\n ... <|im_end|>\n`` with one vision span per image item."""
+        out = []
+        for m in messages:
+            out.append(f"<|im_start|>{m['role']}\n")
+            content = m["content"]
+            if isinstance(content, str):
+                out.append(content)
+            else:
+                for item in content:
+                    if item.get("type") == "image":
+                        out.append("<|vision_start|><|image_pad|><|vision_end|>")
+                    elif item.get("type") == "text":
+                        out.append(item["text"])
+            out.append("<|im_end|>\n")
+        if add_generation_prompt:
+            out.append("<|im_start|>assistant\n")
+        text = "".join(out)
+        return self.tokenizer.encode(text) if tokenize else text
+
+    def __call__(self, text=None, images=None, return_tensors="pt", padding=True, **kw):
+        """Image patches + tokenised text with every ``<|image_pad|>`` expanded to its image's token count."""
+        texts = [text] if isinstance(text, str) else list(text)
+        out = {}
+        if images:
+            img = self.image_processor(images=images, return_tensors=return_tensors)
+            out.update(img)
+            merge2 = self.image_processor.merge_size ** 2
+            counts = [int(g.prod()) // merge2 for g in img["image_grid_thw"]]
+            k = 0
+            expanded = []
+            for t in texts:
+                while "<|image_pad|>" in t and k < len(counts):
+                    t = t.replace("<|image_pad|>", "<|placeholder|>" * counts[k], 1)
+                    k += 1
+                expanded.append(t.replace("<|placeholder|>", "<|image_pad|>"))
+            texts = expanded
+        out.update(self.tokenizer(texts, return_tensors=return_tensors, padding=padding))
+        return out
+
+    def save_pretrained(self, directory: str) -> None:
+        import json
+        import os
+
+        os.makedirs(directory, exist_ok=True)
+        tok = self.tokenizer
+        with open(os.path.join(directory, "synthetic_tokenizer.json"), "w") as f:
+            json.dump({"base_vocab": tok.base_vocab, "special": tok.special, "init_kwargs": tok.init_kwargs,
+                       "length": len(tok), "padding_side": tok.padding_side}, f, indent=1)
+
 
 def make_processor(config: Qwen2_5_VLConfig, action_vocab: int) -> SyntheticProcessor:
     """Tokenizer whose length equals ``config.vocab_size`` (base + <|propri|> + <|action|> + FAST ids)."""
@@ -213,7 +284,12 @@ def make_processor(config: Qwen2_5_VLConfig, action_vocab: int) -> SyntheticProc
     tok = SyntheticTokenizer(base, action_vocab, config.image_token_id, config.video_token_id,
                              config.vision_start_token_id, config.vision_end_token_id,
                              pad_token_id=config.pad_token_id if config.pad_token_id is not None else 0)
-    return SyntheticProcessor(tok)
+    proc = SyntheticProcessor(tok)
+    if action_vocab >= 3:
+        from .fast_tokenizer import DctActionTokenizer
+
+        proc.action_processor = DctActionTokenizer(action_vocab)
+    return proc
 
 
 def _text_ids(n: int, hi: int, forbidden: Sequence[int], gen: torch.Generator) -> torch.Tensor:

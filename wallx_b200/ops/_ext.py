@@ -73,7 +73,13 @@ def build(verbose: bool = False):
 def _load_prebuilt():
     path = so_path()
     if not os.path.exists(path):
-        return None
+        # a `setup.py build_ext --inplace` build carries the interpreter tag in its file name
+        import glob
+
+        tagged = sorted(glob.glob(os.path.join(BUILD_DIR, EXT_NAME + ".*.so")))
+        if not tagged:
+            return None
+        path = tagged[-1]
     import torch  # noqa: F401  (libtorch symbols must be loaded first)
 
     spec = importlib.util.spec_from_file_location(EXT_NAME, path)
@@ -112,7 +118,7 @@ class LaunchCounter:
     """Counts kernel launches issued through the extension (each binding knows how many kernels it
     launches). Used by the benchmark to report how many of our kernels ran in the timed region."""
 
-    PER_CALL = {"rms_norm_bwd": 2, "column_sum": 2}
+    PER_CALL = {"rms_norm_bwd": 2, "column_sum": 2}  # gemm_ag: one kernel (copy CTAs are part of its grid)
 
     def __init__(self, mod):
         self._mod = mod
