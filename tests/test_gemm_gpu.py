@@ -25,7 +25,7 @@ def _check(out, ref, K):
 
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (200, 328, 136), (1000, 1280, 1176), (64, 40, 2048)])
-@pytest.mark.parametrize("bn", [0, 64, 128, 256])
+@pytest.mark.parametrize("bn", [0, 64, 128, 256, 512])  # 512 = CTA pairs, 256 x 256 tiles
 def test_layouts(a_mn, b_mn, M, N, K, bn):
     from wallx_b200.ops import gemm as G
 
@@ -120,6 +120,52 @@ def test_k_offset_segment_reduction():
     G.launch([G.GemmSpec(dy[: k0 + K], x[: k0 + K], out, a_mn=True, b_mn=True, K=K, k0=k0, flags=G.OUT_FP32)])
     ref = dy[k0:k0 + K].float().t() @ x[k0:k0 + K].float()
     _check(out, ref, K)
+    G.check_status()
+
+
+# --------------------------------------------------------------------------- CTA-pair kernel
+def test_pair_kernel_epilogues_and_groups():
+    """256 x 256 tiles over CTA pairs: every epilogue, two problems with device-side segments, the
+    zero-fill of pad rows that must stop at the 128-row boundary of a segment, many tiles per pair."""
+    from wallx_b200.ops import gemm as G
+
+    M, N, K = 700, 640, 320
+    a, b = _mk((M, K), 3), _mk((N, K), 4, 0.1)
+    bias, res = _mk((N,), 5), _mk((M, N), 6)
+    ref = a.float() @ b.float().t()
+    _check(G.gemm(a, b, bias=bias, force_bn=512), ref + bias.float(), K)
+    _check(G.gemm(a, b, bias=bias, flags=G.ACT_GELU, force_bn=512), torch.nn.functional.gelu(ref + bias.float()), K)
+    _check(G.gemm(a, b, residual=res, force_bn=512), ref + res.float(), K)
+    acc = torch.ones((M, N), device="cuda", dtype=torch.float32)
+    G.gemm(a, b, out=acc, flags=G.OUT_FP32 | G.ACCUMULATE, force_bn=512)
+    _check(acc, ref + 1.0, K)
+    # two experts, segments at 128-aligned starts, zero padding only up to the next 128 boundary
+    K2, I0, I1 = 256, 192, 64
+    M0, M1 = 300, 100           # expert 0 rows [0, 300) padded to 384; expert 1 starts at 384
+    T = 384 + 128
+    x = _mk((T, K2), 10)
+    w0, w1 = _mk((2 * I0, K2), 11, 0.1), _mk((2 * I1, K2), 12, 0.1)
+    h = torch.full((T, I0), 7.0, device="cuda", dtype=torch.bfloat16)
+    dyn0 = torch.tensor([0, M0, 0, K2], dtype=torch.int32, device="cuda")
+    dyn1 = torch.tensor([384, M1, 0, K2], dtype=torch.int32, device="cuda")
+    G.launch([G.GemmSpec(x, w0, h, M=T, dyn=dyn0, flags=G.ACT_SWIGLU | G.ZERO_PAD_ROWS),
+              G.GemmSpec(x, w1, h, M=T, dyn=dyn1, flags=G.ACT_SWIGLU | G.ZERO_PAD_ROWS)], force_bn=512)
+
+    def swiglu(xx, w):
+        z = (xx.float() @ w.float().t()).bfloat16().float().view(xx.shape[0], -1, 2, 16)
+        return (torch.nn.functional.silu(z[:, :, 0]) * z[:, :, 1]).reshape(xx.shape[0], -1)
+
+    _check(h[:M0], swiglu(x[:M0], w0), K2)
+    assert (h[M0:384] == 0).all()                       # pad rows of expert 0
+    _check(h[384:384 + M1, :I1], swiglu(x[384:384 + M1], w1), K2)
+    assert (h[384 + M1:512, :I1] == 0).all()            # pad rows of expert 1
+    assert (h[384:, I1:] == 7.0).all()                  # columns expert 1 does not own are untouched
+    # many tiles per pair + wgrad layout with fp32 accumulation
+    dy, xx = _mk((4096, 1536), 13, 0.1), _mk((4096, 1024), 14)
+    dw = torch.zeros((1536, 1024), device="cuda", dtype=torch.float32)
+    G.launch([G.GemmSpec(dy, xx, dw, a_mn=True, b_mn=True, flags=G.OUT_FP32 | G.ACCUMULATE)], force_bn=512)
+    _check(dw, dy.float().t() @ xx.float(), 4096)
+    torch.cuda.synchronize()
     G.check_status()
 
 

@@ -38,7 +38,7 @@ def _bf(*shape, scale=1.0):
 
 # Each case returns (fn, kernel_regex, bytes, flops, note). bytes / flops are algorithmic (one
 # read of every input, one write of every output).
-def case_gemm(M, N, K, a_mn=False, b_mn=False, flags=0, extra=None):
+def case_gemm(M, N, K, a_mn=False, b_mn=False, flags=0, extra=None, force_bn=0):
     def build():
         from wallx_b200.ops import gemm as G
 
@@ -55,7 +55,8 @@ def case_gemm(M, N, K, a_mn=False, b_mn=False, flags=0, extra=None):
             kw["residual"] = _bf(M, N)
             nbytes += M * N * 2
         spec = G.GemmSpec(a, b, out, a_mn=a_mn, b_mn=b_mn, flags=flags, **kw)
-        return (lambda: G.launch([spec])), "gemm_kernel", nbytes, 2.0 * M * N * K, f"M={M} N={N} K={K} a_mn={a_mn} b_mn={b_mn}"
+        name = "gemm_pair_kernel" if force_bn == 512 else "gemm_kernel"
+        return (lambda: G.launch([spec], force_bn)), name, nbytes, 2.0 * M * N * K, f"M={M} N={N} K={K} a_mn={a_mn} b_mn={b_mn}"
     return build
 
 
@@ -261,6 +262,12 @@ CASES = {
     "gemm_dgrad": case_gemm(16384, 2048, 22016, b_mn=True),
     "gemm_wgrad_fp32_accumulate": case_gemm(22016, 2048, 16384, a_mn=True, b_mn=True, flags=3),
     "gemm_vit_qkv": case_gemm(62208, 3840, 1280),
+    "gemm_qkv_pair": case_gemm(16384, 2560, 2048, force_bn=512),
+    "gemm_gate_up_swiglu_pair": case_gemm(16384, 22016, 2048, flags=8, extra="swiglu_raw", force_bn=512),
+    "gemm_down_residual_pair": case_gemm(16384, 2048, 11008, extra="residual", force_bn=512),
+    "gemm_dgrad_pair": case_gemm(16384, 2048, 22016, b_mn=True, force_bn=512),
+    "gemm_wgrad_fp32_accumulate_pair": case_gemm(22016, 2048, 16384, a_mn=True, b_mn=True, flags=3, force_bn=512),
+    "gemm_vit_qkv_pair": case_gemm(62208, 3840, 1280, force_bn=512),
     "gemm_dual_expert": case_gemm_dual,
     "gemm_gathered_weight": case_gemm_gathered,
     "attn_llm_fwd": case_attn_llm("fwd"),

@@ -61,6 +61,8 @@ struct GemmArgs {
 constexpr int kAgRing = 12;          // 16 KB buffers in the (otherwise unused) stage area of a puller CTA
 constexpr int kAgChunkMax = 16384;
 constexpr int kAgDepth = kAgRing - 2;  // loads in flight
+constexpr int kAgLag = 3;               // store groups that may still be in flight behind a published tile
+constexpr int kAgPend = 8;              // tiles waiting for their stores' completion (power of two)
 
 template <int BN>
 struct Cfg {
@@ -80,7 +82,7 @@ struct Dims {
   int M[2], K[2], m0[2], k0[2], tiles_m[2], tiles_n[2], tiles[2];
 };
 
-template <int BN>
+template <int BN, int TM = BM>
 __device__ __forceinline__ void load_dims(const GemmArgs& args, Dims& d) {
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -98,7 +100,7 @@ __device__ __forceinline__ void load_dims(const GemmArgs& args, Dims& d) {
       d.K[i] = K;
       d.m0[i] = m0;
       d.k0[i] = k0;
-      d.tiles_m[i] = (M + BM - 1) / BM;
+      d.tiles_m[i] = (M + TM - 1) / TM;
       d.tiles_n[i] = (p.N + BN - 1) / BN;
       d.tiles[i] = (K > 0) ? d.tiles_m[i] * d.tiles_n[i] : 0;
     } else {
@@ -130,6 +132,144 @@ __device__ __forceinline__ TileInfo decode_tile(const Dims& d, int t, int rot0 =
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
+// Epilogue of one warp for one output tile: the warp's 32 accumulator rows (TMEM lanes of its
+// quarter, BN fp32 columns starting at taddr0) go through bias / activation / residual / row map /
+// accumulate and are stored. `row_in_prob` is this thread's row within the problem.
+template <int BN>
+__device__ __forceinline__ void epilogue_rows(const Problem& p, int M, int m0, int row_in_prob, int n_base,
+                                              uint32_t taddr0) {
+  const bool row_ok = row_in_prob < M;
+  long drow = static_cast<long>(m0) + row_in_prob;
+  // Rows between M and the end of the 128-row tile are zero-filled on request, so that a
+  // 128-aligned token segment can later be reduced over without reading garbage.
+  // (A 256-row pair tile can reach past that boundary into the next segment: those rows are left alone.)
+  const bool zero_row = !row_ok && (p.flags & GEMM_ZERO_PAD_ROWS) != 0 && p.row_map == nullptr &&
+                        row_in_prob < ((M + BM - 1) & ~(BM - 1));
+  bool store_ok = row_ok || zero_row;
+  if (row_ok && p.row_map != nullptr) {
+    const int r = p.row_map[drow];
+    store_ok = r >= 0;
+    drow = r;
+  }
+  const int flags = p.flags;
+  const bool swiglu = (flags & GEMM_ACT_SWIGLU) != 0;
+  const bool out_fp32 = (flags & GEMM_OUT_FP32) != 0;
+  const bool accum = (flags & GEMM_ACCUMULATE) != 0 && !zero_row;
+
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32(taddr0 + c * 32, r);
+    tmem_ld_wait();
+    const int n0 = n_base + c * 32;
+    if (!store_ok || n0 >= p.N) continue;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = zero_row ? 0.f : __uint_as_float(r[j]);
+    const int nvalid = min(32, p.N - n0);
+    if (p.bias != nullptr && !zero_row) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < nvalid) v[j] += __bfloat162float(p.bias[n0 + j]);
+    }
+    if (swiglu) {
+      // columns [n0, n0+16) are gate, [n0+16, n0+32) are up; N is a multiple of 32 here.
+      if (p.D2 != nullptr) {
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D2) + drow * p.ldd2 + n0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          dst[q] = make_uint4(pack_bf16x2(v[8 * q + 0], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                              pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+      }
+      float h[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        // round gate and up to bf16 first so that the result equals the unfused path
+        const float g = __bfloat162float(__float2bfloat16(v[j]));
+        const float u = __bfloat162float(__float2bfloat16(v[16 + j]));
+        h[j] = silu_f(g) * u;
+      }
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + drow * p.ldd + (n0 >> 1));
+#pragma unroll
+      for (int q = 0; q < 2; ++q)
+        dst[q] = make_uint4(pack_bf16x2(h[8 * q + 0], h[8 * q + 1]), pack_bf16x2(h[8 * q + 2], h[8 * q + 3]),
+                            pack_bf16x2(h[8 * q + 4], h[8 * q + 5]), pack_bf16x2(h[8 * q + 6], h[8 * q + 7]));
+      continue;
+    }
+    if (flags & GEMM_ACT_GELU) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+    }
+    if (p.residual != nullptr && !zero_row) {
+      const __nv_bfloat16* rs = p.residual + drow * p.ldr + n0;
+      if (nvalid == 32 && (p.ldr & 7) == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0) {
+        const uint4* rs4 = reinterpret_cast<const uint4*>(rs);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 x = rs4[q];
+          const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(xb[e]);
+            v[8 * q + 2 * e] += f.x;
+            v[8 * q + 2 * e + 1] += f.y;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < nvalid) v[j] += __bfloat162float(rs[j]);
+      }
+    }
+    if (out_fp32) {
+      float* dst = reinterpret_cast<float*>(p.D) + drow * p.ldd + n0;
+      if (nvalid == 32 && (p.ldd & 3) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15) == 0) {
+        float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          if (accum) {
+            const float4 old = d4[q];
+            o.x += old.x;
+            o.y += old.y;
+            o.z += old.z;
+            o.w += old.w;
+          }
+          d4[q] = o;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < nvalid) dst[j] = accum ? dst[j] + v[j] : v[j];
+      }
+    } else {
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.D) + drow * p.ldd + n0;
+      if (nvalid == 32 && (p.ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15) == 0) {
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (accum) {
+            const uint4 x = d4[q];
+            const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = __bfloat1622float2(xb[e]);
+              v[8 * q + 2 * e] += f.x;
+              v[8 * q + 2 * e + 1] += f.y;
+            }
+          }
+          d4[q] = make_uint4(pack_bf16x2(v[8 * q + 0], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                             pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < nvalid) dst[j] = __float2bfloat16(accum ? __bfloat162float(dst[j]) + v[j] : v[j]);
+      }
+    }
+  }
+}
+
 // Copies the weight tiles from the ranks that own them into this GPU's staging buffer; run by one
 // thread of a puller CTA. Global -> shared by bulk copy (mbarrier completion), shared -> global by
 // bulk store (bulk-group completion), kAgDepth loads in flight. All pullers share every tile
@@ -153,6 +293,9 @@ __device__ bool ag_pull(const AgDev& ag, int q, uint8_t* ring, uint64_t* bars, v
   int issued = seq, stored = seq;  // chunk sequence numbers of this puller (all stores up to seq are complete)
   int lbuf = seq % kAgRing, sbuf = lbuf;
   uint32_t sphase = (seq / kAgRing) & 1u;
+  // tiles whose last store has been issued but not yet confirmed complete
+  int pend_tile[kAgPend], pend_seq[kAgPend];
+  int pend_head = 0, pend_n = 0;
   AgCursor L{0, q, 0, 0}, S{0, q, 0, 0};
   ag_enter(ag, L);
   ag_enter(ag, S);
@@ -185,10 +328,30 @@ __device__ bool ag_pull(const AgDev& ag, int q, uint8_t* ring, uint64_t* bars, v
         sphase ^= 1u;
       }
       S.i += np;
-      if (S.i >= S.n) {  // last chunk of this puller in the tile: publish
-        bulk_store_wait_all();
+      // tiles whose stores are certainly complete: kAgLag or more groups were committed after theirs
+      if (pend_n > 0 && stored - pend_seq[pend_head] >= kAgLag) {
+        bulk_store_wait<kAgLag>();
         fence_proxy_async_global();
-        red_release_gpu_add(&ag.flags[S.nt], 1);
+        while (pend_n > 0 && stored - pend_seq[pend_head] >= kAgLag) {
+          red_release_gpu_add(&ag.flags[pend_tile[pend_head]], 1);
+          pend_head = (pend_head + 1) & (kAgPend - 1);
+          --pend_n;
+        }
+      }
+      if (S.i >= S.n) {  // last chunk of this puller in the tile: publish once its stores have landed
+        if (pend_n == kAgPend) {  // queue full: drain
+          bulk_store_wait_all();
+          fence_proxy_async_global();
+          while (pend_n > 0) {
+            red_release_gpu_add(&ag.flags[pend_tile[pend_head]], 1);
+            pend_head = (pend_head + 1) & (kAgPend - 1);
+            --pend_n;
+          }
+        }
+        const int slot = (pend_head + pend_n) & (kAgPend - 1);
+        pend_tile[slot] = S.nt;
+        pend_seq[slot] = stored;
+        ++pend_n;
         S.i = q;
         if (++S.j < ag.ntiles) ag_enter(ag, S);
         else S.n = 0x7fffffff;  // nothing left: the store side is only entered again with a loaded chunk
@@ -208,7 +371,13 @@ __device__ bool ag_pull(const AgDev& ag, int q, uint8_t* ring, uint64_t* bars, v
     L.i += np;
   }
   bulk_store_wait_all();
+  fence_proxy_async_global();
   if (ok) {
+    while (pend_n > 0) {
+      red_release_gpu_add(&ag.flags[pend_tile[pend_head]], 1);
+      pend_head = (pend_head + 1) & (kAgPend - 1);
+      --pend_n;
+    }
     // trailing tiles without a chunk of this puller
     while (S.j < ag.ntiles) {
       if (S.n != 0x7fffffff) red_release_gpu_add(&ag.flags[S.nt], 1);
@@ -415,137 +584,8 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
       if (!mbar_wait(&tfull_bar[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
 
-      const int row_in_prob = ti.mt * BM + quarter * 32 + lane;
-      const bool row_ok = row_in_prob < d.M[ti.prob];
-      long drow = static_cast<long>(d.m0[ti.prob]) + row_in_prob;
-      // Rows between M and the end of the 128-row tile are zero-filled on request, so that a
-      // 128-aligned token segment can later be reduced over without reading garbage.
-      const bool zero_row = !row_ok && (p.flags & GEMM_ZERO_PAD_ROWS) != 0 && p.row_map == nullptr;
-      bool store_ok = row_ok || zero_row;
-      if (row_ok && p.row_map != nullptr) {
-        const int r = p.row_map[drow];
-        store_ok = r >= 0;
-        drow = r;
-      }
-      const int flags = p.flags;
-      const bool swiglu = (flags & GEMM_ACT_SWIGLU) != 0;
-      const bool out_fp32 = (flags & GEMM_OUT_FP32) != 0;
-      const bool accum = (flags & GEMM_ACCUMULATE) != 0 && !zero_row;
-      const int n_base = ti.nt * BN;
-      const uint32_t taddr0 = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr0 + c * 32, r);
-        tmem_ld_wait();
-        const int n0 = n_base + c * 32;
-        if (!store_ok || n0 >= p.N) continue;
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = zero_row ? 0.f : __uint_as_float(r[j]);
-        const int nvalid = min(32, p.N - n0);
-        if (p.bias != nullptr && !zero_row) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j < nvalid) v[j] += __bfloat162float(p.bias[n0 + j]);
-        }
-        if (swiglu) {
-          // columns [n0, n0+16) are gate, [n0+16, n0+32) are up; N is a multiple of 32 here.
-          if (p.D2 != nullptr) {
-            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D2) + drow * p.ldd2 + n0);
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              dst[q] = make_uint4(pack_bf16x2(v[8 * q + 0], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
-                                  pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
-          }
-          float h[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            // round gate and up to bf16 first so that the result equals the unfused path
-            const float g = __bfloat162float(__float2bfloat16(v[j]));
-            const float u = __bfloat162float(__float2bfloat16(v[16 + j]));
-            h[j] = silu_f(g) * u;
-          }
-          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + drow * p.ldd + (n0 >> 1));
-#pragma unroll
-          for (int q = 0; q < 2; ++q)
-            dst[q] = make_uint4(pack_bf16x2(h[8 * q + 0], h[8 * q + 1]), pack_bf16x2(h[8 * q + 2], h[8 * q + 3]),
-                                pack_bf16x2(h[8 * q + 4], h[8 * q + 5]), pack_bf16x2(h[8 * q + 6], h[8 * q + 7]));
-          continue;
-        }
-        if (flags & GEMM_ACT_GELU) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
-        }
-        if (p.residual != nullptr && !zero_row) {
-          const __nv_bfloat16* rs = p.residual + drow * p.ldr + n0;
-          if (nvalid == 32 && (p.ldr & 7) == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0) {
-            const uint4* rs4 = reinterpret_cast<const uint4*>(rs);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint4 x = rs4[q];
-              const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&x);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 f = __bfloat1622float2(xb[e]);
-                v[8 * q + 2 * e] += f.x;
-                v[8 * q + 2 * e + 1] += f.y;
-              }
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < nvalid) v[j] += __bfloat162float(rs[j]);
-          }
-        }
-        if (out_fp32) {
-          float* dst = reinterpret_cast<float*>(p.D) + drow * p.ldd + n0;
-          if (nvalid == 32 && (p.ldd & 3) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15) == 0) {
-            float4* d4 = reinterpret_cast<float4*>(dst);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-              if (accum) {
-                const float4 old = d4[q];
-                o.x += old.x;
-                o.y += old.y;
-                o.z += old.z;
-                o.w += old.w;
-              }
-              d4[q] = o;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < nvalid) dst[j] = accum ? dst[j] + v[j] : v[j];
-          }
-        } else {
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.D) + drow * p.ldd + n0;
-          if (nvalid == 32 && (p.ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15) == 0) {
-            uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              if (accum) {
-                const uint4 x = d4[q];
-                const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&x);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const float2 f = __bfloat1622float2(xb[e]);
-                  v[8 * q + 2 * e] += f.x;
-                  v[8 * q + 2 * e + 1] += f.y;
-                }
-              }
-              d4[q] = make_uint4(pack_bf16x2(v[8 * q + 0], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
-                                 pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < nvalid) dst[j] = __float2bfloat16(accum ? __bfloat162float(dst[j]) + v[j] : v[j]);
-          }
-        }
-      }
+      epilogue_rows<BN>(p, d.M[ti.prob], d.m0[ti.prob], ti.mt * BM + quarter * 32 + lane, ti.nt * BN,
+                        tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16));
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
@@ -679,6 +719,12 @@ int fill_args(GemmArgs& args, const GemmCall* calls, int ncalls, int bn) {
 
 }  // namespace
 
+}  // namespace wx
+
+#include "gemm2.cuh"
+
+namespace wx {
+
 int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* status, int force_bn) {
   if (ncalls < 1 || ncalls > 2) return -1;
   const bool a_mn = calls[0].a_mn, b_mn = calls[0].b_mn;
@@ -695,9 +741,10 @@ int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* sta
   // Tile width: minimise (number of waves) x (time of one tile); per-width MMA efficiency measured
   // on B200 (BN 256 / 128 / 64 reach about 1260 / 970 / 525 TFLOP/s with every SM busy).
   int bn = 64;
+  bool use_pair = force_bn == 512;
   if (force_bn == 64 || force_bn == 128 || force_bn == 256) {
     bn = force_bn;
-  } else {
+  } else if (!use_pair) {
     int max_n = 0;
     for (int i = 0; i < ncalls; ++i) max_n = calls[i].N > max_n ? calls[i].N : max_n;
     const int widths[3] = {256, 128, 64};
@@ -714,9 +761,32 @@ int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* sta
         bn = widths[w];
       }
     }
+    // CTA pairs (256 x 256 tiles, one per two SMs): same work per SM and tile as the 128 x 256
+    // kernel at about 1.08x its rate; chosen when its wave count does not eat that up.
+    if (max_n > 128) {
+      long pt = 0;
+      for (int i = 0; i < ncalls; ++i)
+        pt += static_cast<long>((calls[i].M + 255) / 256) * ((calls[i].N + 255) / 256);
+      const long pairs = sms / 2;
+      const long pwaves = (pt + pairs - 1) / pairs;
+      const double pcost = static_cast<double>(pwaves) * 256 / 1360.0;
+      if (pcost < best) use_pair = true;
+    }
   }
   for (int i = 0; i < ncalls; ++i)
     if ((calls[i].flags & GEMM_ACT_SWIGLU) && (calls[i].N % 32 != 0)) return -3;
+
+  if (use_pair) {  // CTA pairs: 256 x 256 tiles
+    GemmArgs pargs;
+    const int prc = fill_args(pargs, calls, ncalls, 128);
+    if (prc != 0) return prc;
+    long ptiles = 0;
+    for (int i = 0; i < ncalls; ++i)
+      ptiles += static_cast<long>((calls[i].M + 255) / 256) * ((calls[i].N + 255) / 256);
+    if (ptiles <= 0) return 0;
+    const int prc2 = launch_pair(pargs, a_mn, b_mn, ptiles, stream, status);
+    if (prc2 != -10 || force_bn == 512) return prc2;  // -10: clusters cannot be scheduled here -> single-CTA kernel
+  }
 
   GemmArgs args;
   const int rc = fill_args(args, calls, ncalls, bn);
@@ -740,7 +810,7 @@ int gemm_ag_launch(const GemmCall* calls, const AgInfo* ags, int ncalls, cudaStr
   const int rc = fill_args(args, calls, ncalls, 256);
   if (rc != 0) return rc;
   const int sms = num_sms();
-  int np = ags[0].n_pullers > 0 ? ags[0].n_pullers : 12;
+  int np = ags[0].n_pullers > 0 ? ags[0].n_pullers : 16;
   if (np > sms / 2) np = sms / 2;
   long tiles = 0;
   for (int i = 0; i < ncalls; ++i) {
