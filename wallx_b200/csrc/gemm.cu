@@ -4,7 +4,8 @@
 //   warp 0      TMA producer   (one lane): global -> 128B-swizzled shared-memory stages
 //   warp 1      MMA issuer     (one lane): tcgen05.mma 128 x BN x 16 per instruction, fp32
 //                                          accumulators in tensor memory, double buffered
-//   warps 2..5  epilogue       (128 thr):  tcgen05.ld -> bias / GELU / SwiGLU / residual /
+//   warps 2..9  epilogue       (256 thr):  tcgen05.ld -> bias / GELU / SwiGLU / residual /   (two warps per
+//                                          TMEM lane quarter, half of the tile's columns each)
 //                                          row scatter / accumulate -> global
 // The producer, the issuer and the epilogue are decoupled by mbarriers, so the epilogue of tile
 // i overlaps the main loop of tile i+1. All four operand layouts are handled with UMMA
@@ -24,7 +25,8 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;  // TMA warp, MMA warp, 8 epilogue warps (two per TMEM lane quarter)
+constexpr int kEpiWarps = 8;
 constexpr int kEpiWarp0 = 2;
 
 struct Problem {
@@ -134,10 +136,11 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)
 
 // Epilogue of one warp for one output tile: the warp's 32 accumulator rows (TMEM lanes of its
 // quarter, BN fp32 columns starting at taddr0) go through bias / activation / residual / row map /
-// accumulate and are stored. `row_in_prob` is this thread's row within the problem.
+// accumulate and are stored. `row_in_prob` is this thread's row within the problem; the warp
+// handles the 32-column chunks [chunk0, chunk1) (two warps share a lane quarter).
 template <int BN>
 __device__ __forceinline__ void epilogue_rows(const Problem& p, int M, int m0, int row_in_prob, int n_base,
-                                              uint32_t taddr0) {
+                                              uint32_t taddr0, int chunk0, int chunk1) {
   const bool row_ok = row_in_prob < M;
   long drow = static_cast<long>(m0) + row_in_prob;
   // Rows between M and the end of the 128-row tile are zero-filled on request, so that a
@@ -157,7 +160,7 @@ __device__ __forceinline__ void epilogue_rows(const Problem& p, int M, int m0, i
   const bool accum = (flags & GEMM_ACCUMULATE) != 0 && !zero_row;
 
 #pragma unroll 1
-  for (int c = 0; c < BN / 32; ++c) {
+  for (int c = chunk0; c < chunk1; ++c) {
     uint32_t r[32];
     tmem_ld_32x32(taddr0 + c * 32, r);
     tmem_ld_wait();
@@ -443,7 +446,7 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
       }
       for (int a = 0; a < 2; ++a) {
         mbar_init(&tfull_bar[a], 1);
-        mbar_init(&tempty_bar[a], 4);
+        mbar_init(&tempty_bar[a], kEpiWarps);
       }
     }
     *abort_flag = 0;
@@ -575,6 +578,10 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
   } else {
     // ------------------------------------------------------------------ epilogue
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    const int half = (warp - kEpiWarp0) >> 2;  // which half of the tile's columns
+    constexpr int kChunks = BN / 32;
+    const int chunk0 = (kChunks >= 2) ? half * (kChunks / 2) : 0;
+    const int chunk1 = (kChunks >= 2) ? chunk0 + kChunks / 2 : (half == 0 ? 1 : 0);
     int it = 0;
     for (int t = cta; t < total_tiles; t += ncta, ++it) {
       const TileInfo ti = decode_tile(d, t, rot0, rot1);
@@ -585,7 +592,7 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
       tc_fence_after();
 
       epilogue_rows<BN>(p, d.M[ti.prob], d.m0[ti.prob], ti.mt * BM + quarter * 32 + lane, ti.nt * BN,
-                        tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16));
+                        tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16), chunk0, chunk1);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);

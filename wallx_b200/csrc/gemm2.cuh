@@ -12,8 +12,8 @@
 //     (`.cta_group::2` form of the load, no multicast);
 //   * leader: warp 1 lane 0 waits on `full`, issues the pair MMAs, and commits to the `empty`
 //     barrier of each CTA (two commits; a remote commit uses the peer's shared::cluster address);
-//   * both CTAs: warps 2..5 wait on their own `tfull`, run the same epilogue as the single-CTA
-//     kernel on their 128 rows, and arrive (8 arrivals per tile) on the leader's `tempty`.
+//   * both CTAs: warps 2..9 wait on their own `tfull`, run the same epilogue as the single-CTA
+//     kernel on their 128 rows, and arrive (16 arrivals per tile) on the leader's `tempty`.
 // Every wait is bounded; a CTA that gives up still reaches the final cluster barrier, so its peer
 // is never left signalling a CTA that has exited.
 #pragma once
@@ -53,7 +53,7 @@ gemm_pair_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);   // one commit per tile, in each CTA
-      mbar_init(&tempty_bar[a], 8);  // used in the leader only: 4 epilogue warps of each CTA
+      mbar_init(&tempty_bar[a], 2 * kEpiWarps);  // used in the leader only: the epilogue warps of both CTAs
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -172,6 +172,8 @@ gemm_pair_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status
   } else {
     // ------------------------------------------------------------------ epilogue (both CTAs)
     const int quarter = warp & 3;
+    const int half = (warp - kEpiWarp0) >> 2;  // two warps per lane quarter, half of the columns each
+    const int chunk0 = half * (kPairTileN / 64), chunk1 = chunk0 + kPairTileN / 64;
     int it = 0;
     for (int t = pair; t < total_tiles; t += npair, ++it) {
       const TileInfo ti = decode_tile(d, t);
@@ -183,7 +185,7 @@ gemm_pair_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status
       epilogue_rows<kPairTileN>(p, d.M[ti.prob], d.m0[ti.prob],
                                 ti.mt * kPairTileM + static_cast<int>(rank) * BM + quarter * 32 + lane,
                                 ti.nt * kPairTileN,
-                                tmem_base + acc * kPairTileN + (static_cast<uint32_t>(quarter * 32) << 16));
+                                tmem_base + acc * kPairTileN + (static_cast<uint32_t>(quarter * 32) << 16), chunk0, chunk1);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
