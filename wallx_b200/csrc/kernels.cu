@@ -175,6 +175,110 @@ rms_norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* _
   }
 }
 
+// ------------------------------------------------------------------------------ RMSNorm, one warp per row
+// For C = 256 * CH <= 2048 a warp owns a whole row: CH 16-byte loads per lane are in flight at
+// once and the reduction is shuffles only (no block barrier per row). Eight rows per block.
+template <int CH>
+__global__ void __launch_bounds__(256)
+rms_norm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                         __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, const int* __restrict__ dest,
+                         int T, float eps) {
+  constexpr int C = CH * 256;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const BF8* wr = reinterpret_cast<const BF8*>(w);
+  for (int row = blockIdx.x * 8 + warp; row < T; row += gridDim.x * 8) {
+    const BF8* xr = reinterpret_cast<const BF8*>(x + static_cast<size_t>(row) * C);
+    BF8 raw[CH];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) raw[c] = xr[lane + 32 * c];
+    float v[CH][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      unpack8(raw[c], v[c]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += v[c][e] * v[c][e];
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / static_cast<float>(C) + eps);
+    if (lane == 0) rstd_out[row] = rstd;
+    const int orow = dest ? dest[row] : row;
+    BF8* yr = reinterpret_cast<BF8*>(y + static_cast<size_t>(orow) * C);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      float wf[8], o[8];
+      unpack8(wr[lane + 32 * c], wf);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = wf[e] * bf16_round(v[c][e] * rstd);
+      yr[lane + 32 * c] = pack8(o);
+    }
+  }
+}
+
+template <int CH>
+__global__ void __launch_bounds__(256)
+rms_norm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                         const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
+                         const int* __restrict__ dest, __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial,
+                         int T) {
+  constexpr int C = CH * 256;
+  __shared__ float dws[C];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < C; i += 256) dws[i] = 0.f;
+  __syncthreads();
+  float dwacc[CH][8];
+#pragma unroll
+  for (int c = 0; c < CH; ++c)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dwacc[c][e] = 0.f;
+  const BF8* wr = reinterpret_cast<const BF8*>(w);
+  for (int row = blockIdx.x * 8 + warp; row < T; row += gridDim.x * 8) {
+    const int grow = dest ? dest[row] : row;
+    const BF8* xr = reinterpret_cast<const BF8*>(x + static_cast<size_t>(row) * C);
+    const BF8* gr = reinterpret_cast<const BF8*>(dy + static_cast<size_t>(grow) * C);
+    const float rstd = rstd_in[row];
+    BF8 xraw[CH], graw[CH];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      xraw[c] = xr[lane + 32 * c];
+      graw[c] = gr[lane + 32 * c];
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      float xf[8], df[8], wf[8];
+      unpack8(xraw[c], xf);
+      unpack8(graw[c], df);
+      unpack8(wr[lane + 32 * c], wf);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float xh = xf[e] * rstd;
+        dot += df[e] * wf[e] * xh;
+        dwacc[c][e] += df[e] * bf16_round(xh);
+      }
+    }
+    dot = warp_sum(dot) / static_cast<float>(C);
+    BF8* dxr = reinterpret_cast<BF8*>(dx + static_cast<size_t>(row) * C);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      float xf[8], df[8], wf[8], o[8];
+      unpack8(xraw[c], xf);
+      unpack8(graw[c], df);
+      unpack8(wr[lane + 32 * c], wf);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = rstd * (df[e] * wf[e] - xf[e] * rstd * dot);
+      dxr[lane + 32 * c] = pack8(o);
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < CH; ++c)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) atomicAdd(&dws[(lane + 32 * c) * 8 + e], dwacc[c][e]);
+  __syncthreads();
+  float* dp = dw_partial + static_cast<size_t>(blockIdx.x) * C;
+  for (int i = threadIdx.x; i < C; i += 256) dp[i] = dws[i];
+}
+
 __global__ void reduce_partials_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int nblk,
                                        int C) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -244,15 +348,22 @@ __global__ void rope_qk_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat
   unpack8(*reinterpret_cast<const BF8*>(row + h * D + half + d0), b);
   const float* cs = cos_t + static_cast<size_t>(t) * D;
   const float* sn = sin_t + static_cast<size_t>(t) * D;
+  float c1[8], s1[8], c2[8], s2[8];  // 16-byte loads: d0 is a multiple of 8 floats, rows are 16-byte aligned
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    *reinterpret_cast<float4*>(c1 + 4 * q) = *reinterpret_cast<const float4*>(cs + d0 + 4 * q);
+    *reinterpret_cast<float4*>(s1 + 4 * q) = *reinterpret_cast<const float4*>(sn + d0 + 4 * q);
+    *reinterpret_cast<float4*>(c2 + 4 * q) = *reinterpret_cast<const float4*>(cs + half + d0 + 4 * q);
+    *reinterpret_cast<float4*>(s2 + 4 * q) = *reinterpret_cast<const float4*>(sn + half + d0 + 4 * q);
+  }
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
-    const float c1 = cs[d0 + e], s1 = sn[d0 + e], c2 = cs[half + d0 + e], s2 = sn[half + d0 + e];
     if (!inverse) {
-      oa[e] = a[e] * c1 - b[e] * s1;
-      ob[e] = b[e] * c2 + a[e] * s2;
+      oa[e] = a[e] * c1[e] - b[e] * s1[e];
+      ob[e] = b[e] * c2[e] + a[e] * s2[e];
     } else {
-      oa[e] = a[e] * c1 + b[e] * s2;
-      ob[e] = b[e] * c2 - a[e] * s1;
+      oa[e] = a[e] * c1[e] + b[e] * s2[e];
+      ob[e] = b[e] * c2[e] - a[e] * s1[e];
     }
   }
   *reinterpret_cast<BF8*>(orow + h * D + d0) = pack8(oa);
@@ -541,6 +652,18 @@ int rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, const int* 
                  cudaStream_t s) {
   if (C % 8 != 0 || C > NORM_THREADS * 8 * NORM_MAX_CHUNKS) return -1;
   if (T == 0) return 0;
+  if (C % 256 == 0 && C <= 2048) {  // one warp per row
+    const int g = (T + 7) / 8 < 148 * 8 ? (T + 7) / 8 : 148 * 8;
+    const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+    const __nv_bfloat16* wb = reinterpret_cast<const __nv_bfloat16*>(w);
+    __nv_bfloat16* yb = reinterpret_cast<__nv_bfloat16*>(y);
+    switch (C / 256) {
+#define WX_CASE(n) case n: rms_norm_fwd_warp_kernel<n><<<g, 256, 0, s>>>(xb, wb, yb, rstd, dest, T, eps); break;
+      WX_CASE(1) WX_CASE(2) WX_CASE(3) WX_CASE(4) WX_CASE(5) WX_CASE(6) WX_CASE(7) WX_CASE(8)
+#undef WX_CASE
+    }
+    return static_cast<int>(cudaGetLastError());
+  }
   const int grid = T < 148 * 8 ? T : 148 * 8;
   rms_norm_fwd_kernel<<<grid, NORM_THREADS, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x),
                                                      reinterpret_cast<const __nv_bfloat16*>(w),
@@ -554,6 +677,19 @@ int rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd
                  float* dw_partial, void* dw, int T, int C, cudaStream_t s) {
   if (C % 8 != 0 || C > NORM_THREADS * 8 * NORM_MAX_CHUNKS) return -1;
   const int grid = rms_norm_bwd_blocks(T);
+  if (C % 256 == 0 && C <= 2048) {  // one warp per row; the number of partial rows is the same
+    const __nv_bfloat16* dyb = reinterpret_cast<const __nv_bfloat16*>(dy);
+    const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+    const __nv_bfloat16* wb = reinterpret_cast<const __nv_bfloat16*>(w);
+    __nv_bfloat16* dxb = reinterpret_cast<__nv_bfloat16*>(dx);
+    switch (C / 256) {
+#define WX_CASE(n) case n: rms_norm_bwd_warp_kernel<n><<<grid, 256, 0, s>>>(dyb, xb, wb, rstd, dest, dxb, dw_partial, T); break;
+      WX_CASE(1) WX_CASE(2) WX_CASE(3) WX_CASE(4) WX_CASE(5) WX_CASE(6) WX_CASE(7) WX_CASE(8)
+#undef WX_CASE
+    }
+    reduce_partials_kernel<<<(C + 255) / 256, 256, 0, s>>>(dw_partial, reinterpret_cast<__nv_bfloat16*>(dw), grid, C);
+    return static_cast<int>(cudaGetLastError());
+  }
   rms_norm_bwd_kernel<<<grid, NORM_THREADS, 0, s>>>(
       reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x),
       reinterpret_cast<const __nv_bfloat16*>(w), rstd, dest, reinterpret_cast<__nv_bfloat16*>(dx), dw_partial, T, C);
