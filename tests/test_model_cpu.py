@@ -239,3 +239,37 @@ def test_lora_freezes_base_and_trains_adapters(setup):
     out.loss.backward()
     got = [n for n, p in m.model.named_parameters() if p.requires_grad and p.grad is not None]
     assert len(got) == len(names)
+
+
+def test_flow_engine_matches_predict_on_cpu():
+    """FlowEngine without a graph (CPU): identical to ``predict`` for the same noise; a changed
+    placeholder layout is refused."""
+    import copy
+
+    from wallx_b200.config import tiny_config
+    from wallx_b200.data.collator import add_pack_info
+    from wallx_b200.data.synthetic import make_batch, make_processor
+    from wallx_b200.models import Qwen2_5_VLMoEForAction
+    from wallx_b200.models.inference import FlowEngine
+
+    cfg = tiny_config()
+    proc = make_processor(cfg, 16)
+    torch.manual_seed(0)
+    model = Qwen2_5_VLMoEForAction(cfg, processor=proc).float().eval()
+    batch = make_batch(cfg, proc, 2, views=1, image_hw=(112, 112), prompt_len=16, horizon=8, mode="flow",
+                       generator=torch.Generator().manual_seed(1))
+    inp = {k: v for k, v in batch.items() if k not in ("action_chunk", "labels")}
+    A = model.action_preprocessor.action_dim
+    noise = torch.randn(2, 8, A)
+    eng = FlowEngine(model, inp, num_inference_timesteps=3)
+    new = dict(inp)
+    new["proprioception"] = torch.randn_like(inp["proprioception"])
+    ref = model(mode="predict", predict_mode="diffusion", noise=noise, num_inference_timesteps=3, **new)
+    got = eng(new, noise=noise)
+    assert torch.equal(ref["predict_action"], got["predict_action"])
+    bad = dict(inp)
+    ids = inp["input_ids"].clone()
+    ids[0, 3] = cfg.image_token_id
+    bad["input_ids"] = ids
+    with pytest.raises(ValueError):
+        eng(bad)

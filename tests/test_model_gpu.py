@@ -154,3 +154,33 @@ def test_generate_gpu_matches_cpu():
     new_c, new_g = out_c[0, ids.shape[1]:], out_g[0, ids.shape[1]:].cpu()
     assert new_c[0] == new_g[0]
     assert (new_c == new_g).float().mean() >= 0.5
+
+
+def test_flow_engine_graph_matches_eager_sampler():
+    """The serving engine (static buffers + one CUDA graph for ViT, prefix pass and Euler loop)
+    returns the same chunk as ``predict`` for the same noise, also after the inputs change."""
+    from wallx_b200.data.collator import to_device
+    from wallx_b200.models.inference import FlowEngine
+    from wallx_b200.ops import gemm as G
+
+    cfg, model, batch = _build("flow")
+    model_g = copy.deepcopy(model).to(torch.bfloat16).cuda().eval()
+    inp = _predict_inputs(batch)
+    B = inp["input_ids"].shape[0]
+    A = model.action_preprocessor.action_dim
+    gen = torch.Generator().manual_seed(7)
+    eng = FlowEngine(model_g, inp, num_inference_timesteps=4)
+    assert eng.graph is not None
+    for trial in range(2):
+        cur = dict(inp)
+        if trial == 1:  # new observation, same layout
+            cur["pixel_values"] = torch.randn(inp["pixel_values"].shape, generator=gen)
+            cur["proprioception"] = torch.randn(inp["proprioception"].shape, generator=gen)
+        noise = torch.randn(B, 16, A, generator=gen)
+        ref = model_g(mode="predict", predict_mode="diffusion", noise=noise.cuda(), num_inference_timesteps=4,
+                      **to_device(cur, "cuda", torch.bfloat16))["predict_action"]
+        got = eng(cur, noise=noise)["predict_action"]
+        torch.cuda.synchronize()
+        scale = ref.abs().max().item()
+        assert (ref - got).abs().max().item() < 1e-3 * scale
+    G.check_status()

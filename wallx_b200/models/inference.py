@@ -56,6 +56,7 @@ class FlowSampler:
         pos, _ = model._positions(input_ids, position_ids.to(dev) if position_ids is not None else None, attention_mask,
                                   image_grid_thw, video_grid_thw, second_per_grid_ts)
         pack = PackInfo.build(attention_mask, B, S, dev, seq_lens, pack_index)
+        self.pack = pack
         ids = input_ids.reshape(-1).index_select(0, pack.pack_index)
         types = moe_token_types.to(dev).reshape(-1).index_select(0, pack.pack_index).to(torch.int32)
         pos3 = pos.reshape(3, -1).index_select(1, pack.pack_index)
@@ -82,7 +83,8 @@ class FlowSampler:
         self.suf_is_action = self.suf_ids == action_id
         self.n_action = int(sum(1 for r in suf_rows if ids_host[r] == action_id))
         self.horizon = self.n_action // B
-        self.suf_emb_static = emb.index_select(0, suf_idx)
+        self.pre_idx, self.suf_idx = pre_idx, suf_idx
+        self.suf_emb_static = None
         hq, hkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         caps = [p + s for p, s in zip(pre_lens, suf_lens)]
         self.cache = KVCache(cfg.num_hidden_layers, caps, hkv * d, dev, emb.dtype)
@@ -100,11 +102,8 @@ class FlowSampler:
                                k_rows=self.cache.offsets[-1])
         cos, sin = model.model.rotary(pos3.index_select(1, pre_idx))
         plan = F_.make_route_plan(pre_types, cfg.num_experts) if cfg.mlp_moe else None
-        ctx = StepContext(meta_pre, cos, sin, plan, cache=self.cache, cache_mode="prefill")
-        x = emb.index_select(0, pre_idx)
-        if x.shape[0] > 0:
-            for layer in model.model.layers:
-                x = layer(x, ctx)
+        meta_pre.device_tables(dev)
+        self.ctx_pre = StepContext(meta_pre, cos, sin, plan, cache=self.cache, cache_mode="prefill")
 
         # ---- per-step context over the suffix tokens
         cu_suf = [0]
@@ -129,6 +128,21 @@ class FlowSampler:
         self.dtype = emb.dtype
         self.device = dev
         self._graph = None
+        self.prefill(emb)
+
+    def prefill(self, emb: torch.Tensor) -> None:
+        """Run the prefix tokens of packed embeddings ``emb [T, H]`` through the model (fills the KV
+        cache) and keep the suffix rows (action placeholders and what follows them). Shapes and
+        buffer addresses do not change between calls, so this can be replayed from a CUDA graph."""
+        x = emb.index_select(0, self.pre_idx)
+        if x.shape[0] > 0:
+            for layer in self.model.model.layers:
+                x = layer(x, self.ctx_pre)
+        suf = emb.index_select(0, self.suf_idx)
+        if self.suf_emb_static is None:
+            self.suf_emb_static = suf
+        else:
+            self.suf_emb_static.copy_(suf)
 
     # ------------------------------------------------------------------
     def velocity(self, t: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
@@ -204,6 +218,112 @@ def predict_flow(model, pred_horizon=None, action_dim=None, input_ids=None, acti
         out["gt_action"] = model.action_preprocessor.normalizer_action.unnormalize_data(
             action_chunk.to(sampler.device).float(), names)
     return out
+
+
+class FlowEngine:
+    """Serving engine for a fixed observation layout: one CUDA graph per action chunk.
+
+    A robot controller sends the same prompt template at every step: the positions of the image,
+    proprioception and action placeholders, the image sizes and the batch size do not change, only
+    the pixel values, the proprioception, the text ids and the noise do. The engine analyses that
+    layout once (host side), keeps static device buffers for the inputs, and captures the whole
+    chunk -- embedding, ViT, prefix pass that fills the KV cache, ``num_steps`` Euler evaluations
+    reusing it, un-normalisation -- in one CUDA graph. A call copies the new inputs into the static
+    buffers, replays the graph and returns the chunk; no Python runs per kernel and nothing is
+    allocated. Reference behaviour being replaced: modeling_qwen2_5_vl_act.py:1886-1981.
+    """
+
+    INPUT_KEYS = ("input_ids", "pixel_values", "proprioception", "agent_pos_mask", "dof_mask")
+
+    def __init__(self, model, example: Dict, num_inference_timesteps: int = 10, reference_grid: bool = False,
+                 use_cuda_graph: bool = True):
+        self.model = model
+        dev = model.device
+        fdtype = model.model.embed_tokens.weight.dtype
+        self.steps, self.reference_grid = num_inference_timesteps, reference_grid
+        self.static: Dict[str, torch.Tensor] = {}
+        for k in self.INPUT_KEYS:
+            v = example.get(k)
+            if torch.is_tensor(v):
+                self.static[k] = v.to(dev, fdtype if v.is_floating_point() else v.dtype).clone()
+        self.names = list(example.get("dataset_names") or ["x2_normal"] * example["input_ids"].shape[0])
+        self.grid = example.get("image_grid_thw")
+        self.grid_host = example.get("image_grid_host")
+        if self.grid_host is None and self.grid is not None:
+            self.grid_host = [[int(v) for v in g] for g in self.grid.tolist()]
+        layout = {k: v for k, v in example.items() if k not in self.INPUT_KEYS and k not in ("action_chunk", "labels")}
+        layout["image_grid_host"] = self.grid_host
+        with torch.no_grad():
+            self.sampler = FlowSampler(model, self.static["input_ids"], dataset_names=self.names,
+                                       pixel_values=self.static.get("pixel_values"),
+                                       proprioception=self.static.get("proprioception"),
+                                       agent_pos_mask=self.static.get("agent_pos_mask"),
+                                       dof_mask=self.static.get("dof_mask"),
+                                       **{k: v for k, v in layout.items() if k != "dataset_names"})
+        self.sampler.dof_mask = self.static.get("dof_mask")  # the sampler reads the static buffer
+        B = example["input_ids"].shape[0]
+        A = model.action_preprocessor.action_dim
+        self.noise = torch.zeros(B, self.sampler.horizon, A, device=dev, dtype=fdtype)
+        cfg = model.config
+        ids_host = example["input_ids"].cpu()
+        specials = [cfg.image_token_id, cfg.video_token_id, model.action_token_id_set["action_token_id"],
+                    model.action_token_id_set["propri_token_id"]]
+        self._special_ids = specials
+        self._signature = self._layout_signature(ids_host)
+        self.out = None
+        self.graph = None
+        with torch.no_grad():
+            self._run()  # eager warm-up: builds every cached table before capture
+            if use_cuda_graph and dev.type == "cuda":
+                torch.cuda.synchronize(dev)
+                side = torch.cuda.Stream(device=dev)
+                side.wait_stream(torch.cuda.current_stream(dev))
+                with torch.cuda.stream(side):
+                    self._run()
+                torch.cuda.current_stream(dev).wait_stream(side)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._run()
+                self.graph = g
+
+    def _layout_signature(self, ids_host: torch.Tensor) -> torch.Tensor:
+        sig = torch.zeros_like(ids_host, dtype=torch.int8)
+        for i, t in enumerate(self._special_ids):
+            sig[ids_host == t] = i + 1
+        return sig
+
+    def _run(self) -> None:
+        s, m = self.sampler, self.model
+        ids = self.static["input_ids"].reshape(-1).index_select(0, s.pack.pack_index)
+        emb = m._embed_packed(ids, s.pack, self.static.get("pixel_values"), self.grid, None, None,
+                              self.static.get("proprioception"), self.static.get("agent_pos_mask"), self.names,
+                              self.grid_host, None)
+        s.prefill(emb)
+        x = s.sample(self.noise, self.steps, self.reference_grid, use_cuda_graph=False)
+        self.out = m.action_preprocessor.normalizer_action.unnormalize_data(x.float(), self.names)
+
+    @torch.no_grad()
+    def __call__(self, batch: Optional[Dict] = None, noise: Optional[torch.Tensor] = None, check_layout: bool = True,
+                 **kw) -> Dict[str, torch.Tensor]:
+        batch = dict(batch or {}, **kw)
+        ids = batch.get("input_ids")
+        if check_layout and torch.is_tensor(ids) and ids.device.type == "cpu":
+            if ids.shape != self._signature.shape or not torch.equal(self._layout_signature(ids), self._signature):
+                raise ValueError("FlowEngine: the observation layout changed (placeholder positions or shape); "
+                                 "build a new engine for it")
+        for k, buf in self.static.items():
+            v = batch.get(k)
+            if torch.is_tensor(v):
+                buf.copy_(v, non_blocking=True)
+        if noise is not None:
+            self.noise.copy_(noise, non_blocking=True)
+        else:
+            self.noise.normal_()
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self._run()
+        return {"predict_action": self.out.clone()}
 
 
 # ------------------------------------------------------------------------------------ text / FAST
