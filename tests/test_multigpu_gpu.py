@@ -36,12 +36,16 @@ def _worker(rank, world, port, tmp, transport):
     m.init_weights(seed=0)
     m = m.to(torch.bfloat16).to(dev)
     symm = None
+    overlap = transport == "symm_overlap"
+    if overlap:
+        transport = "symm"
     if transport == "symm":
         from wallx_b200.parallel.symm import SymmComm
 
         symm = SymmComm(torch.distributed.group.WORLD, dev)
     eng = TrainEngine(m, lr=1e-3, weight_decay=0.1, max_grad_norm=1.0, grad_accum=1, world=world, rank=rank,
                       transport=transport, symm=symm)
+    eng.overlap_reduce = overlap
     g = torch.Generator().manual_seed(5)
     batches = []
     for _ in range(2 * world):
@@ -59,8 +63,10 @@ def _worker(rank, world, port, tmp, transport):
     G.check_status()
     if symm is not None:
         symm.check()
-    torch.save({"params": {n: p.detach().float().cpu() for n, p in m.named_parameters()}, "norms": norms},
-               os.path.join(tmp, f"{transport}_{rank}.pt"))
+    tag = "symm_overlap" if overlap else transport
+    early = len(eng._early) if overlap else 0
+    torch.save({"params": {n: p.detach().float().cpu() for n, p in m.named_parameters()}, "norms": norms,
+                "early_units": early}, os.path.join(tmp, f"{tag}_{rank}.pt"))
     torch.distributed.barrier()
     torch.distributed.destroy_process_group()
 
@@ -69,7 +75,7 @@ def _worker(rank, world, port, tmp, transport):
 def test_symm_transport_matches_nccl(tmp_path):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    for transport in ("dist", "symm"):
+    for transport in ("dist", "symm", "symm_overlap"):
         mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), transport), nprocs=2, join=True)
     d0, d1 = torch.load(tmp_path / "dist_0.pt"), torch.load(tmp_path / "dist_1.pt")
     s0, s1 = torch.load(tmp_path / "symm_0.pt"), torch.load(tmp_path / "symm_1.pt")
@@ -82,6 +88,14 @@ def test_symm_transport_matches_nccl(tmp_path):
         assert torch.allclose(a, b, atol=8e-3, rtol=8e-3), k
         assert ((a - b).abs() > 2.5e-3).float().mean() < 0.2, k
     assert abs(s0["norms"][0] - d0["norms"][0]) / d0["norms"][0] < 2e-2
+    # reduce-scatter per unit during backward: the same kernels on the same data; only the order in
+    # which the squared-norm atomics land differs, so at most a few bf16 roundings may flip
+    o0, o1 = torch.load(tmp_path / "symm_overlap_0.pt"), torch.load(tmp_path / "symm_overlap_1.pt")
+    for k in s0["params"]:
+        assert torch.equal(o0["params"][k], o1["params"][k]), k  # replicas identical
+        assert torch.allclose(o0["params"][k], s0["params"][k], atol=8e-3, rtol=8e-3), k
+        assert (o0["params"][k] != s0["params"][k]).float().mean() < 0.01, k
+    assert o0["early_units"] >= 3 and o1["early_units"] >= 3
 
 
 def test_barrier_wait_runs_out_and_reports_status():

@@ -84,13 +84,48 @@ class TrainEngine:
         self.check_touched = True
         if self.transport == "symm":
             symm.register_buffers(self.buffers)
+        # Overlap of the gradient reduce-scatter with backward (symmetric transport): a unit is
+        # reduced on a side stream as soon as the last of its gradients of the last micro-step has
+        # been enqueued. Which parameter comes last, and how many are touched, is learned from the
+        # first step; a unit whose pattern differs in a later step is simply reduced after backward.
+        self.overlap_reduce = False
+        self._micro = 0
+        self._armed = False
+        self._learned = False
+        self._order: Dict[int, list] = {}
+        self._trigger: Dict[int, Optional[int]] = {}
+        self._expected: Dict[int, int] = {}
+        self._seen: Dict[int, set] = {}
+        self._early: set = set()
+        self._step_begun = False
+        self._comm_stream = None
+        for k, b in enumerate(self.buffers):
+            b.index = k
+            b.on_touch = self._on_touch
 
     # ------------------------------------------------------------------ collectives
     def _reduce_scatter(self) -> Optional[List[torch.Tensor]]:
         if self.transport == "local":
             return None
         if self.transport == "symm":
-            return self.symm.reduce_scatter_grads(self.buffers)
+            if not self.overlap_reduce:
+                return self.symm.reduce_scatter_grads(self.buffers)
+            if not self._step_begun:  # the last backward did not go through engine.backward(): nothing was overlapped
+                self.symm.begin_step()
+                self._early = set()
+            self._step_begun = False
+            for k in range(len(self.buffers)):  # units that were not reduced during backward
+                if k not in self._early:
+                    self.symm.reduce_scatter_unit(k)
+            if self._comm_stream is not None:
+                torch.cuda.current_stream(self.buffers[0].device).wait_stream(self._comm_stream)
+            if not self._learned and self._order:
+                for k, order in self._order.items():
+                    self._expected[k] = len({i for i, _ in order})
+                    last_i, last_kind = order[-1]
+                    self._trigger[k] = last_i if last_kind == "accumulate" else None
+                self._learned = True
+            return self.symm.grad_shards()
         import torch.distributed as dist
 
         shards = []
@@ -164,8 +199,41 @@ class TrainEngine:
         return opt.norm_sq
 
     # ------------------------------------------------------------------ step
+    def _on_touch(self, buf, i: int, kind: str) -> None:
+        if not self._armed:
+            return
+        k = buf.index
+        if not self._learned:
+            self._order.setdefault(k, []).append((i, kind))
+            return
+        seen = self._seen.setdefault(k, set())
+        seen.add(i)
+        if kind == "accumulate" and self._trigger.get(k) == i and len(seen) == self._expected.get(k, -1) \
+                and k not in self._early:
+            self._early_reduce(k)
+
+    def _early_reduce(self, k: int) -> None:
+        dev = self.buffers[k].device
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=dev)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(self._comm_stream):
+            self._comm_stream.wait_event(ev)
+            self.symm.reduce_scatter_unit(k)
+        self._early.add(k)
+
     def backward(self, loss: torch.Tensor) -> None:
+        self._micro += 1
+        overlap = self.overlap_reduce and self.transport == "symm"
+        if overlap and self._micro == self.grad_accum:  # last micro-step: gradients become final
+            self.symm.begin_step()
+            self._step_begun = True
+            self._armed = True
+            self._seen = {}
+            self._early = set()
         loss.backward()
+        self._armed = False
 
     def optimizer_step(self, lr: float) -> torch.Tensor:
         """Reduce gradients, clip by global norm, update shards, refresh parameters, clear grads.
@@ -177,6 +245,7 @@ class TrainEngine:
         self.optimizer.step(lr=lr, norm_sq=norm_sq, grad_shards=shards)
         self._all_gather_params()
         self.optimizer.zero_grad()
+        self._micro = 0
         self.last_norm_sq = norm_sq
         return norm_sq
 

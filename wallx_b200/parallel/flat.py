@@ -80,14 +80,15 @@ class FlatBuffer:
         # whose grad is None untouched -- no decay, no moment update -- e.g. the LM head in flow-only
         # training); filled by post-accumulate hooks, merged across ranks by the engine
         self.touched = [False] * len(self.params)
+        self.on_touch = None  # optional callback(buffer, param_index, kind) used by the engine to overlap the reduction
         for i, p in enumerate(self.params):
-            p.register_post_accumulate_grad_hook(self._make_hook(i))
+            p.register_post_accumulate_grad_hook(self._make_hook(i, "accumulate"))
         if self.param.is_cuda:  # weight-gradient GEMMs add straight into the flat gradient buffer
             from ..ops import functional as F_
 
             for i, (p, o) in enumerate(zip(self.params, self.offsets)):
                 if p.dim() == 2:
-                    F_.register_grad_sink(p, self.grad[o:o + p.numel()].view(p.shape), self._make_hook(i))
+                    F_.register_grad_sink(p, self.grad[o:o + p.numel()].view(p.shape), self._make_hook(i, "sink"))
         self.seg_of_param = []
         for o in self.offsets:
             self.seg_of_param.append(next(k for k, sg in enumerate(self.segments) if sg.start <= o < sg.end))
@@ -97,9 +98,14 @@ class FlatBuffer:
         self.exp_avg = torch.zeros(self.shard_size, device=self.device, dtype=master_dtype)
         self.exp_avg_sq = torch.zeros(self.shard_size, device=self.device, dtype=master_dtype)
 
-    def _make_hook(self, i: int):
+    def _make_hook(self, i: int, kind: str = "accumulate"):
+        # kind "accumulate": fired by autograd after the gradient kernel was enqueued; kind "sink":
+        # fired just before the weight-gradient GEMM that writes into the flat buffer is enqueued
         def hook(_p=None):
             self.touched[i] = True
+            cb = self.on_touch
+            if cb is not None:
+                cb(self, i, kind)
 
         return hook
 

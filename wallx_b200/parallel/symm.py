@@ -20,6 +20,7 @@ from ..ops import _ext
 from ..ops import gemm as G
 
 MAX_VEC = 4096  # floats per rank in the small all-reduce scratch
+FLAG_WORDS = 8 * 128  # int32 flag slots: 8 for the global barrier, then 8 per unit (up to 127 units)
 
 
 class SymmComm:
@@ -34,14 +35,15 @@ class SymmComm:
         self.world = dist.get_world_size(group)
         if self.world > 8:
             raise ValueError("symmetric transport supports up to 8 ranks of one NVSwitch domain")
-        # control block: [0, 32) int32 flags (8 used) | then world * MAX_VEC floats of scratch
-        self.ctrl = symm_mem.empty(32 + self.world * MAX_VEC, dtype=torch.float32, device=device)
+        # control block: [0, FLAG_WORDS) int32 flags | then world * MAX_VEC floats of scratch
+        self.ctrl = symm_mem.empty(FLAG_WORDS + self.world * MAX_VEC, dtype=torch.float32, device=device)
         self.ctrl.zero_()
         self.ctrl_hdl = symm_mem.rendezvous(self.ctrl, group)
         base = [int(p) for p in self.ctrl_hdl.buffer_ptrs]
         self.flag_ptrs = base
-        self.scratch_ptrs = [p + 32 * 4 for p in base]
-        self.scratch = self.ctrl[32:]
+        self.scratch_ptrs = [p + FLAG_WORDS * 4 for p in base]
+        self.scratch = self.ctrl[FLAG_WORDS:]
+        self.unit_step = 0
         self.epoch = 0
         self.status = torch.zeros(4, dtype=torch.int32, device=device)
         self.param_arena = self.grad_arena = None
@@ -108,6 +110,24 @@ class SymmComm:
         self.barrier()  # every rank has finished writing its gradients
         self.local_sumsq.zero_()
         C.rs_reduce(self.grad_ptrs, self.table, self.gshard, self.local_sumsq)
+        return [self.gshard[o:o + n] for o, n in self.views]
+
+    # Per-unit variant: every unit has its own flag slots, so the ranks may reach the units at
+    # different times and in any order (one rank can reduce a unit while backward still runs, another
+    # after it) without the barriers of different units getting mixed up.
+    def begin_step(self) -> None:
+        self.unit_step += 1
+        self.local_sumsq.zero_()
+
+    def reduce_scatter_unit(self, k: int) -> None:
+        """Barrier on unit k's flags, then pull and sum unit k's gradient shard (current stream)."""
+        if 8 * (k + 2) > FLAG_WORDS:
+            raise ValueError("too many units for the per-unit flag block")
+        C = _ext.get()
+        C.symm_barrier([p + 32 * (k + 1) for p in self.flag_ptrs], self.rank, self.unit_step, self.status)
+        C.rs_reduce(self.grad_ptrs, self.table[k:k + 1], self.gshard, self.local_sumsq)
+
+    def grad_shards(self) -> List[torch.Tensor]:
         return [self.gshard[o:o + n] for o, n in self.views]
 
     def all_reduce_vector(self, t: torch.Tensor) -> torch.Tensor:
