@@ -83,6 +83,28 @@ def test_swiglu_interleaved():
     G.check_status()
 
 
+@pytest.mark.parametrize("bn", [0, 128, 256, 512])
+def test_swiglu_backward_epilogue(bn):
+    """dgrad of the down projection with the SwiGLU backward in its epilogue vs autograd in fp32."""
+    from wallx_b200.ops import gemm as G
+
+    M, I, H = 300, 192, 256
+    dy = _mk((M, H), 20)
+    w_dn = _mk((H, I), 21, 0.1)
+    gu = _mk((M, 2 * I), 22)                      # raw [16 gate | 16 up] blocks
+    dgu = torch.full((M, 2 * I), 9.0, device="cuda", dtype=torch.bfloat16)
+    G.launch([G.GemmSpec(dy, w_dn, dgu, b_mn=True, out2=gu, flags=G.SWIGLU_BWD)], force_bn=bn)
+    torch.cuda.synchronize()
+    G.check_status()
+    z = gu.float().view(M, I // 16, 2, 16)
+    g = z[:, :, 0].reshape(M, I).clone().requires_grad_(True)
+    u = z[:, :, 1].reshape(M, I).clone().requires_grad_(True)
+    dh = dy.float() @ w_dn.float()
+    (torch.nn.functional.silu(g) * u).backward(dh)
+    ref = torch.stack([g.grad.view(M, I // 16, 16), u.grad.view(M, I // 16, 16)], dim=2).reshape(M, 2 * I)
+    _check(dgu, ref, H)
+
+
 def test_grouped_two_problems_with_row_map_and_dyn():
     from wallx_b200.ops import gemm as G
 

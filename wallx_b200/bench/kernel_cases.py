@@ -51,6 +51,10 @@ def case_gemm(M, N, K, a_mn=False, b_mn=False, flags=0, extra=None, force_bn=0):
         if extra == "swiglu_raw":
             kw["out2"] = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
             nbytes += M * N * 2
+        if extra == "swiglu_bwd":  # accumulator = dL/dh [M, N]; reads raw gate/up [M, 2N], writes dL/d(gate|up) [M, 2N]
+            out = torch.empty(M, 2 * N, device="cuda", dtype=torch.bfloat16)
+            kw["out2"] = _bf(M, 2 * N)
+            nbytes = (M * K + N * K) * 2 + 2 * M * 2 * N * 2
         if extra == "residual":
             kw["residual"] = _bf(M, N)
             nbytes += M * N * 2
@@ -268,6 +272,8 @@ CASES = {
     "gemm_dgrad_pair": case_gemm(16384, 2048, 22016, b_mn=True, force_bn=512),
     "gemm_wgrad_fp32_accumulate_pair": case_gemm(22016, 2048, 16384, a_mn=True, b_mn=True, flags=3, force_bn=512),
     "gemm_vit_qkv_pair": case_gemm(62208, 3840, 1280, force_bn=512),
+    "gemm_down_dgrad": case_gemm(16384, 11008, 2048, b_mn=True),
+    "gemm_down_dgrad_swiglu_bwd": case_gemm(16384, 11008, 2048, b_mn=True, flags=32, extra="swiglu_bwd"),
     "gemm_dual_expert": case_gemm_dual,
     "gemm_gathered_weight": case_gemm_gathered,
     "attn_llm_fwd": case_attn_llm("fwd"),

@@ -97,6 +97,12 @@ void fill_call(wx::GemmCall& c, const GemmTuple& g) {
   c.ldd2 = c.D2 ? D2->stride(0) : 0;
   const bool fp32 = (c.flags & wx::GEMM_OUT_FP32) != 0;
   TORCH_CHECK(D.scalar_type() == (fp32 ? at::kFloat : at::kBFloat16), "gemm: output dtype does not match flags");
+  if (c.flags & wx::GEMM_SWIGLU_BWD) {
+    TORCH_CHECK(!fp32 && c.D2 != nullptr && (c.ldd % 8) == 0 && (c.ldd2 % 8) == 0 &&
+                    (reinterpret_cast<uintptr_t>(c.D) % 16) == 0 && (reinterpret_cast<uintptr_t>(c.D2) % 16) == 0 &&
+                    D.size(1) >= 2 * c.N && D2->size(1) >= 2 * c.N && c.row_map == nullptr && c.bias == nullptr,
+                "gemm: swiglu-backward epilogue needs bf16 [*, 2N] output and saved raw gate/up values");
+  }
   if (c.flags & wx::GEMM_ACT_SWIGLU) {
     TORCH_CHECK(!fp32 && (c.ldd % 8) == 0 && (reinterpret_cast<uintptr_t>(c.D) % 16) == 0, "gemm: swiglu output");
     if (c.D2) TORCH_CHECK((c.ldd2 % 8) == 0 && (reinterpret_cast<uintptr_t>(c.D2) % 16) == 0, "gemm: swiglu raw output");

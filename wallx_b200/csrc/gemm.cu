@@ -175,6 +175,35 @@ __device__ __forceinline__ void epilogue_rows(const Problem& p, int M, int m0, i
       for (int j = 0; j < 32; ++j)
         if (j < nvalid) v[j] += __bfloat162float(p.bias[n0 + j]);
     }
+    if (flags & GEMM_SWIGLU_BWD) {
+      // v = dL/dh for channels [n0, n0 + 32): two 32-column blocks [16 gate | 16 up] of the saved raw values
+      const uint4* gsrc =
+          reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.D2) + drow * p.ldd2 + 2 * n0);
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + drow * p.ldd + 2 * n0);
+#pragma unroll
+      for (int blk = 0; blk < 2; ++blk) {
+        uint4 raw[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) raw[q] = zero_row ? make_uint4(0u, 0u, 0u, 0u) : gsrc[4 * blk + q];
+        const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&raw[0]);  // 16 gate values
+        const __nv_bfloat162* ub = reinterpret_cast<const __nv_bfloat162*>(&raw[2]);  // 16 up values
+        uint32_t og[8], ou[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float2 g2 = __bfloat1622float2(gb[e]);
+          const float2 u2 = __bfloat1622float2(ub[e]);
+          const float d0 = v[16 * blk + 2 * e], d1 = v[16 * blk + 2 * e + 1];
+          const float s0 = 1.0f / (1.0f + __expf(-g2.x)), s1 = 1.0f / (1.0f + __expf(-g2.y));
+          og[e] = pack_bf16x2(d0 * u2.x * s0 * (1.0f + g2.x * (1.0f - s0)), d1 * u2.y * s1 * (1.0f + g2.y * (1.0f - s1)));
+          ou[e] = pack_bf16x2(d0 * g2.x * s0, d1 * g2.y * s1);
+        }
+        dst[4 * blk + 0] = make_uint4(og[0], og[1], og[2], og[3]);
+        dst[4 * blk + 1] = make_uint4(og[4], og[5], og[6], og[7]);
+        dst[4 * blk + 2] = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+        dst[4 * blk + 3] = make_uint4(ou[4], ou[5], ou[6], ou[7]);
+      }
+      continue;
+    }
     if (swiglu) {
       // columns [n0, n0+16) are gate, [n0+16, n0+32) are up; N is a multiple of 32 here.
       if (p.D2 != nullptr) {
@@ -781,7 +810,7 @@ int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* sta
     }
   }
   for (int i = 0; i < ncalls; ++i)
-    if ((calls[i].flags & GEMM_ACT_SWIGLU) && (calls[i].N % 32 != 0)) return -3;
+    if ((calls[i].flags & (GEMM_ACT_SWIGLU | GEMM_SWIGLU_BWD)) && (calls[i].N % 32 != 0)) return -3;
 
   if (use_pair) {  // CTA pairs: 256 x 256 tiles
     GemmArgs pargs;
@@ -812,7 +841,7 @@ int gemm_ag_launch(const GemmCall* calls, const AgInfo* ags, int ncalls, cudaStr
   for (int i = 0; i < ncalls; ++i)
     if (calls[i].a_mn || calls[i].b_mn != b_mn) return -2;
   for (int i = 0; i < ncalls; ++i)
-    if ((calls[i].flags & GEMM_ACT_SWIGLU) && (calls[i].N % 32 != 0)) return -3;
+    if ((calls[i].flags & (GEMM_ACT_SWIGLU | GEMM_SWIGLU_BWD)) && (calls[i].N % 32 != 0)) return -3;
   GemmArgs args;
   const int rc = fill_args(args, calls, ncalls, 256);
   if (rc != 0) return rc;

@@ -19,6 +19,10 @@ enum GemmFlags : int {
   GEMM_ACT_GELU = 4,     // exact (erf) GELU after bias
   GEMM_ACT_SWIGLU = 8,   // B rows interleaved [16 gate | 16 up]: D[:, j] = silu(g_j) * u_j, ld = N/2
   GEMM_ZERO_PAD_ROWS = 16,  // rows in [M, round_up(M, 128)) are written as zeros (no row_map)
+  // SwiGLU backward fused into the dgrad of the down projection: the accumulator is dL/dh [*, N];
+  // D2 (input) holds the saved raw gate/up values [*, 2N] in 16-column interleaved blocks and D
+  // (output, bf16, 2N wide) receives dL/d(gate|up) in the same layout. N % 32 == 0.
+  GEMM_SWIGLU_BWD = 32,
 };
 
 struct GemmCall {

@@ -117,8 +117,7 @@ class SwiGLUFFN(nn.Module):
         self._register_load_state_dict_pre_hook(self._merge_hook)
 
     def forward(self, x, residual=None):
-        h = F_.gate_up_swiglu(x, self.gate_up_weight, self.gate_up_bias)
-        return F_.linear(h, self.down_weight, self.down_bias, residual)
+        return F_.swiglu_ffn(x, self.gate_up_weight, self.gate_up_bias, self.down_weight, self.down_bias, residual)
 
     def weights(self):
         return self.gate_up_weight, self.down_weight

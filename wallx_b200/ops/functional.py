@@ -219,6 +219,66 @@ class _GateUpFn(torch.autograd.Function):
         return dx, dw, db
 
 
+class _SwiGLUFfnFn(torch.autograd.Function):
+    """Whole SwiGLU FFN, ``down(silu(gate(x)) * up(x)) (+ bias) (+ residual)``, as one autograd node so
+    that the backward of the activation runs in the epilogue of the down-projection's dgrad GEMM:
+    ``dL/dh`` never goes to memory."""
+
+    @staticmethod
+    def forward(ctx, x, w_gu, b_gu, w_dn, b_dn, residual):
+        M, N = x.shape[0], w_gu.shape[0]
+        need_bwd = any(ctx.needs_input_grad)
+        gu = torch.empty((M, N), device=x.device, dtype=torch.bfloat16) if need_bwd else None
+        h = torch.empty((M, N // 2), device=x.device, dtype=torch.bfloat16)
+        G.launch([G.GemmSpec(x, w_gu, h, out2=gu, bias=b_gu, flags=G.ACT_SWIGLU)])
+        out = torch.empty((M, w_dn.shape[0]), device=x.device, dtype=torch.bfloat16)
+        G.launch([G.GemmSpec(h, w_dn, out, bias=b_dn, residual=residual)])
+        if need_bwd:
+            ctx.save_for_backward(x, w_gu, w_dn, gu, h)
+        ctx.has_bgu, ctx.has_bdn, ctx.has_res = b_gu is not None, b_dn is not None, residual is not None
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w_gu, w_dn, gu, h = ctx.saved_tensors
+        dy = dy.contiguous()
+        dgu = torch.empty_like(gu)
+        # dL/dh = dy @ w_dn, turned into dL/d(gate|up) in the epilogue
+        G.launch([G.GemmSpec(dy, w_dn, dgu, b_mn=True, out2=gu, flags=G.SWIGLU_BWD)])
+        dx = dw_gu = db_gu = dw_dn = db_dn = dres = None
+        if ctx.needs_input_grad[3]:
+            dw_dn = _wgrad(dy, h, w_dn)
+        if ctx.has_bdn and ctx.needs_input_grad[4]:
+            db_dn = column_sum(dy)
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty_like(x)
+            G.launch([G.GemmSpec(dgu, w_gu, dx, b_mn=True)])
+        if ctx.needs_input_grad[1]:
+            dw_gu = _wgrad(dgu, x, w_gu)
+        if ctx.has_bgu and ctx.needs_input_grad[2]:
+            db_gu = column_sum(dgu)
+        if ctx.has_res and ctx.needs_input_grad[5]:
+            dres = dy
+        return dx, dw_gu, db_gu, dw_dn, db_dn, dres
+
+
+def swiglu_ffn(x: torch.Tensor, w_gu: torch.Tensor, b_gu: Optional[torch.Tensor], w_dn: torch.Tensor,
+               b_dn: Optional[torch.Tensor], residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``down(silu(gate(x)) * up(x)) + b (+ residual)`` with ``w_gu [2I, K]`` interleaved in 16-row blocks.
+    Reference: Qwen2_5_VLMLP / Qwen2MLP (modeling_qwen2_5_vl.py:357-363, 715-728) as three cuBLAS GEMMs and
+    unfused elementwise kernels."""
+    shp = x.shape
+    x2 = x.reshape(-1, shp[-1])
+    if _is_cuda(x2):
+        r2 = residual.reshape(-1, w_dn.shape[0]) if residual is not None else None
+        if r2 is not None and r2.stride(1) != 1:
+            r2 = r2.contiguous()
+        y = _SwiGLUFfnFn.apply(x2.contiguous(), w_gu, b_gu, w_dn, b_dn, r2)
+        return y.reshape(*shp[:-1], w_dn.shape[0])
+    h = gate_up_swiglu(x, w_gu, b_gu)
+    return linear(h, w_dn, b_dn, residual)
+
+
 def gate_up_swiglu(x: torch.Tensor, w_gu: torch.Tensor, b_gu: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Fused gate/up projection + SwiGLU; ``w_gu`` is ``[2I, K]`` interleaved in 16-row blocks."""
     x2 = x.reshape(-1, x.shape[-1])
@@ -310,12 +370,13 @@ class _MoeFfnFn(torch.autograd.Function):
         dout = dout.contiguous()
         dyp = _C().permute_rows(dout, dest, rows)  # grouped order, zero padding rows
         wmax = gu.shape[1]
-        dh = torch.empty((rows, wmax // 2), device=xp.device, dtype=torch.bfloat16)
+        # dL/dh = dy @ w_down per expert, turned into dL/d(gate|up) in the GEMM epilogue (pad rows zeroed)
+        dgu = torch.empty((rows, wmax), device=xp.device, dtype=torch.bfloat16)
         specs = []
         for e in range(n_exp):
             w_dn = weights[2 * e + 1]
-            specs.append(G.GemmSpec(dyp, w_dn, dh[:, : w_dn.shape[1]], M=rows, dyn=seg[e], b_mn=True,
-                                    flags=G.ZERO_PAD_ROWS))
+            specs.append(G.GemmSpec(dyp, w_dn, dgu, M=rows, dyn=seg[e], b_mn=True, out2=gu,
+                                    flags=G.SWIGLU_BWD | G.ZERO_PAD_ROWS))
         for i in range(0, n_exp, 2):
             G.launch(specs[i:i + 2])
         grads = [None] * (2 * n_exp)
@@ -334,7 +395,6 @@ class _MoeFfnFn(torch.autograd.Function):
             specs.append(G.GemmSpec(dyp, h[:, :I], dw, a_mn=True, b_mn=True, M=H, N=I, K=rows, dyn=segk[e], flags=fl))
         for i in range(0, n_exp, 2):
             G.launch(specs[i:i + 2])
-        dgu = _C().swiglu_bwd(dh, gu)
         dxp = torch.empty((rows, H), device=xp.device, dtype=torch.bfloat16)
         specs = []
         for e in range(n_exp):

@@ -23,6 +23,7 @@ ACCUMULATE = 2
 ACT_GELU = 4
 ACT_SWIGLU = 8
 ZERO_PAD_ROWS = 16
+SWIGLU_BWD = 32  # accumulator = dL/dh; out2 = saved raw gate/up (input); out = dL/d(gate|up), 2N wide
 
 
 class GemmSpec:
