@@ -699,6 +699,13 @@ class _LmHeadCeFn(torch.autograd.Function):
     CHUNK = 4096
 
     @staticmethod
+    def _logits_buffer(rows: int, V: int, device) -> torch.Tensor:
+        # the backward pass reads the logits as a GEMM operand through TMA: the row pitch must be a
+        # multiple of 16 bytes even when the vocabulary size is not a multiple of 8
+        Vp = (V + 7) // 8 * 8
+        return torch.empty((rows, Vp), device=device, dtype=torch.bfloat16)[:, :V]
+
+    @staticmethod
     def forward(ctx, hidden, weight, labels):
         R = hidden.shape[0]
         V = weight.shape[0]
@@ -708,7 +715,7 @@ class _LmHeadCeFn(torch.autograd.Function):
         w2 = _aligned2d(weight)
         for s in range(0, R, _LmHeadCeFn.CHUNK):
             e = min(R, s + _LmHeadCeFn.CHUNK)
-            logits = torch.empty((e - s, V), device=hidden.device, dtype=torch.bfloat16)
+            logits = _LmHeadCeFn._logits_buffer(e - s, V, hidden.device)
             G.launch([G.GemmSpec(hidden[s:e], w2, logits)])
             _C().ce_fwd(logits, labels[s:e], loss[s:e], lse[s:e], pred[s:e])
         ctx.save_for_backward(hidden, weight, labels, lse)
@@ -725,7 +732,7 @@ class _LmHeadCeFn(torch.autograd.Function):
         dloss = dloss.contiguous().float()
         for s in range(0, R, _LmHeadCeFn.CHUNK):
             e = min(R, s + _LmHeadCeFn.CHUNK)
-            logits = torch.empty((e - s, V), device=hidden.device, dtype=torch.bfloat16)
+            logits = _LmHeadCeFn._logits_buffer(e - s, V, hidden.device)
             G.launch([G.GemmSpec(hidden[s:e], w2, logits)])
             _C().ce_bwd(logits, labels[s:e], lse[s:e], dloss[s:e])  # in place: logits -> dlogits
             G.launch([G.GemmSpec(logits, w2, dh[s:e], b_mn=True)])
