@@ -138,13 +138,36 @@ __global__ void adamw_f32g_kernel(__nv_bfloat16* __restrict__ p16, float* __rest
   }
   const float step_size = lr / bc1;
   const float inv_sqrt_bc2 = rsqrtf(bc2);
-  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
-       i += static_cast<long>(gridDim.x) * blockDim.x) {
-    const float gi = g[i] * scale;
-    float pi = p32[i] * (1.f - lr * wd);
-    const float mi = b1 * m[i] + (1.f - b1) * gi;
-    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+  const long tid0 = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long nthr = static_cast<long>(gridDim.x) * blockDim.x;
+  auto update = [&](float gi, float& pi, float& mi, float& vi) {
+    gi *= scale;
+    pi *= (1.f - lr * wd);
+    mi = b1 * mi + (1.f - b1) * gi;
+    vi = b2 * vi + (1.f - b2) * gi * gi;
     pi -= step_size * mi / (sqrtf(vi) * inv_sqrt_bc2 + eps);
+  };
+  // four elements per thread with 16-byte accesses when every array allows it
+  const bool vec = ((reinterpret_cast<uintptr_t>(p32) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
+                     reinterpret_cast<uintptr_t>(g)) & 15) == 0 && (reinterpret_cast<uintptr_t>(p16) & 7) == 0;
+  const long n4 = vec ? n >> 2 : 0;
+  for (long i = tid0; i < n4; i += nthr) {
+    float4 p4 = reinterpret_cast<float4*>(p32)[i], m4 = reinterpret_cast<float4*>(m)[i], v4 = reinterpret_cast<float4*>(v)[i];
+    const float4 g4 = reinterpret_cast<const float4*>(g)[i];
+    update(g4.x, p4.x, m4.x, v4.x);
+    update(g4.y, p4.y, m4.y, v4.y);
+    update(g4.z, p4.z, m4.z, v4.z);
+    update(g4.w, p4.w, m4.w, v4.w);
+    reinterpret_cast<float4*>(m)[i] = m4;
+    reinterpret_cast<float4*>(v)[i] = v4;
+    reinterpret_cast<float4*>(p32)[i] = p4;
+    const __nv_bfloat162 o01 = __floats2bfloat162_rn(p4.x, p4.y), o23 = __floats2bfloat162_rn(p4.z, p4.w);
+    reinterpret_cast<uint2*>(p16)[i] =
+        make_uint2(*reinterpret_cast<const uint32_t*>(&o01), *reinterpret_cast<const uint32_t*>(&o23));
+  }
+  for (long i = (n4 << 2) + tid0; i < n; i += nthr) {
+    float pi = p32[i], mi = m[i], vi = v[i];
+    update(g[i], pi, mi, vi);
     m[i] = mi;
     v[i] = vi;
     p32[i] = pi;

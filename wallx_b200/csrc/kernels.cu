@@ -320,32 +320,22 @@ swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dh, const __nv_bfloat16* __r
 }
 
 // ------------------------------------------------------------------------------ rotary on q|k|v
-// One thread rotates 8 channels of the first half of a head and their partners in the second
-// half; v columns (heads >= n_rot) are copied. `inverse` applies the transposed rotation.
-__global__ void rope_qk_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
-                               const float* __restrict__ cos_t, const float* __restrict__ sin_t, int T, int W,
-                               int n_rot, int D, int inverse) {
+// One thread owns 8 channels of the first half of the head dimension (and their partners in the
+// second half) of one token and walks over all rotated heads with them, so the fp32 cos/sin
+// values are loaded once per token instead of once per head; the v columns (heads >= n_rot) are
+// copied by the same threads. `inverse` applies the transposed rotation (the backward pass).
+__global__ void __launch_bounds__(256)
+rope_qk_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+               const float* __restrict__ cos_t, const float* __restrict__ sin_t, int T, int W, int n_rot, int D,
+               int inverse) {
   const int half = D >> 1;
-  const int chunks_per_head = half >> 3;
-  const int rot_chunks = n_rot * chunks_per_head;
-  const int copy_chunks = (W - n_rot * D) >> 3;
-  const int per_row = rot_chunks + copy_chunks;
+  const int tpr = half >> 3;  // threads per token
   const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= static_cast<long>(T) * per_row) return;
-  const int t = static_cast<int>(idx / per_row);
-  const int c = static_cast<int>(idx - static_cast<long>(t) * per_row);
+  if (idx >= static_cast<long>(T) * tpr) return;
+  const int t = static_cast<int>(idx / tpr);
+  const int d0 = static_cast<int>(idx - static_cast<long>(t) * tpr) * 8;
   const __nv_bfloat16* row = in + static_cast<size_t>(t) * W;
   __nv_bfloat16* orow = out + static_cast<size_t>(t) * W;
-  if (c >= rot_chunks) {
-    const int off = n_rot * D + (c - rot_chunks) * 8;
-    *reinterpret_cast<BF8*>(orow + off) = *reinterpret_cast<const BF8*>(row + off);
-    return;
-  }
-  const int h = c / chunks_per_head;
-  const int d0 = (c - h * chunks_per_head) * 8;
-  float a[8], b[8], oa[8], ob[8];
-  unpack8(*reinterpret_cast<const BF8*>(row + h * D + d0), a);
-  unpack8(*reinterpret_cast<const BF8*>(row + h * D + half + d0), b);
   const float* cs = cos_t + static_cast<size_t>(t) * D;
   const float* sn = sin_t + static_cast<size_t>(t) * D;
   float c1[8], s1[8], c2[8], s2[8];  // 16-byte loads: d0 is a multiple of 8 floats, rows are 16-byte aligned
@@ -356,18 +346,28 @@ __global__ void rope_qk_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat
     *reinterpret_cast<float4*>(c2 + 4 * q) = *reinterpret_cast<const float4*>(cs + half + d0 + 4 * q);
     *reinterpret_cast<float4*>(s2 + 4 * q) = *reinterpret_cast<const float4*>(sn + half + d0 + 4 * q);
   }
+#pragma unroll 2
+  for (int h = 0; h < n_rot; ++h) {
+    float a[8], b[8], oa[8], ob[8];
+    unpack8(*reinterpret_cast<const BF8*>(row + h * D + d0), a);
+    unpack8(*reinterpret_cast<const BF8*>(row + h * D + half + d0), b);
 #pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    if (!inverse) {
-      oa[e] = a[e] * c1[e] - b[e] * s1[e];
-      ob[e] = b[e] * c2[e] + a[e] * s2[e];
-    } else {
-      oa[e] = a[e] * c1[e] + b[e] * s2[e];
-      ob[e] = b[e] * c2[e] - a[e] * s1[e];
+    for (int e = 0; e < 8; ++e) {
+      if (!inverse) {
+        oa[e] = a[e] * c1[e] - b[e] * s1[e];
+        ob[e] = b[e] * c2[e] + a[e] * s2[e];
+      } else {
+        oa[e] = a[e] * c1[e] + b[e] * s2[e];
+        ob[e] = b[e] * c2[e] - a[e] * s1[e];
+      }
     }
+    *reinterpret_cast<BF8*>(orow + h * D + d0) = pack8(oa);
+    *reinterpret_cast<BF8*>(orow + h * D + half + d0) = pack8(ob);
   }
-  *reinterpret_cast<BF8*>(orow + h * D + d0) = pack8(oa);
-  *reinterpret_cast<BF8*>(orow + h * D + half + d0) = pack8(ob);
+  // pass-through columns, 16 bytes at a time, spread over the token's threads
+  const int base = n_rot * D;
+  for (int off = base + d0; off < W; off += tpr * 8)
+    *reinterpret_cast<BF8*>(orow + off) = *reinterpret_cast<const BF8*>(row + off);
 }
 
 // ------------------------------------------------------------------------------ routing plan
@@ -624,13 +624,38 @@ __global__ void adamw_kernel(__nv_bfloat16* __restrict__ p16, float* __restrict_
   }
   const float step_size = lr / bc1;
   const float inv_sqrt_bc2 = rsqrtf(bc2);
-  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
-       i += static_cast<long>(gridDim.x) * blockDim.x) {
-    const float gi = __bfloat162float(g[i]) * scale;
-    float pi = p32[i] * (1.f - lr * wd);
-    const float mi = b1 * m[i] + (1.f - b1) * gi;
-    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+  const long tid0 = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long nthr = static_cast<long>(gridDim.x) * blockDim.x;
+  auto update = [&](float gi, float& pi, float& mi, float& vi) {
+    gi *= scale;
+    pi *= (1.f - lr * wd);
+    mi = b1 * mi + (1.f - b1) * gi;
+    vi = b2 * vi + (1.f - b2) * gi * gi;
     pi -= step_size * mi / (sqrtf(vi) * inv_sqrt_bc2 + eps);
+  };
+  // four elements per thread with 16-byte accesses when every array allows it
+  const bool vec = ((reinterpret_cast<uintptr_t>(p32) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v)) & 15) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(p16) | reinterpret_cast<uintptr_t>(g)) & 7) == 0;
+  const long n4 = vec ? n >> 2 : 0;
+  for (long i = tid0; i < n4; i += nthr) {
+    float4 p4 = reinterpret_cast<float4*>(p32)[i], m4 = reinterpret_cast<float4*>(m)[i], v4 = reinterpret_cast<float4*>(v)[i];
+    const uint2 graw = reinterpret_cast<const uint2*>(g)[i];
+    const float2 g01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&graw.x));
+    const float2 g23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&graw.y));
+    update(g01.x, p4.x, m4.x, v4.x);
+    update(g01.y, p4.y, m4.y, v4.y);
+    update(g23.x, p4.z, m4.z, v4.z);
+    update(g23.y, p4.w, m4.w, v4.w);
+    reinterpret_cast<float4*>(m)[i] = m4;
+    reinterpret_cast<float4*>(v)[i] = v4;
+    reinterpret_cast<float4*>(p32)[i] = p4;
+    const __nv_bfloat162 o01 = __floats2bfloat162_rn(p4.x, p4.y), o23 = __floats2bfloat162_rn(p4.z, p4.w);
+    reinterpret_cast<uint2*>(p16)[i] =
+        make_uint2(*reinterpret_cast<const uint32_t*>(&o01), *reinterpret_cast<const uint32_t*>(&o23));
+  }
+  for (long i = (n4 << 2) + tid0; i < n; i += nthr) {
+    float pi = p32[i], mi = m[i], vi = v[i];
+    update(__bfloat162float(g[i]), pi, mi, vi);
     m[i] = mi;
     v[i] = vi;
     p32[i] = pi;
@@ -712,8 +737,7 @@ int swiglu_bwd(const void* dh, const void* gu, void* dgu, int R, int width_gu, l
 int rope_qk(const void* in, void* out, const float* cos_t, const float* sin_t, int T, int W, int n_rot, int D,
             int inverse, cudaStream_t s) {
   if (D % 16 != 0 || W % 8 != 0 || n_rot * D > W) return -1;
-  const long per_row = static_cast<long>(n_rot) * (D / 16) + (W - n_rot * D) / 8;
-  const long total = per_row * T;
+  const long total = static_cast<long>(D / 16) * T;  // D/16 threads per token
   if (total == 0) return 0;
   rope_qk_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(
       reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(out), cos_t, sin_t, T, W, n_rot, D,
