@@ -25,10 +25,12 @@ def _check(out, ref, K):
 
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (200, 328, 136), (1000, 1280, 1176), (64, 40, 2048)])
-@pytest.mark.parametrize("bn", [0, 64, 128, 256, 512])  # 512 = CTA pairs, 256 x 256 tiles
+@pytest.mark.parametrize("bn", [0, 32, 64, 128, 256, 512])  # 512 = CTA pairs, 256 x 256 tiles; 32 = K-major only
 def test_layouts(a_mn, b_mn, M, N, K, bn):
     from wallx_b200.ops import gemm as G
 
+    if bn == 32 and (a_mn or b_mn):
+        pytest.skip("32-wide tiles exist for K-major operands only")
     if (a_mn and M % 8) or (b_mn and N % 8) or ((not a_mn or not b_mn) and K % 8):
         pytest.skip("pitch not 16-byte aligned for this layout")
     a = _mk((K, M) if a_mn else (M, K), 1)
@@ -62,6 +64,30 @@ def test_epilogues():
     accb = torch.ones((M, N), device="cuda", dtype=torch.bfloat16)
     G.gemm(a, b, out=accb, flags=G.ACCUMULATE)
     _check(accb, ref + 1.0, K)
+    G.check_status()
+
+
+def test_small_m_problems_and_forced_narrow_tiles():
+    """Decode-sized problems (one row tile): bias, residual, SwiGLU; forced 32-wide tiles give the same bits."""
+    from wallx_b200.ops import gemm as G
+
+    M, N, K = 32, 2560, 2048
+    a, b = _mk((M, K), 30), _mk((N, K), 31, 0.05)
+    bias, res = _mk((N,), 32), _mk((M, N), 33)
+    ref = a.float() @ b.float().t()
+    _check(G.gemm(a, b, bias=bias, residual=res), ref + bias.float() + res.float(), K)
+    I = 1024
+    wg, wu = _mk((I, K), 34, 0.05), _mk((I, K), 35, 0.05)
+    w = torch.stack([wg.view(I // 16, 16, K), wu.view(I // 16, 16, K)], dim=1).reshape(2 * I, K).contiguous()
+    h = torch.empty((M, I), device="cuda", dtype=torch.bfloat16)
+    h32 = torch.empty_like(h)
+    G.launch([G.GemmSpec(a, w, h, flags=G.ACT_SWIGLU)])
+    G.launch([G.GemmSpec(a, w, h32, flags=G.ACT_SWIGLU)], force_bn=32)
+    g = (a.float() @ wg.float().t()).bfloat16().float()
+    u = (a.float() @ wu.float().t()).bfloat16().float()
+    _check(h, torch.nn.functional.silu(g) * u, K)
+    assert torch.equal(h, h32)
+    torch.cuda.synchronize()
     G.check_status()
 
 

@@ -778,7 +778,7 @@ int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* sta
   // on B200 (BN 256 / 128 / 64 reach about 1260 / 970 / 525 TFLOP/s with every SM busy).
   int bn = 64;
   bool use_pair = force_bn == 512;
-  if (force_bn == 64 || force_bn == 128 || force_bn == 256) {
+  if (force_bn == 64 || force_bn == 128 || force_bn == 256 || (force_bn == 32 && !a_mn && !b_mn)) {
     bn = force_bn;
   } else if (!use_pair) {
     int max_n = 0;
@@ -809,6 +809,8 @@ int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* sta
       if (pcost < best) use_pair = true;
     }
   }
+  // (32-wide tiles exist for K-major operands and can be forced; measured on decode-sized problems they
+  // are not faster than 64-wide ones -- the 128-row A tile dominates each step -- so they are never chosen.)
   for (int i = 0; i < ncalls; ++i)
     if ((calls[i].flags & (GEMM_ACT_SWIGLU | GEMM_SWIGLU_BWD)) && (calls[i].N % 32 != 0)) return -3;
 
@@ -832,6 +834,7 @@ int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* sta
   int grid = tiles < sms ? static_cast<int>(tiles) : sms;
   if (bn == 256) return launch_bn<256>(args, a_mn, b_mn, grid, stream, status);
   if (bn == 128) return launch_bn<128>(args, a_mn, b_mn, grid, stream, status);
+  if (bn == 32) return launch_t<32, false, false>(args, grid, stream, status);
   return launch_bn<64>(args, a_mn, b_mn, grid, stream, status);
 }
 

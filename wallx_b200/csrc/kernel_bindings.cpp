@@ -23,14 +23,18 @@ const int* opt_int(const OptT& t) {
   return t->data_ptr<int>();
 }
 
+// `zero_pad`: with a row map, rows of the output that no token maps to are zero-filled. The backward
+// pass reduces over padded segments and needs that; inference may skip it (those rows only feed
+// accumulator rows that are never stored).
 std::tuple<at::Tensor, at::Tensor> rms_norm_fwd(const at::Tensor& x, const at::Tensor& w, double eps, const OptT& dest,
-                                                int64_t out_rows) {
+                                                int64_t out_rows, bool zero_pad) {
   check_bf16(x, "x");
   check_bf16(w, "w");
   c10::cuda::CUDAGuard g(x.device());
   const int T = x.size(0), C = x.size(1);
   const int* dp = opt_int(dest);
-  at::Tensor y = dp ? at::zeros({out_rows, C}, x.options()) : at::empty({T, C}, x.options());
+  at::Tensor y = dp ? (zero_pad ? at::zeros({out_rows, C}, x.options()) : at::empty({out_rows, C}, x.options()))
+                    : at::empty({T, C}, x.options());
   at::Tensor rstd = at::empty({T}, x.options().dtype(at::kFloat));
   WX_CHECK_RC(wx::rms_norm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), dp, T, C,
                                static_cast<float>(eps), cur_stream()),
@@ -258,7 +262,8 @@ std::tuple<at::Tensor, at::Tensor> vit_window_index(const at::Tensor& grid, int6
 }  // namespace
 
 void register_kernel_bindings(pybind11::module_& m) {
-  m.def("rms_norm_fwd", &rms_norm_fwd);
+  m.def("rms_norm_fwd", &rms_norm_fwd, pybind11::arg("x"), pybind11::arg("w"), pybind11::arg("eps"),
+        pybind11::arg("dest"), pybind11::arg("out_rows"), pybind11::arg("zero_pad") = true);
   m.def("rms_norm_bwd", &rms_norm_bwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("rope_qk", &rope_qk);

@@ -370,6 +370,56 @@ rope_qk_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__
     *reinterpret_cast<BF8*>(orow + off) = *reinterpret_cast<const BF8*>(row + off);
 }
 
+// Variant for few tokens (decoding, the denoise loop): one thread per (token, head, 8-channel chunk), so that
+// a handful of tokens still spreads over many SMs; it reloads cos/sin per head.
+__global__ void rope_qk_chunk_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                               const float* __restrict__ cos_t, const float* __restrict__ sin_t, int T, int W,
+                               int n_rot, int D, int inverse) {
+  const int half = D >> 1;
+  const int chunks_per_head = half >> 3;
+  const int rot_chunks = n_rot * chunks_per_head;
+  const int copy_chunks = (W - n_rot * D) >> 3;
+  const int per_row = rot_chunks + copy_chunks;
+  const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long>(T) * per_row) return;
+  const int t = static_cast<int>(idx / per_row);
+  const int c = static_cast<int>(idx - static_cast<long>(t) * per_row);
+  const __nv_bfloat16* row = in + static_cast<size_t>(t) * W;
+  __nv_bfloat16* orow = out + static_cast<size_t>(t) * W;
+  if (c >= rot_chunks) {
+    const int off = n_rot * D + (c - rot_chunks) * 8;
+    *reinterpret_cast<BF8*>(orow + off) = *reinterpret_cast<const BF8*>(row + off);
+    return;
+  }
+  const int h = c / chunks_per_head;
+  const int d0 = (c - h * chunks_per_head) * 8;
+  float a[8], b[8], oa[8], ob[8];
+  unpack8(*reinterpret_cast<const BF8*>(row + h * D + d0), a);
+  unpack8(*reinterpret_cast<const BF8*>(row + h * D + half + d0), b);
+  const float* cs = cos_t + static_cast<size_t>(t) * D;
+  const float* sn = sin_t + static_cast<size_t>(t) * D;
+  float c1[8], s1[8], c2[8], s2[8];  // 16-byte loads: d0 is a multiple of 8 floats, rows are 16-byte aligned
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    *reinterpret_cast<float4*>(c1 + 4 * q) = *reinterpret_cast<const float4*>(cs + d0 + 4 * q);
+    *reinterpret_cast<float4*>(s1 + 4 * q) = *reinterpret_cast<const float4*>(sn + d0 + 4 * q);
+    *reinterpret_cast<float4*>(c2 + 4 * q) = *reinterpret_cast<const float4*>(cs + half + d0 + 4 * q);
+    *reinterpret_cast<float4*>(s2 + 4 * q) = *reinterpret_cast<const float4*>(sn + half + d0 + 4 * q);
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    if (!inverse) {
+      oa[e] = a[e] * c1[e] - b[e] * s1[e];
+      ob[e] = b[e] * c2[e] + a[e] * s2[e];
+    } else {
+      oa[e] = a[e] * c1[e] + b[e] * s2[e];
+      ob[e] = b[e] * c2[e] - a[e] * s1[e];
+    }
+  }
+  *reinterpret_cast<BF8*>(orow + h * D + d0) = pack8(oa);
+  *reinterpret_cast<BF8*>(orow + h * D + half + d0) = pack8(ob);
+}
+
 // ------------------------------------------------------------------------------ routing plan
 // Single block: stable grouping of T tokens by expert id (E <= 8) with 128-row aligned segments.
 constexpr int ROUTE_THREADS = 1024;
@@ -739,6 +789,13 @@ int rope_qk(const void* in, void* out, const float* cos_t, const float* sin_t, i
   if (D % 16 != 0 || W % 8 != 0 || n_rot * D > W) return -1;
   const long total = static_cast<long>(D / 16) * T;  // D/16 threads per token
   if (total == 0) return 0;
+  if (total < 148 * 256) {  // too few tokens to fill the GPU with one thread per 8-channel column
+    const long per_row = static_cast<long>(n_rot) * (D / 16) + (W - n_rot * D) / 8;
+    rope_qk_chunk_kernel<<<static_cast<unsigned>((per_row * T + 255) / 256), 256, 0, s>>>(
+        reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(out), cos_t, sin_t, T, W, n_rot, D,
+        inverse);
+    return static_cast<int>(cudaGetLastError());
+  }
   rope_qk_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(
       reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(out), cos_t, sin_t, T, W, n_rot, D,
       inverse);

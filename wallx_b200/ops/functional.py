@@ -157,7 +157,8 @@ def linear_gelu(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor]) -> 
 class _RmsNormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, eps, dest, out_rows):
-        y, rstd = _C().rms_norm_fwd(x, w, float(eps), dest, int(out_rows))
+        # rows that no token maps to must be zero only when a backward pass will reduce over them
+        y, rstd = _C().rms_norm_fwd(x, w, float(eps), dest, int(out_rows), bool(any(ctx.needs_input_grad)))
         ctx.save_for_backward(x, w, rstd, dest if dest is not None else torch.empty(0))
         ctx.has_dest = dest is not None
         return y
