@@ -39,8 +39,6 @@ def parse():
     ap.add_argument("--transport", default="auto", choices=["auto", "dist", "symm"])
     ap.add_argument("--layers", type=int, default=0, help="debug only: override depth (invalidates the number)")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--overlap-push", action="store_true",
-                    help="N > 1, own transport: push updated parameters unit by unit while the next forward starts")
     ap.add_argument("--no-overlap-reduce", action="store_true",
                     help="N > 1, own transport: reduce-scatter after backward instead of per unit during it")
     ap.add_argument("--kernel-table", default="", help="after the timed runs, trace one more step and write per-kernel time shares here")
@@ -156,7 +154,6 @@ def main():
     engine = TrainEngine(model, lr=9e-5, weight_decay=0.1, max_grad_norm=1.0, grad_accum=accum, world=world, rank=rank,
                          transport=transport if world > 1 else "local", symm=symm)
     engine.overlap_reduce = (world > 1 and transport == "symm" and not args.no_overlap_reduce)
-    engine.overlap_push = engine.overlap_reduce and args.overlap_push
     n_params = sum(b.numel for b in engine.buffers)
 
     # ---- synthetic data: a small pool of distinct global batches, pinned on the host
@@ -262,7 +259,7 @@ def main():
                 "global_batch": global_batch, "per_gpu_batch": args.per_gpu_batch, "micro_batch": micro,
                 "grad_accum": accum, "seq_len": int(pool[0][0]["input_ids"].shape[1]),
                 "vit_patches_per_sample": 3 * 18 * 18, "params": n_params,
-                "parallelism": f"dp{world} (resident bf16 params; sharded fp32 master + Adam moments; transport={transport if world > 1 else 'local'}{', reduce-scatter overlapped with backward' if engine.overlap_reduce else ''}{', parameter push overlapped with the next forward' if engine.overlap_push else ''})",
+                "parallelism": f"dp{world} (resident bf16 params; sharded fp32 master + Adam moments; transport={transport if world > 1 else 'local'}{', reduce-scatter overlapped with backward' if engine.overlap_reduce else ''})",
                 "optimizer": "fused AdamW, wd 0.1, clip 1.0, fp32 master",
                 "l2_policy": "inputs and weights (>8 GB) are far larger than L2; no explicit flush",
                 "loss": loss_val,

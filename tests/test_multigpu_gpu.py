@@ -46,7 +46,6 @@ def _worker(rank, world, port, tmp, transport):
     eng = TrainEngine(m, lr=1e-3, weight_decay=0.1, max_grad_norm=1.0, grad_accum=1, world=world, rank=rank,
                       transport=transport, symm=symm)
     eng.overlap_reduce = overlap
-    eng.overlap_push = overlap
     g = torch.Generator().manual_seed(5)
     batches = []
     for _ in range(2 * world):
@@ -60,7 +59,6 @@ def _worker(rank, world, port, tmp, transport):
         eng.backward(m(mode="train", **b).loss)
         eng.optimizer_step(1e-3)
         norms.append(eng.grad_norm().item())
-    eng.wait_params()
     torch.cuda.synchronize()
     G.check_status()
     if symm is not None:

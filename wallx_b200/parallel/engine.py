@@ -89,13 +89,6 @@ class TrainEngine:
         # been enqueued. Which parameter comes last, and how many are touched, is learned from the
         # first step; a unit whose pattern differs in a later step is simply reduced after backward.
         self.overlap_reduce = False
-        # Overlap of the parameter push with the next forward: after the update the units are pushed
-        # in forward order on the side stream (root first: embeddings and heads are used at both
-        # ends), each followed by its own flag barrier; a forward pre-hook makes the compute stream
-        # wait for a unit's event right before the unit runs.
-        self.overlap_push = False
-        self._push_events: Dict[int, "torch.cuda.Event"] = {}
-        self._push_hooks_installed = False
         self._micro = 0
         self._armed = False
         self._learned = False
@@ -147,57 +140,8 @@ class TrainEngine:
             shards.append(out)
         return list(reversed(shards))
 
-    def _install_push_hooks(self) -> None:
-        names = dict(self.model.named_modules())
-        root_k = None
-        for k, b in enumerate(self.buffers):
-            if b.name == "root":
-                root_k = k
-                continue
-            mod = names.get(b.name)
-            if mod is None:
-                continue
-            mod.register_forward_pre_hook(self._make_wait_hook(k))
-        if root_k is not None:
-            self.model.register_forward_pre_hook(self._make_wait_hook(root_k))
-        self._push_hooks_installed = True
-
-    def _make_wait_hook(self, k: int):
-        def hook(_mod, _args):
-            ev = self._push_events.pop(k, None)
-            if ev is not None:
-                torch.cuda.current_stream().wait_event(ev)
-
-        return hook
-
-    def wait_params(self) -> None:
-        """Make the current stream wait for every outstanding parameter push (checkpointing, evaluation
-        code that reads parameters without going through the hooked modules)."""
-        for k in list(self._push_events):
-            torch.cuda.current_stream().wait_event(self._push_events.pop(k))
-
     def _all_gather_params(self) -> None:
         if self.transport == "local":
-            return
-        if self.transport == "symm" and self.overlap_reduce and self.overlap_push:
-            if not self._push_hooks_installed:
-                self._install_push_hooks()
-            dev = self.buffers[0].device
-            if self._comm_stream is None:
-                self._comm_stream = torch.cuda.Stream(device=dev)
-            main = torch.cuda.current_stream(dev)
-            self._comm_stream.wait_stream(main)  # the update has been enqueued
-            order = sorted(range(len(self.buffers)), key=lambda k: (self.buffers[k].name != "root", k))
-            with torch.cuda.stream(self._comm_stream):
-                for k in order:
-                    self.symm.push_unit(k)
-                    ev = torch.cuda.Event()
-                    ev.record(self._comm_stream)
-                    self._push_events[k] = ev
-            # A peer signals its first push barrier only after its own reduce-scatter and update: once
-            # that barrier has passed here, nobody reads this rank's gradient buffers any more, so
-            # the compute stream may clear them.
-            main.wait_event(self._push_events[order[0]])
             return
         if self.transport == "symm":
             self.symm.all_gather_params(self.buffers)
@@ -311,7 +255,6 @@ class TrainEngine:
 
     # ------------------------------------------------------------------ state
     def optimizer_state(self) -> Dict:
-        self.wait_params()
         return {"opt": self.optimizer.state_dict(), "world": self.world, "rank": self.rank,
                 "layout": [(b.name, b.numel, b.padded, list(zip(b.names, b.offsets))) for b in self.buffers]}
 

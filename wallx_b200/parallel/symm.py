@@ -20,9 +20,7 @@ from ..ops import _ext
 from ..ops import gemm as G
 
 MAX_VEC = 4096  # floats per rank in the small all-reduce scratch
-FLAG_WORDS = 8 * 256  # int32 flag slots: 8 for the global barrier, 8 per unit for the reduce-scatter (up to
-#                       127 units), then 8 per unit for the parameter push
-PUSH_FLAG_BASE = 8 * 128
+FLAG_WORDS = 8 * 128  # int32 flag slots: 8 for the global barrier, then 8 per unit (up to 127 units)
 
 
 class SymmComm:
@@ -128,15 +126,6 @@ class SymmComm:
         C = _ext.get()
         C.symm_barrier([p + 32 * (k + 1) for p in self.flag_ptrs], self.rank, self.unit_step, self.status)
         C.rs_reduce(self.grad_ptrs, self.table[k:k + 1], self.gshard, self.local_sumsq)
-
-    def push_unit(self, k: int) -> None:
-        """Push this rank's updated bf16 shard of unit k into every peer, then wait until every peer
-        has done the same for unit k (current stream): after that unit k's parameters are complete here."""
-        if PUSH_FLAG_BASE + 8 * (k + 1) > FLAG_WORDS:
-            raise ValueError("too many units for the per-unit flag block")
-        C = _ext.get()
-        C.ag_push(self.param_ptrs, self.table[k:k + 1], self.rank)
-        C.symm_barrier([p + 4 * (PUSH_FLAG_BASE + 8 * k) for p in self.flag_ptrs], self.rank, self.unit_step, self.status)
 
     def grad_shards(self) -> List[torch.Tensor]:
         return [self.gshard[o:o + n] for o, n in self.views]

@@ -194,7 +194,6 @@ class QwenVlAct_Trainer:
                                   param_group_fn=self._param_group_fn(), master_dtype=master if self.device.type == "cuda" else torch.float32)
         # per-unit reduce-scatter during backward (own transport only; YAML key `overlap_reduce`, default on)
         self.engine.overlap_reduce = transport == "symm" and bool(cfg.get("overlap_reduce", True))
-        self.engine.overlap_push = self.engine.overlap_reduce and bool(cfg.get("overlap_push", False))
         self.lr_scheduler = CosineWithMinLR(float(cfg["learning_rate"]), int(cfg.get("num_warmup_steps", 0)),
                                             int(cfg.get("num_training_steps", 1_000_000)), float(cfg.get("min_lr", 0.0)))
         model.enable_input_require_grads()
