@@ -88,13 +88,17 @@ def test_symm_transport_matches_nccl(tmp_path):
         assert torch.allclose(a, b, atol=8e-3, rtol=8e-3), k
         assert ((a - b).abs() > 2.5e-3).float().mean() < 0.2, k
     assert abs(s0["norms"][0] - d0["norms"][0]) / d0["norms"][0] < 2e-2
-    # reduce-scatter per unit during backward: the same kernels on the same data; only the order in
-    # which the squared-norm atomics land differs, so at most a few bf16 roundings may flip
+    # reduce-scatter per unit during backward: the same kernels on the same data. Runs are not bit-identical
+    # (fp32 atomics in the bias-gradient column sums and the squared norm land in another order), and Adam
+    # turns last-bit differences of noise-level gradients (e.g. the key bias, whose true gradient is zero)
+    # into sign flips of an lr-sized update, so the comparison is the same as for the NCCL transport.
     o0, o1 = torch.load(tmp_path / "symm_overlap_0.pt"), torch.load(tmp_path / "symm_overlap_1.pt")
     for k in s0["params"]:
         assert torch.equal(o0["params"][k], o1["params"][k]), k  # replicas identical
-        assert torch.allclose(o0["params"][k], s0["params"][k], atol=8e-3, rtol=8e-3), k
-        assert (o0["params"][k] != s0["params"][k]).float().mean() < 0.01, k
+        a, b = o0["params"][k], s0["params"][k]
+        assert torch.allclose(a, b, atol=8e-3, rtol=8e-3), k
+        assert ((a - b).abs() > 2.5e-3).float().mean() < 0.2, k
+    assert abs(o0["norms"][0] - s0["norms"][0]) / s0["norms"][0] < 1e-3
     assert o0["early_units"] >= 3 and o1["early_units"] >= 3
 
 
