@@ -49,6 +49,10 @@ struct alignas(16) BF8 {
   __nv_bfloat162 v[4];
 };
 
+constexpr int kRsMaxBlocks = 8192;
+__device__ float g_rs_scratch[kRsMaxBlocks];
+__device__ unsigned g_rs_counter = 0;
+
 __global__ void __launch_bounds__(256)
 rs_reduce_kernel(PeerPtrs grads, const ShardDesc* __restrict__ table, int world, float* __restrict__ out,
                  float* __restrict__ sumsq) {
@@ -86,10 +90,32 @@ rs_reduce_kernel(PeerPtrs grads, const ShardDesc* __restrict__ table, int world,
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
   __syncthreads();
+  // Deterministic grid reduction (see sumsq_bf16_kernel): the last block adds the parked sums in order.
+  __shared__ bool is_last;
+  const unsigned nblk = gridDim.x * gridDim.y;
+  const unsigned bid = blockIdx.y * gridDim.x + blockIdx.x;
   if (threadIdx.x == 0) {
     float t = 0.f;
     for (int w = 0; w < 8; ++w) t += red[w];
-    atomicAdd(sumsq, t);
+    g_rs_scratch[bid] = t;
+    __threadfence();
+    is_last = atomicInc(&g_rs_counter, nblk - 1) == nblk - 1;
+  }
+  __syncthreads();
+  if (is_last) {
+    __threadfence();
+    float t = 0.f;
+    for (unsigned i = threadIdx.x; i < nblk; i += blockDim.x) t += reinterpret_cast<volatile float*>(g_rs_scratch)[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = t;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float u = 0.f;
+      for (int w = 0; w < 8; ++w) u += red[w];
+      *sumsq += u;  // launches that share `sumsq` must be ordered by their streams
+    }
   }
 }
 
@@ -189,6 +215,8 @@ int rs_reduce(const PeerPtrs& grads, const ShardDesc* table_dev, int nbuf, int w
   // about 16 resident blocks per SM in total, whatever the number of buffers
   int gx = (148 * 16 + nbuf - 1) / nbuf;
   gx = gx < 8 ? 8 : gx;
+  if (static_cast<long>(gx) * nbuf > kRsMaxBlocks) gx = kRsMaxBlocks / nbuf;
+  if (gx < 1) return -1;
   rs_reduce_kernel<<<dim3(gx, nbuf), 256, 0, s>>>(grads, table_dev, world, out, sumsq);
   return static_cast<int>(cudaGetLastError());
 }

@@ -117,7 +117,7 @@ at::Tensor gather_rows(const at::Tensor& x, const at::Tensor& idx) {
 at::Tensor column_sum(const at::Tensor& x) {
   check_bf16(x, "x");
   c10::cuda::CUDAGuard g(x.device());
-  at::Tensor acc = at::zeros({x.size(1)}, x.options().dtype(at::kFloat));
+  at::Tensor acc = at::empty({wx::column_sum_slabs(x.size(0)), x.size(1)}, x.options().dtype(at::kFloat));
   at::Tensor out = at::empty({x.size(1)}, x.options());
   WX_CHECK_RC(wx::column_sum(x.data_ptr(), acc.data_ptr<float>(), out.data_ptr(), x.size(0), x.size(1), cur_stream()),
               "column_sum");

@@ -270,11 +270,16 @@ rms_norm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat
       dxr[lane + 32 * c] = pack8(o);
     }
   }
+  // warps add their sums one after the other, so the result does not depend on timing
+  for (int wv = 0; wv < 8; ++wv) {
+    if (warp == wv) {
 #pragma unroll
-  for (int c = 0; c < CH; ++c)
+      for (int c = 0; c < CH; ++c)
 #pragma unroll
-    for (int e = 0; e < 8; ++e) atomicAdd(&dws[(lane + 32 * c) * 8 + e], dwacc[c][e]);
-  __syncthreads();
+        for (int e = 0; e < 8; ++e) dws[(lane + 32 * c) * 8 + e] += dwacc[c][e];
+    }
+    __syncthreads();
+  }
   float* dp = dw_partial + static_cast<size_t>(blockIdx.x) * C;
   for (int i = threadIdx.x; i < C; i += 256) dp[i] = dws[i];
 }
@@ -522,12 +527,15 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const in
 }
 
 // ------------------------------------------------------------------------------ column sum
-__global__ void column_sum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ acc, int R, int C,
+// Two deterministic passes (no atomics, so bias gradients are reproducible bit for bit): row slab y
+// writes its partial sums to part[y][C]; the second kernel adds the slabs in order and rounds.
+__global__ void column_sum_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ part, int R, int C,
                                   int rows_per_block) {
   const int c2 = blockIdx.x * blockDim.x + threadIdx.x;  // pair index
   if (c2 * 2 >= C) return;
   const int r0 = blockIdx.y * rows_per_block;
   const int r1 = min(R, r0 + rows_per_block);
+  float* acc = part + static_cast<size_t>(blockIdx.y) * C;
   float s0 = 0.f, s1 = 0.f;
   if (c2 * 2 + 1 < C && (C & 1) == 0) {
     for (int r = r0; r < r1; ++r) {
@@ -535,16 +543,24 @@ __global__ void column_sum_kernel(const __nv_bfloat16* __restrict__ x, float* __
       s0 += f.x;
       s1 += f.y;
     }
-    atomicAdd(&acc[c2 * 2], s0);
-    atomicAdd(&acc[c2 * 2 + 1], s1);
+    acc[c2 * 2] = s0;
+    acc[c2 * 2 + 1] = s1;
   } else {
     for (int r = r0; r < r1; ++r) {
       s0 += __bfloat162float(x[static_cast<size_t>(r) * C + c2 * 2]);
       if (c2 * 2 + 1 < C) s1 += __bfloat162float(x[static_cast<size_t>(r) * C + c2 * 2 + 1]);
     }
-    atomicAdd(&acc[c2 * 2], s0);
-    if (c2 * 2 + 1 < C) atomicAdd(&acc[c2 * 2 + 1], s1);
+    acc[c2 * 2] = s0;
+    if (c2 * 2 + 1 < C) acc[c2 * 2 + 1] = s1;
   }
+}
+__global__ void column_sum_finish_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out, int nslab,
+                                         int C) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  float s = 0.f;
+  for (int y = 0; y < nslab; ++y) s += part[static_cast<size_t>(y) * C + c];
+  out[c] = __float2bfloat16(s);
 }
 __global__ void f32_to_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, long n) {
   const long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -632,6 +648,10 @@ ce_bwd_kernel(__nv_bfloat16* __restrict__ logits, const long* __restrict__ label
 
 // ------------------------------------------------------------------------------ optimizer
 // sum of squares of a bf16 buffer accumulated (atomically) into out[0].
+constexpr int kSumsqMaxBlocks = 148 * 8;
+__device__ float g_sumsq_scratch[kSumsqMaxBlocks];
+__device__ unsigned g_sumsq_counter = 0;
+
 __global__ void sumsq_bf16_kernel(const __nv_bfloat16* __restrict__ g, long n, float* __restrict__ out) {
   __shared__ float red[32];
   float s = 0.f;
@@ -650,7 +670,23 @@ __global__ void sumsq_bf16_kernel(const __nv_bfloat16* __restrict__ g, long n, f
     s += f * f;
   }
   s = block_sum(s, red);
-  if (threadIdx.x == 0) atomicAdd(out, s);
+  // Deterministic grid reduction: every block parks its sum, the block that finishes last adds them
+  // in index order (no float atomics, so the gradient norm is reproducible bit for bit).
+  __shared__ bool is_last;
+  const unsigned nblk = gridDim.x;
+  if (threadIdx.x == 0) {
+    g_sumsq_scratch[blockIdx.x] = s;
+    __threadfence();
+    is_last = atomicInc(&g_sumsq_counter, nblk - 1) == nblk - 1;
+  }
+  __syncthreads();
+  if (is_last) {
+    __threadfence();
+    float t = 0.f;
+    for (unsigned i = threadIdx.x; i < nblk; i += blockDim.x) t += reinterpret_cast<volatile float*>(g_sumsq_scratch)[i];
+    t = block_sum(t, red);
+    if (threadIdx.x == 0) *out += t;
+  }
 }
 
 // Fused: grad (bf16) * inv_accum * clip -> AdamW on fp32 master/m/v -> bf16 param.
@@ -824,15 +860,21 @@ int gather_rows(const void* x, const int* idx, void* out, int T, int C, cudaStre
   return static_cast<int>(cudaGetLastError());
 }
 
-int column_sum(const void* x, float* acc_zeroed, void* out_bf16, int R, int C, cudaStream_t s) {
-  if (R == 0 || C == 0) return 0;
-  const int pairs = (C + 1) / 2;
+int column_sum_slabs(int R) {
   int ysplit = (R + 255) / 256;
   if (ysplit > 256) ysplit = 256;
+  return ysplit < 1 ? 1 : ysplit;
+}
+
+int column_sum(const void* x, float* partials, void* out_bf16, int R, int C, cudaStream_t s) {
+  if (C == 0) return 0;
+  if (R == 0) return static_cast<int>(cudaMemsetAsync(out_bf16, 0, static_cast<size_t>(C) * 2, s));
+  const int pairs = (C + 1) / 2;
+  const int ysplit = column_sum_slabs(R);
   const int rpb = (R + ysplit - 1) / ysplit;
   dim3 grid((pairs + 127) / 128, ysplit);
-  column_sum_kernel<<<grid, 128, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), acc_zeroed, R, C, rpb);
-  f32_to_bf16_kernel<<<(C + 255) / 256, 256, 0, s>>>(acc_zeroed, reinterpret_cast<__nv_bfloat16*>(out_bf16), C);
+  column_sum_kernel<<<grid, 128, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), partials, R, C, rpb);
+  column_sum_finish_kernel<<<(C + 255) / 256, 256, 0, s>>>(partials, reinterpret_cast<__nv_bfloat16*>(out_bf16), ysplit, C);
   return static_cast<int>(cudaGetLastError());
 }
 

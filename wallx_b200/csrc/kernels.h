@@ -18,7 +18,9 @@ int rope_qk(const void* in, void* out, const float* cos_t, const float* sin_t, i
 int route_plan(const int* types, int T, int E, int rows, int* dest, int* seg, int* segk, int* inv, cudaStream_t s);
 int permute_rows(const void* x, const int* dest, void* out, int T, int C, cudaStream_t s);
 int gather_rows(const void* x, const int* idx, void* out, int T, int C, cudaStream_t s);
-int column_sum(const void* x, float* acc_zeroed, void* out_bf16, int R, int C, cudaStream_t s);
+// `partials`: fp32 scratch of column_sum_slabs(R) * C elements (need not be cleared)
+int column_sum_slabs(int R);
+int column_sum(const void* x, float* partials, void* out_bf16, int R, int C, cudaStream_t s);
 int ce_fwd(const void* logits, const long* labels, float* loss, float* lse, long* pred, int R, int V, long ld,
            cudaStream_t s);
 int ce_bwd(void* logits, const long* labels, const float* lse, const float* dloss, int R, int V, long ld,

@@ -114,11 +114,12 @@ class TrainEngine:
                 self.symm.begin_step()
                 self._early = set()
             self._step_begun = False
+            # the side stream first: the reductions add to one squared-norm word and must not overlap each other
+            if self._comm_stream is not None:
+                torch.cuda.current_stream(self.buffers[0].device).wait_stream(self._comm_stream)
             for k in range(len(self.buffers)):  # units that were not reduced during backward
                 if k not in self._early:
                     self.symm.reduce_scatter_unit(k)
-            if self._comm_stream is not None:
-                torch.cuda.current_stream(self.buffers[0].device).wait_stream(self._comm_stream)
             if not self._learned and self._order:
                 for k, order in self._order.items():
                     self._expected[k] = len({i for i, _ in order})
