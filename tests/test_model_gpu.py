@@ -184,3 +184,36 @@ def test_flow_engine_graph_matches_eager_sampler():
         scale = ref.abs().max().item()
         assert (ref - got).abs().max().item() < 1e-3 * scale
     G.check_status()
+
+
+def test_training_is_bit_reproducible():
+    """Two runs of the same two optimizer steps give bit-identical parameters (no float atomics on the
+    training path: ordered column sums, norm-weight gradients and squared gradient norms)."""
+    from wallx_b200.data.collator import to_device
+    from wallx_b200.ops import gemm as G
+    from wallx_b200.parallel.engine import TrainEngine
+
+    def run():
+        cfg, model, _ = _build("flow")
+        from wallx_b200.data.collator import add_pack_info
+        from wallx_b200.data.synthetic import make_batch
+
+        m = copy.deepcopy(model).to(torch.bfloat16).cuda()
+        eng = TrainEngine(m, lr=1e-3, weight_decay=0.1, max_grad_norm=1.0, grad_accum=1)
+        g = torch.Generator().manual_seed(5)
+        for _ in range(2):
+            b = add_pack_info(make_batch(cfg, m.processor, 2, views=1, image_hw=(112, 112), prompt_len=16, horizon=16,
+                                         generator=g), cfg)
+            b["flow_noise"] = torch.randn(b["action_chunk"].shape, generator=g)
+            b["flow_time"] = torch.rand(2, generator=g)
+            eng.backward(m(mode="train", **to_device(b, "cuda", torch.bfloat16)).loss)
+            eng.optimizer_step(1e-3)
+        torch.cuda.synchronize()
+        G.check_status()
+        return {n: p.detach().clone() for n, p in m.named_parameters()}, eng.grad_norm().item()
+
+    a, na = run()
+    b, nb = run()
+    assert na == nb
+    for k in a:
+        assert torch.equal(a[k], b[k]), k
