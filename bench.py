@@ -212,8 +212,10 @@ def main():
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    t_host0 = time.perf_counter()
     for i in range(args.steps):
         loss = train_step(resident[i % len(resident)])
+    host_ms = (time.perf_counter() - t_host0) * 1e3 / args.steps  # time the host needs to enqueue one step
     e1.record()
     barrier()
     ms_dev = e0.elapsed_time(e1)
@@ -261,6 +263,7 @@ def main():
                 "vit_patches_per_sample": 3 * 18 * 18, "params": n_params,
                 "parallelism": f"dp{world} (resident bf16 params; sharded fp32 master + Adam moments; transport={transport if world > 1 else 'local'}{', reduce-scatter overlapped with backward' if engine.overlap_reduce else ''})",
                 "optimizer": "fused AdamW, wd 0.1, clip 1.0, fp32 master",
+                "host_enqueue_ms_per_step": round(host_ms, 1),
                 "l2_policy": "inputs and weights (>8 GB) are far larger than L2; no explicit flush",
                 "loss": loss_val,
             },

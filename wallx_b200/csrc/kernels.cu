@@ -825,7 +825,9 @@ int rope_qk(const void* in, void* out, const float* cos_t, const float* sin_t, i
   if (D % 16 != 0 || W % 8 != 0 || n_rot * D > W) return -1;
   const long total = static_cast<long>(D / 16) * T;  // D/16 threads per token
   if (total == 0) return 0;
-  if (total < 148 * 256) {  // too few tokens to fill the GPU with one thread per 8-channel column
+  // few tokens: too little parallelism with one thread per 8-channel column; head dims that are not a
+  // multiple of 128 (ViT: 80): a token's threads would read 80-byte pieces
+  if (total < 148 * 256 || D % 128 != 0) {
     const long per_row = static_cast<long>(n_rot) * (D / 16) + (W - n_rot * D) / 8;
     rope_qk_chunk_kernel<<<static_cast<unsigned>((per_row * T + 255) / 256), 256, 0, s>>>(
         reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(out), cos_t, sin_t, T, W, n_rot, D,
