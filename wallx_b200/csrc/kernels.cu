@@ -554,7 +554,7 @@ __global__ void column_sum_kernel(const __nv_bfloat16* __restrict__ x, float* __
     if (c2 * 2 + 1 < C) acc[c2 * 2 + 1] = s1;
   }
 }
-// C % 8 == 0 and 16-byte aligned rows: 8 columns per thread, 16-byte loads, four rows in flight
+// C % 8 == 0 and 16-byte aligned rows: 8 columns per thread, 16-byte loads, eight rows in flight
 __global__ void column_sum8_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ part, int R, int C,
                                    int rows_per_block) {
   const int c8 = blockIdx.x * blockDim.x + threadIdx.x;
@@ -564,12 +564,12 @@ __global__ void column_sum8_kernel(const __nv_bfloat16* __restrict__ x, float* _
   float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   const __nv_bfloat16* col = x + c8 * 8;
   int r = r0;
-  for (; r + 4 <= r1; r += 4) {
-    BF8 v[4];
+  for (; r + 8 <= r1; r += 8) {
+    BF8 v[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const BF8*>(col + static_cast<size_t>(r + u) * C);
+    for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const BF8*>(col + static_cast<size_t>(r + u) * C);
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {  // rows are added in order, so the result does not depend on the unrolling
+    for (int u = 0; u < 8; ++u) {  // rows are added in order, so the result does not depend on the unrolling
       float f[8];
       unpack8(v[u], f);
 #pragma unroll
@@ -895,8 +895,8 @@ int gather_rows(const void* x, const int* idx, void* out, int T, int C, cudaStre
 }
 
 int column_sum_slabs(int R) {
-  int ysplit = (R + 255) / 256;
-  if (ysplit > 256) ysplit = 256;
+  int ysplit = (R + 63) / 64;  // 64-row slabs: enough blocks to keep every SM's memory pipe full
+  if (ysplit > 512) ysplit = 512;
   return ysplit < 1 ? 1 : ysplit;
 }
 
