@@ -211,3 +211,24 @@ def test_timers_accumulate_and_log(capsys):
     out = capsys.readouterr().out
     assert "fwd" in out and "(min, max)" in out
     assert t("fwd", 0).elapsed() == 0.0
+
+
+def test_example_yaml_has_every_trainer_key():
+    """The shipped fine-tuning YAML parses through the CLI loader and carries every key without a default."""
+    import os
+
+    import train_qact
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = train_qact.load_config(os.path.join(root, "workspace", "lerobot_example", "finetune_flow.yml"))
+    for key in ("pretrained_wallx_path", "save_path", "learning_rate", "min_lr", "num_warmup_steps", "num_training_steps",
+                "num_epoch", "gradient_accumulation_steps", "batch_size_per_gpu", "dof_config", "agent_pos_config", "data"):
+        assert key in cfg, key
+    assert cfg["data"]["model_type"] == "qwen2_5"
+    assert cfg["dof_config"] == cfg["agent_pos_config"] and sum(cfg["dof_config"].values()) == 20
+    d = cfg["data"]
+    assert d["action_horizon"] == 32 and d["obs_action_keys"] == d["predict_action_keys"] == list(cfg["dof_config"])
+    assert d["lerobot_config"]["repo_id"] == "lerobot/aloha_mobile_cabinet" and d["resolution"]["face_view"] == 256
+    from wallx_b200.data.lerobot import get_data_configs
+
+    assert get_data_configs(d)["action_horizon"] == 33

@@ -7,7 +7,7 @@ NUM_GPUS=$(echo "$CUDA_VISIBLE_DEVICES" | tr ',' '\n' | wc -l)
 echo "[current time: $(date +'%Y-%m-%d %H:%M:%S')]"
 
 code_dir="$(cd "$(dirname "$0")/../.." && pwd)"
-config_path="${CONFIG:-$code_dir/workspace/lerobot_example/config_qact.yml}"
+config_path="${CONFIG:-$code_dir/workspace/lerobot_example/finetune_flow.yml}"
 PORT=${PORT:-$((21000 + RANDOM % 30000))}
 SEED=${SEED:-10239}
 
