@@ -187,11 +187,15 @@ class QwenVlAct_Trainer:
             from ..parallel.symm import SymmComm
 
             symm = SymmComm(torch.distributed.group.WORLD, self.device)
-        master = torch.bfloat16 if str(cfg.get("optimizer_dtype", "fp32")) in ("bf16", "bfloat16") else torch.float32
+        master = torch.float32
+        if str(cfg.get("optimizer_dtype", "fp32")) in ("bf16", "bfloat16"):
+            # the reference keeps bf16 Adam states; the fused CUDA update works on fp32 shards (they are
+            # sharded over the GPUs, so the memory cost is 12 bytes per parameter divided by the world size)
+            print_rank_last("optimizer_dtype=bf16 requested: this engine keeps fp32 master weights and moments")
         self.engine = TrainEngine(model, lr=float(cfg["learning_rate"]), weight_decay=float(cfg.get("weight_decay", 0.1)),
                                   max_grad_norm=float(cfg.get("max_grad_norm", 1.0)), grad_accum=self.grad_accum,
                                   world=self.world, rank=self.rank, transport=transport, symm=symm,
-                                  param_group_fn=self._param_group_fn(), master_dtype=master if self.device.type == "cuda" else torch.float32)
+                                  param_group_fn=self._param_group_fn(), master_dtype=master)
         # per-unit reduce-scatter during backward (own transport only; YAML key `overlap_reduce`, default on)
         self.engine.overlap_reduce = transport == "symm" and bool(cfg.get("overlap_reduce", True))
         self.lr_scheduler = CosineWithMinLR(float(cfg["learning_rate"]), int(cfg.get("num_warmup_steps", 0)),

@@ -1,16 +1,28 @@
-#!/bin/bash
-# One process per GPU on one node (the reference launches the same script through `accelerate launch`,
-# workspace/lerobot_example/run.sh:1-23).
-set -e
-export CUDA_VISIBLE_DEVICES=${CUDA_VISIBLE_DEVICES:-0,1,2,3,4,5,6,7}
-NUM_GPUS=$(echo "$CUDA_VISIBLE_DEVICES" | tr ',' '\n' | wc -l)
-echo "[current time: $(date +'%Y-%m-%d %H:%M:%S')]"
+#!/usr/bin/env bash
+# Fine-tune on every visible GPU of this node: one process per GPU through torch.distributed.run.
+#   CONFIG=/path/to.yml SEED=42 GPUS=0,1,2,3 bash workspace/lerobot_example/run.sh
+set -euo pipefail
 
-code_dir="$(cd "$(dirname "$0")/../.." && pwd)"
-config_path="${CONFIG:-$code_dir/workspace/lerobot_example/finetune_flow.yml}"
-PORT=${PORT:-$((21000 + RANDOM % 30000))}
-SEED=${SEED:-10239}
+here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
+repo="$(cd "$here/../.." && pwd)"
+config="${CONFIG:-$here/finetune_flow.yml}"
+seed="${SEED:-42}"
 
-LAUNCHER="python -m torch.distributed.run --nnodes=1 --nproc-per-node $NUM_GPUS --master-addr 127.0.0.1 --master-port $PORT"
-echo "Running: $LAUNCHER $code_dir/train_qact.py --config $config_path --seed $SEED"
-$LAUNCHER "$code_dir/train_qact.py" --config "$config_path" --seed "$SEED"
+if [[ -n "${GPUS:-}" ]]; then
+  export CUDA_VISIBLE_DEVICES="$GPUS"
+fi
+if [[ -n "${CUDA_VISIBLE_DEVICES:-}" ]]; then
+  IFS=',' read -r -a devs <<< "$CUDA_VISIBLE_DEVICES"
+  nproc="${#devs[@]}"
+else
+  nproc="$(python -c 'import torch; print(max(torch.cuda.device_count(), 1))')"
+fi
+port="${PORT:-$((20000 + RANDOM % 20000))}"
+
+echo "$(date '+%F %T') launching $nproc process(es), config $config, seed $seed, rendezvous 127.0.0.1:$port"
+if [[ "$nproc" -eq 1 ]]; then
+  exec python "$repo/train_qact.py" --config "$config" --seed "$seed"
+fi
+exec python -m torch.distributed.run --nnodes=1 --nproc-per-node "$nproc" \
+  --master-addr 127.0.0.1 --master-port "$port" \
+  "$repo/train_qact.py" --config "$config" --seed "$seed"
