@@ -267,6 +267,7 @@ def main():
                 "parallelism": f"dp{world} (resident bf16 params; sharded fp32 master + Adam moments; transport={transport if world > 1 else 'local'}{', reduce-scatter overlapped with backward' if engine.overlap_reduce else ''})",
                 "optimizer": "fused AdamW, wd 0.1, clip 1.0, fp32 master",
                 "host_enqueue_ms_per_step": round(host_ms, 1),
+                "peak_device_memory_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 1),
                 "l2_policy": "inputs and weights (>8 GB) are far larger than L2; no explicit flush",
                 "loss": loss_val,
             },
