@@ -1,4 +1,7 @@
 // Host API of the tcgen05 varlen attention kernels (raw pointers + stream).
+// Reference parity: flash-attn 2 behind wall_x/model/qwen2_5_based/modeling_qwen2_5_vl.py:208-210 (ViT, varlen,
+// non-causal) and :1008-1015 (LLM, causal, GQA), plus the bidirectional action block of the mask builder in
+// modeling_qwen2_5_vl_act.py:276-732.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>

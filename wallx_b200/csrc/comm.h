@@ -1,5 +1,8 @@
 // Peer-memory collectives for the sharded optimizer (raw pointers + stream). All kernels read or
 // write other GPUs' memory through plain peer pointers over NVLink / NVSwitch; no NCCL call.
+// Reference parity: the NCCL reduce-scatter / all-gather that torch FSDP2 issues for the reference trainer
+// (train_qact.py:42-49, wall_x/trainer/qwen_vl_act_trainer.py:609-611), its clip_grad_norm_ all-reduce (:335-337)
+// and the per-step scalar gathers (:352-423).
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>

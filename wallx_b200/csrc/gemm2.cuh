@@ -1,5 +1,6 @@
 // CTA-pair variant of the GEMM core: one 256 x 256 output tile per pair of SMs
-// (`tcgen05.mma.cta_group::2`). Included by gemm.cu after its shared declarations.
+// (`tcgen05.mma.cta_group::2`). Included by gemm.cu after its shared declarations. Serves the same calls as the
+// single-CTA kernel (reference: csrc/dual_asym_grouped_gemm.cu:49-136 and the cuBLAS GEMMs behind every nn.Linear).
 //
 // Why: a 128 x 256 x 64 step of the single-CTA kernel moves 48 KB through one SM's shared memory
 // twice (TMA write + operand read), which takes longer than the MMAs themselves; with a pair each

@@ -1,5 +1,8 @@
 // Host launchers of the non-GEMM kernels (raw pointers + stream; no torch types). Every function
 // returns a CUDA error code (0 = ok) or a negative value for an unsupported shape.
+// Reference parity: csrc/permute.cu:39-262 (permute / unpermute), csrc/rope.cu:48-330 (mRoPE), the unfused ATen
+// RMSNorm of modeling_qwen2_5_vl.py:131-136, the SiLU * up product of modeling_qwen2_5_vl_act.py:79-82, the unreduced
+// cross entropy of :1431-1444 and torch.optim.AdamW (wall_x/trainer/qwen_vl_act_trainer.py:577-581).
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>

@@ -7,6 +7,9 @@ peer's gradient shard and sums in fp32, a one-shot all-gather that pushes the up
 into every peer's resident parameters, and a small-vector all-reduce for the gradient norm and
 logged scalars. No NCCL call is made on these paths (NCCL only serves the bootstrap rendezvous).
 
+Reference parity: the NCCL collectives that accelerate / torch FSDP2 issue for the reference trainer
+(train_qact.py:42-49; wall_x/trainer/qwen_vl_act_trainer.py:335-337 grad-norm all-reduce, :352-423 scalar gathers).
+
 Two bf16 arenas (parameters, gradients) are allocated once; every :class:`FlatBuffer` is a view, so
 one rendezvous covers the whole model.
 """
