@@ -76,6 +76,8 @@ struct Cfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 };
 
+constexpr int kRasterGroup = 8;
+
 struct TileInfo {
   int prob, mt, nt;
 };
@@ -111,18 +113,33 @@ __device__ __forceinline__ void load_dims(const GemmArgs& args, Dims& d) {
   }
 }
 
-__device__ __forceinline__ TileInfo decode_tile(const Dims& d, int t, int rot0 = 0, int rot1 = 0) {
+__device__ __forceinline__ TileInfo decode_tile(const Dims& d, int t, bool gathered = false, int rot0 = 0, int rot1 = 0) {
   TileInfo ti;
   ti.prob = 0;
   if (t >= d.tiles[0]) {
     ti.prob = 1;
     t -= d.tiles[0];
   }
-  // m fastest: CTAs that run concurrently share the same few B (weight) tiles in L2.
+  // Grouped raster: tiles are walked in bands of kRasterGroup row tiles, column by column inside a
+  // band, so that the CTAs running at the same time cover about 8 row tiles x 8..18 column tiles.
+  // Every A tile is then shared by the CTAs of its row and every B tile by the 8 CTAs of its column
+  // through L2, instead of one operand being streamed from DRAM once per tile of the other.
+  // (With gathered weights the column order is the arrival order: one band, rows fastest.)
   const int tm = d.tiles_m[ti.prob];
-  ti.nt = t / tm;
-  ti.mt = t - ti.nt * tm;
-  const int rot = ti.prob ? rot1 : rot0;
+  if (gathered) {
+    ti.nt = t / tm;
+    ti.mt = t - ti.nt * tm;
+  } else {
+    const int tn = d.tiles_n[ti.prob];
+    const int per_band = kRasterGroup * tn;
+    const int band = t / per_band;
+    const int r = t - band * per_band;
+    const int m_first = band * kRasterGroup;
+    const int gm = min(kRasterGroup, tm - m_first);
+    ti.nt = r / gm;
+    ti.mt = m_first + (r - ti.nt * gm);
+  }
+  const int rot = gathered ? (ti.prob ? rot1 : rot0) : 0;
   if (rot) {  // gathered weights: start with the tiles this rank owns
     ti.nt += rot;
     const int tn = d.tiles_n[ti.prob];
@@ -512,7 +529,7 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
       bool ok = true;
       int ag_ready[2] = {0, 0};  // MN-major B: 256-row blocks of the weight known to be in place
       for (int t = cta; t < total_tiles && ok; t += ncta) {
-        const TileInfo ti = decode_tile(d, t, rot0, rot1);
+        const TileInfo ti = decode_tile(d, t, AG, rot0, rot1);
         const Problem& p = args.p[ti.prob];
         const int m_base = d.m0[ti.prob] + ti.mt * BM;
         const int n_base = ti.nt * BN;
@@ -572,7 +589,7 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
       int it = 0;
       bool ok = true;
       for (int t = cta; t < total_tiles && ok; t += ncta, ++it) {
-        const TileInfo ti = decode_tile(d, t, rot0, rot1);
+        const TileInfo ti = decode_tile(d, t, AG, rot0, rot1);
         const int nkb = (d.K[ti.prob] + BK - 1) / BK;
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
@@ -613,7 +630,7 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
     const int chunk1 = (kChunks >= 2) ? chunk0 + kChunks / 2 : (half == 0 ? 1 : 0);
     int it = 0;
     for (int t = cta; t < total_tiles; t += ncta, ++it) {
-      const TileInfo ti = decode_tile(d, t, rot0, rot1);
+      const TileInfo ti = decode_tile(d, t, AG, rot0, rot1);
       const Problem& p = args.p[ti.prob];
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
