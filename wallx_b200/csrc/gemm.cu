@@ -17,6 +17,7 @@
 #include "gemm.h"
 #include "ptx.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace wx {
@@ -57,6 +58,7 @@ struct AgDev {
 struct GemmArgs {
   Problem p[2];
   int nprob;
+  int raster_group;  // 0: default
   AgDev ag[2];  // one per problem; used by the AG instantiations only
 };
 
@@ -84,10 +86,12 @@ struct TileInfo {
 
 struct Dims {
   int M[2], K[2], m0[2], k0[2], tiles_m[2], tiles_n[2], tiles[2];
+  int group;  // row tiles per raster band
 };
 
 template <int BN, int TM = BM>
 __device__ __forceinline__ void load_dims(const GemmArgs& args, Dims& d) {
+  d.group = args.raster_group > 0 ? args.raster_group : kRasterGroup;
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     if (i < args.nprob) {
@@ -131,11 +135,12 @@ __device__ __forceinline__ TileInfo decode_tile(const Dims& d, int t, bool gathe
     ti.mt = t - ti.nt * tm;
   } else {
     const int tn = d.tiles_n[ti.prob];
-    const int per_band = kRasterGroup * tn;
+    const int G = d.group;
+    const int per_band = G * tn;
     const int band = t / per_band;
     const int r = t - band * per_band;
-    const int m_first = band * kRasterGroup;
-    const int gm = min(kRasterGroup, tm - m_first);
+    const int m_first = band * G;
+    const int gm = min(G, tm - m_first);
     ti.nt = r / gm;
     ti.mt = m_first + (r - ti.nt * gm);
   }
@@ -735,6 +740,13 @@ int launch_bn(const GemmArgs& args, bool a_mn, bool b_mn, int grid, cudaStream_t
 
 int fill_args(GemmArgs& args, const GemmCall* calls, int ncalls, int bn) {
   args.nprob = ncalls;
+  {
+    static const int env_group = [] {
+      const char* e = getenv("WX_RASTER_GROUP");
+      return e ? atoi(e) : 0;
+    }();
+    args.raster_group = env_group;
+  }
   args.ag[0] = AgDev{};
   args.ag[1] = AgDev{};
   for (int i = 0; i < ncalls; ++i) {
