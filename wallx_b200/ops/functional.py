@@ -12,6 +12,7 @@ routing uses 128-row aligned segments so that forward, dgrad and wgrad are all t
 from __future__ import annotations
 
 import math
+import os
 from typing import List, Optional, Sequence, Tuple
 
 import torch
@@ -220,6 +221,12 @@ class _GateUpFn(torch.autograd.Function):
         return dx, dw, db
 
 
+# SwiGLU backward inside the down-projection's dgrad epilogue (dL/dh never goes to memory) or as a separate
+# streaming kernel after a plain dgrad GEMM. Both are kept: which one is faster depends on how far the GEMM is
+# from being epilogue-bound (environment variable WX_FUSE_SWIGLU_BWD=0/1).
+FUSE_SWIGLU_BWD = os.environ.get("WX_FUSE_SWIGLU_BWD", "1") != "0"
+
+
 class _SwiGLUFfnFn(torch.autograd.Function):
     """Whole SwiGLU FFN, ``down(silu(gate(x)) * up(x)) (+ bias) (+ residual)``, as one autograd node so
     that the backward of the activation runs in the epilogue of the down-projection's dgrad GEMM:
@@ -243,9 +250,14 @@ class _SwiGLUFfnFn(torch.autograd.Function):
     def backward(ctx, dy):
         x, w_gu, w_dn, gu, h = ctx.saved_tensors
         dy = dy.contiguous()
-        dgu = torch.empty_like(gu)
-        # dL/dh = dy @ w_dn, turned into dL/d(gate|up) in the epilogue
-        G.launch([G.GemmSpec(dy, w_dn, dgu, b_mn=True, out2=gu, flags=G.SWIGLU_BWD)])
+        if FUSE_SWIGLU_BWD:
+            dgu = torch.empty_like(gu)
+            # dL/dh = dy @ w_dn, turned into dL/d(gate|up) in the epilogue
+            G.launch([G.GemmSpec(dy, w_dn, dgu, b_mn=True, out2=gu, flags=G.SWIGLU_BWD)])
+        else:
+            dh = torch.empty_like(h)
+            G.launch([G.GemmSpec(dy, w_dn, dh, b_mn=True)])
+            dgu = _C().swiglu_bwd(dh, gu)
         dx = dw_gu = db_gu = dw_dn = db_dn = dres = None
         if ctx.needs_input_grad[3]:
             dw_dn = _wgrad(dy, h, w_dn)
@@ -372,14 +384,24 @@ class _MoeFfnFn(torch.autograd.Function):
         dyp = _C().permute_rows(dout, dest, rows)  # grouped order, zero padding rows
         wmax = gu.shape[1]
         # dL/dh = dy @ w_down per expert, turned into dL/d(gate|up) in the GEMM epilogue (pad rows zeroed)
-        dgu = torch.empty((rows, wmax), device=xp.device, dtype=torch.bfloat16)
         specs = []
-        for e in range(n_exp):
-            w_dn = weights[2 * e + 1]
-            specs.append(G.GemmSpec(dyp, w_dn, dgu, M=rows, dyn=seg[e], b_mn=True, out2=gu,
-                                    flags=G.SWIGLU_BWD | G.ZERO_PAD_ROWS))
-        for i in range(0, n_exp, 2):
-            G.launch(specs[i:i + 2])
+        if FUSE_SWIGLU_BWD:
+            dgu = torch.empty((rows, wmax), device=xp.device, dtype=torch.bfloat16)
+            for e in range(n_exp):
+                w_dn = weights[2 * e + 1]
+                specs.append(G.GemmSpec(dyp, w_dn, dgu, M=rows, dyn=seg[e], b_mn=True, out2=gu,
+                                        flags=G.SWIGLU_BWD | G.ZERO_PAD_ROWS))
+            for i in range(0, n_exp, 2):
+                G.launch(specs[i:i + 2])
+        else:
+            dh = torch.empty((rows, wmax // 2), device=xp.device, dtype=torch.bfloat16)
+            for e in range(n_exp):
+                w_dn = weights[2 * e + 1]
+                specs.append(G.GemmSpec(dyp, w_dn, dh[:, : w_dn.shape[1]], M=rows, dyn=seg[e], b_mn=True,
+                                        flags=G.ZERO_PAD_ROWS))
+            for i in range(0, n_exp, 2):
+                G.launch(specs[i:i + 2])
+            dgu = _C().swiglu_bwd(dh, gu)
         grads = [None] * (2 * n_exp)
         specs = []
         for e in range(n_exp):
