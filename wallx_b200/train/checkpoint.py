@@ -5,7 +5,7 @@
   checkpoints.
 * Training checkpoints are one file per rank (fp32 master shard, Adam moments, step, RNG, sampler
   position, LR-schedule state) plus a manifest that records the world size and flat-parameter
-  layout, so that a run can resume on a different number of GPUs (see ``parallel/fsdp.py``).
+  layout, so that a run can resume on a different number of GPUs (``parallel/reshard.py``).
 """
 from __future__ import annotations
 
