@@ -120,29 +120,30 @@ def _dist_worker(rank, world, port, tmp, mode):
 
 
 @pytest.mark.timeout(300)
-def test_two_rank_gloo_training_equals_single_rank_large_batch(tmp_path):
-    world = 2
+@pytest.mark.parametrize("world", [2, 4])
+def test_gloo_training_equals_single_rank_large_batch(tmp_path, world):
     mp.spawn(_dist_worker, args=(world, _free_port(), str(tmp_path), "ok"), nprocs=world, join=True)
     p0 = torch.load(tmp_path / "params_0.pt")
-    p1 = torch.load(tmp_path / "params_1.pt")
-    for k in p0:
-        assert torch.equal(p0[k], p1[k]), k  # replicas stay identical
-    # single process, both micro-batches per step (== data parallel average)
+    for r in range(1, world):
+        pr = torch.load(tmp_path / f"params_{r}.pt")
+        for k in p0:
+            assert torch.equal(p0[k], pr[k]), k  # replicas stay identical
+    # single process, every rank's micro-batch per step (== data parallel average)
     cfg, proc, m = _model()
-    eng = TrainEngine(m, lr=1e-3, weight_decay=0.1, max_grad_norm=1.0, grad_accum=2)
-    all_b = _batches(cfg, proc, 4, seed=3)
+    eng = TrainEngine(m, lr=1e-3, weight_decay=0.1, max_grad_norm=1.0, grad_accum=world)
+    all_b = _batches(cfg, proc, 2 * world, seed=3)
     for step in range(2):
-        for r in range(2):
-            eng.backward(m(mode="train", **all_b[step * 2 + r]).loss)
+        for r in range(world):
+            eng.backward(m(mode="train", **all_b[step * world + r]).loss)
         eng.optimizer_step(1e-3)
     for n, p in m.named_parameters():
         assert torch.allclose(p, p0[n], atol=3e-5), n  # 3% of one lr-sized Adam step: rounding only
-    # reshard the 2-rank optimizer state onto 1 rank and compare with the single-rank state
+    # reshard the sharded optimizer state onto 1 rank and compare with the single-rank state
     from wallx_b200.parallel.reshard import load_optimizer_shards
 
     cfg, proc, m2 = _model()
     eng2 = TrainEngine(m2, lr=1e-3, grad_accum=1)
-    load_optimizer_shards(eng2, str(tmp_path), 2)
+    load_optimizer_shards(eng2, str(tmp_path), world)
     assert eng2.optimizer.step_count == 2
     for a, b in zip(eng.buffers, eng2.buffers):
         assert torch.allclose(a.exp_avg[: a.numel], b.exp_avg[: b.numel], atol=1e-6)
