@@ -129,8 +129,8 @@ def test_rope_backward_is_rotation_by_minus_angle(T, H, layout, seed):
     dy = torch.randn(T, H, D, dtype=torch.float64, generator=g)
     y = ref.apply_rope(x, cos.double(), sin.double())
     (dx,) = torch.autograd.grad(y, x, dy)
-    # the CUDA kernel's backward is the same kernel with the sine negated (exact for the Hugging Face layout,
-    # where both halves of a pair share the angle)
+    # in the Hugging Face layout both channels of a pair share the angle, so the transposed rotation (what the
+    # kernels apply in backward) is the rotation by the negated angle
     if layout == "hf":
         assert torch.allclose(dx, ref.apply_rope(dy, cos.double(), -sin.double()), rtol=1e-5, atol=1e-5)  # the oracle computes in fp32
         assert torch.allclose(ref.apply_rope(y.detach(), cos.double(), -sin.double()), x.detach(), atol=1e-5)  # cos and sin are fp32 tables

@@ -15,6 +15,7 @@ from typing import Optional, Sequence
 
 import torch
 
+from . import backend as BE
 from . import functional as F_
 from . import gemm as G
 from . import index as IX
@@ -22,7 +23,9 @@ from . import ref
 from .index import get_rope_index  # noqa: F401
 
 
-class _DualGemm(torch.autograd.Function):
+class AsymmetricDualExpertGemm(torch.autograd.Function):
+    """``apply(in0, in1, w0, w1, trans_b)``: forward, dgrad and wgrad are one two-problem launch each (ops.py:6-165)."""
+
     @staticmethod
     def forward(ctx, a0, a1, w0, w1, trans_b):
         ctx.save_for_backward(a0, a1, w0, w1)
@@ -61,45 +64,94 @@ class _DualGemm(torch.autograd.Function):
 def asym_dual_gmm(input_expert0, input_expert1, weight_expert0, weight_expert1, trans_b: bool = False):
     if input_expert0.is_cuda:
         mk = lambda t: F_._aligned2d(t.contiguous())
-        return _DualGemm.apply(mk(input_expert0), mk(input_expert1), mk(weight_expert0), mk(weight_expert1), trans_b)
+        return AsymmetricDualExpertGemm.apply(mk(input_expert0), mk(input_expert1), mk(weight_expert0), mk(weight_expert1), trans_b)
     f = (lambda a, w: a @ w.t()) if trans_b else (lambda a, w: a @ w)
     return f(input_expert0, weight_expert0), f(input_expert1, weight_expert1)
 
 
-def _compact_dest(indices: torch.Tensor) -> torch.Tensor:
-    """Row of every token after a stable sort by expert id (compact: no alignment padding)."""
-    idx = indices.reshape(-1).long()
-    order = torch.sort(idx, stable=True).indices
-    dest = torch.empty_like(order)
-    dest[order] = torch.arange(order.numel(), device=idx.device)
-    return dest
+class PermuteMoE_topK(torch.autograd.Function):
+    """``apply(input_act, indices, num_out_tokens, max_token_num) -> (permuted, row_id_map)``.
 
+    ``indices`` is ``[T]`` (top-1, the token-type routing of this model) or ``[T, K]``; rows are grouped
+    by a stable sort of the flattened expert ids; ``row_id_map[k * T + t]`` (int32) is the row of token
+    t's k-th copy. The backward pass sums the gradients of a token's copies (ops.py:175-274).
+    """
 
-class _Permute(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, dest):
-        ctx.save_for_backward(dest)
-        out = torch.empty_like(x)
-        out.index_copy_(0, dest, x)
-        return out
+    def forward(ctx, input_act, indices, num_out_tokens=0, max_token_num=0):
+        if not input_act.numel():
+            return input_act, None
+        out, row_id_map = BE.permute(input_act, indices, int(num_out_tokens or 0), None, int(max_token_num or 0))
+        ctx.row_id_map = row_id_map
+        ctx.topk = 1 if indices.dim() == 1 else int(indices.shape[1])
+        ctx.mark_non_differentiable(row_id_map)
+        return out, row_id_map
+
+    @staticmethod
+    def backward(ctx, g, _):
+        if not g.numel():
+            return g, None, None, None
+        return BE.unpermute(g.contiguous(), ctx.row_id_map, None, 0, ctx.topk), None, None, None
+
+
+class UnpermuteMoE_topK(torch.autograd.Function):
+    """``apply(input_act, row_id_map, probs=None) -> [T, C]``: the inverse gather, with the K copies of a
+    token weighted by ``probs [T, K]`` and summed; differentiable in the rows and in ``probs`` (ops.py:284-383)."""
+
+    @staticmethod
+    def forward(ctx, input_act, row_id_map, probs=None):
+        if not input_act.numel():
+            ctx.probs = probs
+            return input_act
+        ctx.save_for_backward(input_act, row_id_map)
+        ctx.probs = probs
+        return BE.unpermute(input_act, row_id_map, probs, 0, 1 if probs is None else int(probs.reshape(-1, probs.shape[-1]).shape[1]))
 
     @staticmethod
     def backward(ctx, g):
-        (dest,) = ctx.saved_tensors
-        return g.index_select(0, dest), None
+        if not g.numel():
+            return g, None, None
+        x, row_id_map = ctx.saved_tensors
+        probs = ctx.probs
+        if probs is None and row_id_map.numel() != g.shape[0]:  # top-K copies without weights
+            k = row_id_map.numel() // g.shape[0]
+            probs = torch.ones((g.shape[0], k), device=g.device, dtype=g.dtype)
+            dx, _ = BE.unpermute_bwd(g.contiguous(), x, row_id_map, probs)
+            return dx, None, None
+        dx, dp = BE.unpermute_bwd(g.contiguous(), x, row_id_map, probs)
+        return dx, None, (dp if probs is not None and probs.requires_grad else None)
 
 
 def permute(input_act, indices, num_out_tokens=None, max_token_num=0):
-    """Returns ``(permuted_act, row_id_map)`` with ``row_id_map`` int32 ``[T]``."""
-    dest = _compact_dest(indices)
-    return _Permute.apply(input_act, dest), dest.to(torch.int32)
+    """Returns ``(permuted_act, row_id_map)`` with ``row_id_map`` int32 ``[K * T]``."""
+    return PermuteMoE_topK.apply(input_act, indices, 0 if num_out_tokens is None else num_out_tokens, max_token_num)
 
 
 def unpermute(input_act, row_id_map, probs=None):
-    out = input_act.index_select(0, row_id_map.long())
-    if probs is not None:
-        out = out * probs.reshape(-1, 1).to(out.dtype)
-    return out
+    return UnpermuteMoE_topK.apply(input_act, row_id_map, probs)
+
+
+class MultimodalRoPE(torch.autograd.Function):
+    """``apply(q, k, cos, sin, mrope_section) -> (q_out, k_out)`` in the reference's ``[B, H, S, D]`` layout with
+    its contiguous channel-to-axis rule; fresh outputs, backward = the transposed rotation (ops.py:402-497)."""
+
+    @staticmethod
+    def forward(ctx, q, k, cos, sin, mrope_section):
+        if len(mrope_section) != 3:
+            raise RuntimeError("mrope_section must hold three integers (frequency pairs for t, h, w)")
+        doubled = [2 * int(x) for x in mrope_section]
+        q_out, k_out = torch.empty_like(q), torch.empty_like(k)
+        BE.rope(q, k, cos, sin, q_out, k_out, doubled)
+        ctx.save_for_backward(cos, sin)
+        ctx.doubled = doubled
+        return q_out, k_out
+
+    @staticmethod
+    def backward(ctx, gq, gk):
+        cos, sin = ctx.saved_tensors
+        dq, dk = torch.empty_like(gq), torch.empty_like(gk)
+        BE.rope_bwd(gq, gk, None, None, cos, sin, dq, dk, ctx.doubled)
+        return dq, dk, None, None, None
 
 
 def multimodal_rope(q, k, cos, sin, mrope_section: Sequence[int]):
