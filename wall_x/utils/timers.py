@@ -1,1 +1,1 @@
-from wallx_b200.utils.timers import DummyTimer, Timer, Timers  # noqa: F401
+from wallx_b200.utils.timers import DummyTimer, Timer, TimerBase, Timers  # noqa: F401

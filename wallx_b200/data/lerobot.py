@@ -172,6 +172,16 @@ class PreprocessedDataset:
         return self._loader(False)
 
 
+def get_distributed_dataloader(dataset, config=None, rank: int = 0, world_size: int = 1, seed: int = 42, is_train: bool = True):
+    """``(loader, sampler)`` of a :class:`PreprocessedDataset` for one rank (load_lerobot_dataset.py:517-538).
+    ``config`` is accepted for signature parity; the dataset already holds it."""
+    dataset.rank, dataset.world_size = int(rank), int(world_size)
+    if is_train:
+        dataset.seed = seed
+        return dataset.get_train_dataloader()
+    return dataset.get_val_dataloader()
+
+
 def load_lerobot_data(config: Dict, lerobot_config: Dict, rank: int = 0, world_size: int = 1, seed: int = 42,
                       processor=None, action_tokenizer=None, model_config=None) -> PreprocessedDataset:
     """Open a LeRobot dataset with an action chunk of ``action_horizon - 1`` future steps."""

@@ -12,8 +12,10 @@ from __future__ import annotations
 
 from ..config import Qwen2_5_VLConfig
 from .layers import RMSNorm, SwiGLUFFN
-from .llm import DecoderLayer, Qwen2_5_VLMoEModel
-from .vision import PatchMerger, VisionBlock, VisionPatchEmbed, VisionTransformer
+from .llm import Attention, DecoderLayer, Qwen2_5_VLMoEModel
+from .rotary import (Qwen2_5_VisionRotaryEmbedding, Qwen2_5_VLRotaryEmbedding, apply_multimodal_rotary_pos_emb,  # noqa: F401
+                     apply_rotary_pos_emb_flashatt, apply_rotary_pos_emb_vision, repeat_kv, rotate_half)
+from .vision import PatchMerger, VisionAttention, VisionBlock, VisionPatchEmbed, VisionTransformer
 from .vla import Qwen2_5_VLACausalLMOutputWithPast, Qwen2_5_VLMoEForAction
 
 
@@ -48,3 +50,10 @@ Qwen2RMSNorm = RMSNorm
 Qwen2MLP = SwiGLUFFN
 Qwen2_5_VLMLP = SwiGLUFFN
 Qwen2_5_VLCausalLMOutputWithPast = Qwen2_5_VLACausalLMOutputWithPast
+Qwen2_5_VLPreTrainedModel = Qwen2_5_VLMoEForAction  # from_pretrained / save_pretrained / state-dict hooks live there
+# One attention implementation per tower: the reference's eager / flash-attn 2 / SDPA variants are all
+# served by the same tcgen05 attention kernels, whatever ``attn_implementation`` a config names.
+Qwen2_5_VLAttention = Qwen2_5_VLFlashAttention2 = Qwen2_5_VLSdpaAttention = Attention
+QWEN2_5_VL_ATTENTION_CLASSES = {"eager": Attention, "flash_attention_2": Attention, "sdpa": Attention}
+Qwen2_5_VLVisionAttention = Qwen2_5_VLVisionFlashAttention2 = Qwen2_5_VLVisionSdpaAttention = VisionAttention
+QWEN2_5_VL_VISION_ATTENTION_CLASSES = {"eager": VisionAttention, "flash_attention_2": VisionAttention, "sdpa": VisionAttention}

@@ -15,7 +15,29 @@ from typing import Dict, Iterable, List, Optional
 import torch
 
 
-class DummyTimer:
+class TimerBase:
+    """Interface of a named timer: ``start`` / ``stop`` / ``reset`` / ``elapsed`` (timers.py:42-78 of the reference)."""
+
+    def __init__(self, name: str = ""):
+        self.name = name
+
+    def start(self, barrier: bool = False):
+        raise NotImplementedError
+
+    def stop(self, barrier: bool = False):
+        raise NotImplementedError
+
+    def reset(self):
+        raise NotImplementedError
+
+    def elapsed(self, reset: bool = True, barrier: bool = False) -> float:
+        raise NotImplementedError
+
+
+class DummyTimer(TimerBase):
+    def __init__(self):
+        super().__init__("dummy")
+
     def start(self, barrier: bool = False):
         return None
 
@@ -29,9 +51,9 @@ class DummyTimer:
         raise RuntimeError("dummy timer has no elapsed time")
 
 
-class Timer:
+class Timer(TimerBase):
     def __init__(self, name: str, use_cuda_events: Optional[bool] = None, nvtx: bool = False):
-        self.name = name
+        super().__init__(name)
         self._elapsed = 0.0
         self._started = False
         self._t0 = 0.0
