@@ -25,17 +25,6 @@ from . import ref
 
 
 # ----------------------------------------------------------------------------- grouped GEMM
-def _gemm_into(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, trans_a: bool, trans_b: bool):
-    """``out = op(a) @ op(w)`` as a GemmSpec, or None when the problem is empty."""
-    from . import gemm as G
-
-    if out.numel() == 0:
-        return None
-    # the core computes D[M, N] = A[M, K] * B[N, K]^T; ``a_mn`` / ``b_mn`` describe operands stored
-    # with the contraction dimension outermost, which is exactly trans_a / not trans_b here
-    return G.GemmSpec(a, w, out, a_mn=trans_a, b_mn=not trans_b)
-
-
 def asym_dual_gmm_separated(input_expert0: torch.Tensor, input_expert1: torch.Tensor, weight_expert0: torch.Tensor,
                             weight_expert1: torch.Tensor, output_expert0: Optional[torch.Tensor] = None,
                             output_expert1: Optional[torch.Tensor] = None, trans_a: bool = False,
@@ -57,13 +46,21 @@ def asym_dual_gmm_separated(input_expert0: torch.Tensor, input_expert1: torch.Te
         from . import functional as F_
         from . import gemm as G
 
-        specs = []
+        # the core computes D[M, N] = A[M, K] * B[N, K]^T; ``a_mn`` / ``b_mn`` mark operands stored with the
+        # contraction dimension outermost, which is trans_a / not trans_b here
+        specs, copies = [], []
         for a, w, o in ((input_expert0, weight_expert0, outs[0]), (input_expert1, weight_expert1, outs[1])):
-            s = _gemm_into(F_._aligned2d(a.contiguous()), F_._aligned2d(w.contiguous()), o, trans_a, trans_b)
-            if s is not None:
-                specs.append(s)
+            if o.numel() == 0:
+                continue
+            dst = o if F_._pitch_ok(o) else F_._aligned2d(torch.empty_like(o))
+            if dst is not o:
+                copies.append((o, dst))
+            specs.append(G.GemmSpec(F_._aligned2d(a.contiguous()), F_._aligned2d(w.contiguous()), dst, a_mn=trans_a,
+                                    b_mn=not trans_b))
         if specs:
             G.launch(specs)
+        for o, dst in copies:
+            o.copy_(dst)
     else:
         for a, w, o in ((input_expert0, weight_expert0, outs[0]), (input_expert1, weight_expert1, outs[1])):
             aa = a.t() if trans_a else a
