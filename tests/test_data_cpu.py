@@ -4,7 +4,7 @@ import torch
 
 from wallx_b200.config import tiny_config
 from wallx_b200.data import text as T
-from wallx_b200.data.collator import DataCollator, add_pack_info, minmax_normalize
+from wallx_b200.data.collator import DataCollator, minmax_normalize
 from wallx_b200.data.lerobot import PreprocessedDataset, SyntheticEpisodeDataset, get_data_configs
 from wallx_b200.data.synthetic import images_to_patches, make_processor, smart_resize
 

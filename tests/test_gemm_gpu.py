@@ -290,7 +290,6 @@ def test_gemm_gathered_dual_gate_up():
     """Two experts' interleaved gate/up weights gathered and multiplied in one launch, SwiGLU epilogue."""
     from wallx_b200.ops import _ext
     from wallx_b200.ops import gemm as G
-    from wallx_b200.ops import ref as R
 
     torch.manual_seed(2)
     dev = torch.device("cuda")

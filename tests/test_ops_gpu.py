@@ -1,5 +1,4 @@
 """Each sm_100a kernel against the plain PyTorch fp32 oracle of the same op."""
-import math
 
 import pytest
 import torch

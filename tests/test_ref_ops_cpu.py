@@ -1,5 +1,4 @@
 """CPU oracle properties (no GPU): routing, rope index, window index, mRoPE, flow maths."""
-import math
 
 import pytest
 import torch

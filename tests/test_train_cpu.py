@@ -3,7 +3,6 @@ import copy
 import json
 import os
 import socket
-import sys
 
 import pytest
 import torch

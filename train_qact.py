@@ -42,7 +42,7 @@ def main(argv=None):
     args = ap.parse_args(argv)
     config = load_config(args.config)
     setup_distributed()
-    from wallx_b200.train.trainer import QwenVlAct_Trainer, print_rank_last
+    from wallx_b200.train.trainer import QwenVlAct_Trainer
 
     if int(os.environ.get("RANK", "0")) == 0:
         if config.get("save_path"):

@@ -9,7 +9,6 @@ before the reference is imported.
 """
 from __future__ import annotations
 
-import os
 import sys
 import types
 

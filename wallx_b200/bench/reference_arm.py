@@ -19,7 +19,6 @@ from __future__ import annotations
 import json
 import os
 import sys
-import time
 
 
 def unavailable(reason: str) -> None:

@@ -10,7 +10,7 @@ from __future__ import annotations
 import copy
 import json
 import os
-from typing import Any, Dict, List, Optional
+from typing import Any, Dict, List
 
 
 class _Base:

@@ -8,7 +8,7 @@ attached to the batch here and travel with it. The model falls back to computing
 """
 from __future__ import annotations
 
-from typing import Dict, Optional
+from typing import Dict
 
 import torch
 

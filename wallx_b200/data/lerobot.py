@@ -11,8 +11,7 @@ dataset object that offers ``__getitem__``, ``__len__`` and a ``meta`` with ``re
 """
 from __future__ import annotations
 
-import math
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, Optional
 
 import torch
 from torch.utils.data import DataLoader, DistributedSampler, random_split

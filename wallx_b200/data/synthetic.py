@@ -19,7 +19,6 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 
 from ..config import Qwen2_5_VLConfig
-from ..ops import ref
 
 CLIP_MEAN = (0.48145466, 0.4578275, 0.40821073)
 CLIP_STD = (0.26862954, 0.26130258, 0.27577711)

@@ -15,7 +15,6 @@ from typing import Dict, List, Optional, Sequence
 import torch
 import torch.nn as nn
 
-from ..ops import functional as F_
 from ..utils.constant import action_statistic_dof
 from .layers import Linear
 

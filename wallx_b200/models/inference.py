@@ -15,7 +15,7 @@ evaluations. The Euler loop can be captured in a CUDA graph (``use_cuda_graph=Tr
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List, Optional
 
 import torch
 

@@ -8,7 +8,7 @@ modeling_qwen2_5_vl_act.py:67-82) through state-dict hooks.
 """
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import Optional
 
 import torch
 import torch.nn as nn

@@ -10,12 +10,11 @@ added to the matching output columns. Base weights are frozen, as peft does.
 from __future__ import annotations
 
 import math
-from typing import Dict, List, Optional, Tuple
+from typing import List, Tuple
 
 import torch
 import torch.nn as nn
 
-from ..ops import functional as F_
 from .layers import FusedQKV, Linear
 
 

@@ -14,11 +14,10 @@ What is different by design:
 """
 from __future__ import annotations
 
-import glob
 import json
 import os
 from dataclasses import dataclass, fields
-from typing import Any, Dict, List, Optional, Sequence, Tuple
+from typing import Any, List, Optional
 
 import torch
 import torch.nn as nn
@@ -26,10 +25,9 @@ import torch.nn as nn
 from ..config import Qwen2_5_VLConfig
 from ..ops import functional as F_
 from ..ops import index as IX
-from ..ops import ref
 from .action_head import ActionProcessor
 from .layers import Linear
-from .llm import KVCache, Qwen2_5_VLMoEModel, StepContext
+from .llm import Qwen2_5_VLMoEModel, StepContext
 from .vision import VisionTransformer
 
 ACTION_DATASET_NAMES: List[str] = []

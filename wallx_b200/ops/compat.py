@@ -11,7 +11,7 @@ tensors and the PyTorch oracle on CPU tensors, and is differentiable.
 """
 from __future__ import annotations
 
-from typing import Optional, Sequence
+from typing import Sequence
 
 import torch
 

@@ -6,7 +6,7 @@ CUDA inputs run the single-launch kernels of the extension.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence, Tuple
+from typing import List, Sequence, Tuple
 
 import torch
 

@@ -16,9 +16,7 @@ over NVLink, :mod:`wallx_b200.parallel.symm`).
 """
 from __future__ import annotations
 
-import math
-import os
-from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, List, Optional, Tuple
 
 import torch
 import torch.nn as nn

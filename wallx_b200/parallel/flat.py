@@ -13,7 +13,7 @@ qwen_vl_act_trainer.py:527,577-581,609-611) this keeps fp32 master weights and m
 """
 from __future__ import annotations
 
-from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 import torch.nn as nn

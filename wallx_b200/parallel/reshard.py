@@ -9,7 +9,6 @@ qwen_vl_act_trainer.py:797-837; optimizer, scheduler and step are not restored t
 from __future__ import annotations
 
 import os
-from typing import Dict, List
 
 import torch
 

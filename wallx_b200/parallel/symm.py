@@ -15,12 +15,11 @@ one rendezvous covers the whole model.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence
+from typing import List
 
 import torch
 
 from ..ops import _ext
-from ..ops import gemm as G
 
 MAX_VEC = 4096  # floats per rank in the small all-reduce scratch
 FLAG_WORDS = 8 * 128  # int32 flag slots: 8 for the global barrier, then 8 per unit (up to 127 units)

@@ -12,7 +12,7 @@ from __future__ import annotations
 import glob
 import json
 import os
-from typing import Dict, Iterable, List, Optional
+from typing import Dict, Iterable, List
 
 import torch
 

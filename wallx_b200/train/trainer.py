@@ -20,16 +20,15 @@ from __future__ import annotations
 
 import gc
 import json
-import math
 import os
 import random
 import time
-from typing import Dict, List, Optional
+from typing import Dict, Optional
 
 import numpy as np
 import torch
 
-from ..config import Qwen2_5_VLConfig, tiny_config, wall_oss_config
+from ..config import tiny_config, wall_oss_config
 from ..data.collator import to_device
 from ..models import Qwen2_5_VLMoEForAction
 from ..parallel.engine import TrainEngine
