@@ -107,3 +107,25 @@ def test_topk_permute_unpermute_on_gpu_matches_cpu(K):
         outs.append((y.detach().cpu(), m.cpu(), o.detach().cpu(), xd.grad.cpu(), pd.grad.cpu()))
     for a, b in zip(*outs):
         assert torch.allclose(a.float(), b.float(), atol=1e-5)
+
+
+def test_top1_permute_of_bf16_rows_uses_the_row_kernels_and_matches_indexing():
+    from wall_x.fusions.ops import permute, unpermute
+    from wallx_b200.ops import backend as BE
+
+    torch.manual_seed(0)
+    T, C = 1000, 2048
+    x = _mk((T, C), 1)
+    idx = (torch.rand(T) < 0.2).long().cuda()
+    assert BE._row_kernels_apply(x)
+    xg = x.clone().requires_grad_()
+    y, m = permute(xg, idx)
+    want_pos = BE.sorted_rows(idx).reshape(-1)
+    want = torch.empty_like(x)
+    want[want_pos] = x
+    assert m.dtype == torch.int32 and torch.equal(m.long(), want_pos) and torch.equal(y.detach(), want)
+    back = unpermute(y, m)
+    assert torch.equal(back.detach(), x)
+    g = _mk((T, C), 2)
+    back.backward(g)
+    assert torch.equal(xg.grad, g)  # permutation followed by its inverse

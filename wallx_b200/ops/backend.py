@@ -11,8 +11,9 @@ that layer (``from wall_x.fusions import backend``) finds the same names here:
 
 None of these is differentiable (the autograd layer is ``wallx_b200.ops.compat``). CUDA tensors
 run this framework's kernels where one exists for the layout (GEMMs, rotary, index generation);
-the top-K grouping uses index operations, because the model itself never materialises a
-permutation: it fuses the routing into the RMSNorm store and the down-projection epilogue.
+top-1 grouping of bf16 rows uses the row-copy kernels (``permute_rows`` / ``gather_rows``), top-K with
+probabilities uses index operations: the model itself never materialises a permutation, it fuses the
+routing into the RMSNorm store and the down-projection epilogue.
 """
 from __future__ import annotations
 
@@ -70,6 +71,11 @@ def asym_dual_gmm_separated(input_expert0: torch.Tensor, input_expert1: torch.Te
 
 
 # ----------------------------------------------------------------------------- top-K grouping
+def _row_kernels_apply(x: torch.Tensor) -> bool:
+    """The row-copy kernels move bf16 rows in 16-byte pieces."""
+    return x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[1] % 8 == 0 and x.shape[0] > 0
+
+
 def sorted_rows(indices: torch.Tensor) -> torch.Tensor:
     """Row of every (token, k) pair after a stable sort of the flattened expert ids: ``[T, K]`` long."""
     idx = indices.reshape(indices.shape[0], -1)
@@ -92,6 +98,11 @@ def permute(input: torch.Tensor, indices: torch.Tensor, num_out_tokens: int = 0,
     pos = sorted_rows(indices)  # [T, K]
     T, K = pos.shape
     rows = int(num_out_tokens) if num_out_tokens and num_out_tokens > 0 else T * K
+    if _row_kernels_apply(input) and K == 1 and rows == T:  # the top-1 routing of this model: one row-copy kernel
+        from . import _ext
+
+        dest = pos.reshape(-1).to(torch.int32)
+        return _ext.get().permute_rows(input.contiguous(), dest, rows), dest
     out = input.new_zeros((rows, input.shape[1]))
     src = torch.arange(T, device=input.device).view(T, 1).expand(T, K).reshape(-1)
     flat = pos.reshape(-1)
@@ -109,6 +120,10 @@ def unpermute(input: torch.Tensor, row_id_map: torch.Tensor, prob: Optional[torc
     """``out[t] = sum_k prob[t, k] * input[row_id_map[k * T + t]]`` (rows beyond ``input`` count as dropped)."""
     K = int(prob.shape[1]) if prob is not None and prob.dim() == 2 else max(int(num_topK), 1)
     T = row_id_map.numel() // K
+    if prob is None and K == 1 and input.shape[0] == T and _row_kernels_apply(input) and row_id_map.dtype == torch.int32:
+        from . import _ext
+
+        return _ext.get().gather_rows(input.contiguous(), row_id_map.contiguous())  # nothing was dropped: a plain gather
     acc = _acc_dtype(input)
     rows = row_id_map.view(K, T).long()
     valid = rows < input.shape[0]
