@@ -273,3 +273,72 @@ def test_flow_engine_matches_predict_on_cpu():
     bad["input_ids"] = ids
     with pytest.raises(ValueError):
         eng(bad)
+
+
+def test_dense_mask_rule_equals_the_interval_rule_of_the_kernels(setup):
+    """The reference-named dense mask builder and the varlen rule the attention kernels implement agree."""
+    from wallx_b200.ops import ref
+
+    cfg, proc, model = setup
+    B, S, C = 2, 9, 4
+    x = torch.zeros(B, S, C)
+    types = torch.zeros(B, S, dtype=torch.long)
+    types[0, 5:8] = 1
+    types[1, 6:9] = 1
+    am = torch.ones(B, S, dtype=torch.long)
+    am[1, :2] = 0  # left padding
+    mask = model.model._update_causal_mask(am, x, torch.arange(S), None, False, moe_token_types=types)
+    assert mask.shape == (B, 1, S, S)
+    for b in range(B):
+        keep = am[b] == 1
+        n = int(keep.sum())
+        want = ref.attention_mask_varlen([0, n], True, (types[b][keep] == 1), "cpu")
+        got = (mask[b, 0] == 0)[keep][:, keep]
+        assert torch.equal(got, want)
+        assert not (mask[b, 0] == 0)[:, ~keep].any()  # nothing attends to padding
+    # decoding step: one query at position 9 sees everything before it
+    step = model.model._prepare_4d_causal_attention_mask_with_cache_position(None, 1, 10, torch.float32, "cpu", torch.tensor([9]), B)
+    assert step.shape == (B, 1, 1, 10) and (step == 0).all()
+
+
+def test_generation_hooks(setup):
+    cfg, proc, model = setup
+
+    class Past:
+        def __init__(self, n):
+            self.n = n
+
+        def get_seq_length(self):
+            return self.n
+
+    ids = torch.tensor([[5, cfg.vision_start_token_id, cfg.image_token_id, cfg.image_token_id, 7, 8],
+                        [cfg.vision_start_token_id, cfg.image_token_id, cfg.vision_start_token_id, cfg.image_token_id, 9, 9]])
+    pix = torch.randn(12, 6)
+    first = model.prepare_inputs_for_generation(ids, past_key_values=Past(0), pixel_values=pix, cache_position=torch.arange(6))
+    assert first["pixel_values"] is pix and torch.equal(first["input_ids"], ids)
+    assert first["moe_token_types"].shape == ids.shape and not first["moe_token_types"].any()
+    grown = torch.cat([ids, torch.tensor([[3], [4]])], dim=1)
+    later = model.prepare_inputs_for_generation(grown, past_key_values=Past(6), pixel_values=pix, cache_position=torch.tensor([6]),
+                                                moe_token_types=torch.zeros_like(ids))
+    assert later["pixel_values"] is None and later["input_ids"].tolist() == [[3], [4]]
+    assert later["moe_token_types"].shape == (2, 1)
+    img_n, vid_n = model._get_image_nums_and_video_nums(ids)
+    assert img_n.tolist() == [1, 2] and vid_n.tolist() == [0, 0]
+    grid = torch.tensor([[1, 2, 2], [1, 2, 2], [1, 2, 2]])  # 4 patches each: sample 0 owns 4 rows, sample 1 owns 8
+    ids2, kw = model._expand_inputs_for_generation(2, input_ids=ids, pixel_values=pix, image_grid_thw=grid,
+                                                   attention_mask=torch.ones_like(ids), dataset_names=["a", "b"])
+    assert ids2.shape == (4, 6) and torch.equal(ids2[0], ids2[1]) and torch.equal(ids2[2], ids[1])
+    assert kw["pixel_values"].shape == (24, 6) and torch.equal(kw["pixel_values"][:4], kw["pixel_values"][4:8])
+    assert torch.equal(kw["pixel_values"][8:16], pix[4:12]) and kw["image_grid_thw"].shape == (6, 3)
+    assert kw["attention_mask"].shape == (4, 6) and kw["dataset_names"] == ["a", "a", "b", "b"]
+
+
+def test_decoder_stack_from_pretrained(setup, tmp_path):
+    from wallx_b200.models.llm import Qwen2_5_VLMoEModel
+
+    cfg, proc, model = setup
+    model.save_pretrained(str(tmp_path))
+    stack = Qwen2_5_VLMoEModel.from_pretrained(str(tmp_path))
+    assert not stack._load_report["missing"]
+    for (n1, p1), (n2, p2) in zip(model.model.state_dict().items(), stack.state_dict().items()):
+        assert n1 == n2 and torch.equal(p1, p2), n1

@@ -232,3 +232,25 @@ def test_example_yaml_has_every_trainer_key():
     from wallx_b200.data.lerobot import get_data_configs
 
     assert get_data_configs(d)["action_horizon"] == 33
+
+
+def test_timer_active_time_survives_reset_and_collator_normalize():
+    import time
+
+    from wallx_b200.data.collator import DataCollator, minmax_normalize
+    from wallx_b200.utils.timers import DummyTimer, Timer
+
+    t = Timer("t", use_cuda_events=False)
+    for _ in range(2):
+        t.start()
+        time.sleep(0.01)
+        t.stop()
+        assert t.elapsed(reset=True) >= 0.009
+    assert t.active_time() >= 0.018 and t.elapsed(reset=False) == 0.0
+    with pytest.raises(RuntimeError):
+        DummyTimer().active_time()
+    x = torch.tensor([[0.0, 5.0, 10.0], [2.0, 5.0, 20.0]])
+    mn, mx = [0.0, 5.0, 0.0], [4.0, 5.0, 10.0]
+    a = DataCollator._normalize(x, mn, [4.0, 0.0, 10.0])
+    assert torch.equal(a, minmax_normalize(x, mn, mx))
+    assert a.tolist() == [[-1.0, -1.0, 1.0], [0.0, -1.0, 1.0]]  # zero range counts as 1; values are clamped

@@ -103,28 +103,11 @@ class DataCollator:
         self.min_stat = stats["action"]["min"]
         self.max_stat = stats["action"]["max"]
         self.use_fast_tokenizer = bool(config.get("use_fast_tokenizer", False))
-        if processor is None:
-            from transformers import AutoProcessor
-
-            processor = AutoProcessor.from_pretrained(config["pretrained_wallx_path"], use_fast=True)
-        if config.get("padding_side", "left") == "left":
-            processor.tokenizer.padding_side = "left"
-        self.processor = processor
-        if self.use_fast_tokenizer and action_tokenizer is None:
-            action_tokenizer = getattr(processor, "action_processor", None)
-        if self.use_fast_tokenizer and action_tokenizer is None:
-            if config.get("action_tokenizer_path"):
-                from transformers import AutoProcessor
-
-                action_tokenizer = AutoProcessor.from_pretrained(config["action_tokenizer_path"], trust_remote_code=True)
-            else:  # no pretrained FAST tokenizer given: the built-in DCT tokenizer over the same id range
-                from .fast_tokenizer import DctActionTokenizer
-
-                action_tokenizer = DctActionTokenizer(int(processor.tokenizer.init_kwargs["action_token_vocab_size"]))
+        self.processor, action_tokenizer = self.load_processor(processor, action_tokenizer)
         self.train_action_tokenizer = action_tokenizer if self.use_fast_tokenizer else None
         self.action_mapper = None
         if self.train_action_tokenizer is not None:
-            tok = processor.tokenizer
+            tok = self.processor.tokenizer
             self.action_mapper = {tok.convert_tokens_to_ids(f"<|action_token_{i}|>"): i
                                   for i in range(self.train_action_tokenizer.vocab_size)}
         self.model_config = model_config
@@ -137,6 +120,44 @@ class DataCollator:
         mask = (~torch.isnan(x)).float()
         x = minmax_normalize(torch.nan_to_num(x, nan=0.0), self.min_stat, self.max_stat)
         return _pad_last(x, ACTION_PAD_DIM), _pad_last(mask, ACTION_PAD_DIM)
+
+    _processor_cache: Dict[str, object] = {}  # one processor per path and process (DataLoader workers re-create collators)
+
+    def load_processor(self, processor=None, action_tokenizer=None):
+        """``(processor, action_tokenizer)``: the given objects, else loaded from ``pretrained_wallx_path`` /
+        ``action_tokenizer_path`` (cached per path), else -- FAST branch without a tokenizer path -- the built-in DCT
+        tokenizer over the checkpoint's action id range (reference: load_lerobot_dataset.py:254-285)."""
+        config = self.config
+        if processor is None:
+            path = config["pretrained_wallx_path"]
+            if path not in DataCollator._processor_cache:
+                from transformers import AutoProcessor
+
+                DataCollator._processor_cache[path] = AutoProcessor.from_pretrained(path, use_fast=True)
+            processor = DataCollator._processor_cache[path]
+        if config.get("padding_side", "left") == "left":
+            processor.tokenizer.padding_side = "left"
+        if self.use_fast_tokenizer and action_tokenizer is None:
+            action_tokenizer = getattr(processor, "action_processor", None)
+        if self.use_fast_tokenizer and action_tokenizer is None:
+            path = config.get("action_tokenizer_path")
+            if path:
+                if path not in DataCollator._processor_cache:
+                    from transformers import AutoProcessor
+
+                    DataCollator._processor_cache[path] = AutoProcessor.from_pretrained(path, trust_remote_code=True)
+                action_tokenizer = DataCollator._processor_cache[path]
+            else:
+                from .fast_tokenizer import DctActionTokenizer
+
+                action_tokenizer = DctActionTokenizer(int(processor.tokenizer.init_kwargs["action_token_vocab_size"]))
+        return processor, action_tokenizer
+
+    @classmethod
+    def _normalize(cls, action: torch.Tensor, min_stat, delta) -> torch.Tensor:
+        """Min-max normalisation from ``min`` and ``delta = max - min`` (reference: load_lerobot_dataset.py:294-304)."""
+        mn = torch.as_tensor(min_stat, dtype=action.dtype)
+        return minmax_normalize(action, mn, mn + torch.as_tensor(delta, dtype=action.dtype))
 
     def __call__(self, items):
         known = {"agent_pos", "action", "image_inputs", "text", "frame_index"}

@@ -20,6 +20,7 @@ import torch.nn as nn
 from ..config import Qwen2_5_VLConfig
 from ..ops import functional as F_
 from ..ops import ref
+from .generation import MoEModelMaskMixin
 from .layers import FusedQKV, Linear, RMSNorm, SwiGLUFFN
 
 
@@ -126,8 +127,31 @@ class DecoderLayer(nn.Module):
         return self.mlp(self.post_attention_layernorm(x), residual=x)
 
 
-class Qwen2_5_VLMoEModel(nn.Module):
+class Qwen2_5_VLMoEModel(MoEModelMaskMixin, nn.Module):
     """Embedding, N decoder layers, final norm. ``forward`` works on packed embeddings."""
+
+    @classmethod
+    def from_pretrained(cls, pretrained_model_name_or_path: str, num_experts: Optional[int] = None, *args, **kwargs):
+        """Decoder stack from a checkpoint directory: ``config.json`` (or ``config=``), optionally with another
+        number of experts, and the ``model.*`` tensors of its safetensors files; stock Qwen2.5-VL FFN keys are mapped
+        onto expert 0 (reference: modeling_qwen2_5_vl_act.py:283-311)."""
+        import os
+
+        from ..train.checkpoint import load_safetensors_dir, rename_qwen_to_moe
+
+        config = kwargs.get("config")
+        if config is None:
+            config = Qwen2_5_VLConfig.from_pretrained(os.path.join(pretrained_model_name_or_path, "config.json"))
+        if num_experts is not None:
+            config.num_experts = int(num_experts)
+        model = cls(config)
+        state = load_safetensors_dir(pretrained_model_name_or_path)
+        if config.mlp_moe:
+            state = rename_qwen_to_moe(state)
+        own = {k[len("model."):]: v for k, v in state.items() if k.startswith("model.")}
+        missing, unexpected = model.load_state_dict(own, strict=False)
+        model._load_report = {"missing": list(missing), "unexpected": list(unexpected)}
+        return model
 
     def __init__(self, config: Qwen2_5_VLConfig):
         super().__init__()

@@ -27,6 +27,7 @@ from ..ops import functional as F_
 from ..ops import index as IX
 from .action_head import ActionProcessor
 from .layers import Linear
+from .generation import GenerationHooksMixin
 from .llm import Qwen2_5_VLMoEModel, StepContext
 from .vision import VisionTransformer
 
@@ -106,7 +107,7 @@ class PackInfo:
         return PackInfo(B, S, [int(l) for l in lens], idx)
 
 
-class Qwen2_5_VLMoEForAction(nn.Module):
+class Qwen2_5_VLMoEForAction(GenerationHooksMixin, nn.Module):
     _tied_weights_keys = ["lm_head.weight"]
     config_class = Qwen2_5_VLConfig
     _no_split_modules = ["DecoderLayer", "VisionBlock"]

@@ -374,6 +374,21 @@ class QwenVlAct_Trainer:
         model.train()
         return val
 
+    def print_rank0(self, msg, flush: bool = True) -> None:
+        """Print on the main rank only."""
+        if self.is_main:
+            print(msg, flush=flush)
+
+    def _load_fsdp_state_dict_with_distribute_tensor(self, ckpt_path: str) -> None:
+        """Reference name of the sharded resume path (qwen_vl_act_trainer.py:797-837: full safetensors file ->
+        ``distribute_tensor`` per parameter). Here parameters are resident on every rank, so the file is loaded
+        as is and each rank refreshes its fp32 master shard from it."""
+        state = CK.strip_prefixes(CK.load_safetensors_dir(ckpt_path))
+        self.model.load_state_dict(state, strict=False)
+        for b in self.engine.buffers:
+            s0, s1 = b.shard_range
+            b.master.copy_(b.param[s0:s1].to(b.master.dtype))
+
     def training_log(self, epoch, iteration, logd, seconds):
         msg = (f"epoch {epoch} iter {iteration} step {self.global_step} loss {logd.get('train_loss', float('nan')):.5f} "
                f"lr {logd['lr']:.3e} grad_norm {logd.get('total_norm', float('nan')):.3f} time {seconds:.3f}s")

@@ -50,11 +50,15 @@ class DummyTimer(TimerBase):
     def elapsed(self, reset: bool = True, barrier: bool = False) -> float:
         raise RuntimeError("dummy timer has no elapsed time")
 
+    def active_time(self) -> float:
+        raise RuntimeError("dummy timer has no active time: the timer's log level is above the registry's")
+
 
 class Timer(TimerBase):
     def __init__(self, name: str, use_cuda_events: Optional[bool] = None, nvtx: bool = False):
         super().__init__(name)
         self._elapsed = 0.0
+        self._active = 0.0  # total over the timer's life; `reset` does not clear it
         self._started = False
         self._t0 = 0.0
         self._use_events = torch.cuda.is_available() if use_cuda_events is None else use_cuda_events
@@ -88,7 +92,9 @@ class Timer(TimerBase):
             ev1.record()
             self._pending.append((self._ev0, ev1))
         else:
-            self._elapsed += time.time() - self._t0
+            dt = time.time() - self._t0
+            self._elapsed += dt
+            self._active += dt
         if self._nvtx and torch.cuda.is_available():
             torch.cuda.nvtx.range_pop()
         self._started = False
@@ -96,13 +102,20 @@ class Timer(TimerBase):
     def _resolve(self):
         for e0, e1 in self._pending:
             e1.synchronize()
-            self._elapsed += e0.elapsed_time(e1) / 1e3
+            dt = e0.elapsed_time(e1) / 1e3
+            self._elapsed += dt
+            self._active += dt
         self._pending = []
 
     def reset(self):
-        self._pending = []
+        self._resolve()  # keep the life-time total exact
         self._elapsed = 0.0
         self._started = False
+
+    def active_time(self) -> float:
+        """Seconds this timer has been running since it was created, resets included."""
+        self._resolve()
+        return self._active
 
     def elapsed(self, reset: bool = True, barrier: bool = False) -> float:
         """Seconds accumulated so far (resolves outstanding CUDA events)."""
