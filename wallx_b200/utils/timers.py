@@ -167,6 +167,38 @@ class Timers:
             return buf.cpu()
         return local.unsqueeze(0)
 
+    # the reference's helper names (timers.py:302-436), for code that calls them directly
+    def _get_elapsed_time_all_ranks(self, names, reset: bool = True, barrier: bool = False) -> torch.Tensor:
+        """Seconds per rank and timer, ``[world, len(names)]`` (zero where a rank has no such timer)."""
+        return self._gather(list(names), reset, barrier)
+
+    def _get_global_min_max_time(self, names, reset: bool = True, barrier: bool = False, normalizer: float = 1.0):
+        """``{name: (min, max)}`` over ranks, divided by ``normalizer``; timers that never ran are left out."""
+        names = list(names)
+        table = self._gather(names, reset, barrier) / normalizer
+        return {n: (float(table[:, i].min()), float(table[:, i].max())) for i, n in enumerate(names) if float(table[:, i].max()) > 0.0}
+
+    def _get_global_min_max_time_string(self, names, reset: bool = True, barrier: bool = False, normalizer: float = 1.0,
+                                        max_only: bool = False) -> Optional[str]:
+        mm = self._get_global_min_max_time(names, reset, barrier, normalizer)
+        if not mm:
+            return None
+        lines = ["max time across ranks (ms):" if max_only else "(min, max) time across ranks (ms):"]
+        for n, (lo, hi) in mm.items():
+            lines.append(f"    {n:.<48s}: {hi * 1e3:.2f}" if max_only else f"    {n:.<48s}: ({lo * 1e3:.2f}, {hi * 1e3:.2f})")
+        return "\n".join(lines)
+
+    def _get_all_ranks_time_string(self, names, reset: bool = True, barrier: bool = False, normalizer: float = 1.0) -> Optional[str]:
+        names = list(names)
+        table = self._gather(names, reset, barrier) * 1e3 / normalizer
+        lines = ["times across ranks (ms):"]
+        for i, n in enumerate(names):
+            if float(table[:, i].max()) == 0.0:
+                continue
+            lines.append(f"  {n}:")
+            lines += [f"     rank {r:2d}: {float(table[r, i]):.2f}" for r in range(table.shape[0])]
+        return "\n".join(lines) if len(lines) > 1 else None
+
     def get_all_timers_string(self, names: Optional[Iterable[str]] = None, normalizer: float = 1.0, reset: bool = True,
                               barrier: bool = False) -> Optional[str]:
         names = list(names) if names is not None else list(self._timers.keys())
