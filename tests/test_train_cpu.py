@@ -254,3 +254,43 @@ def test_timer_active_time_survives_reset_and_collator_normalize():
     a = DataCollator._normalize(x, mn, [4.0, 0.0, 10.0])
     assert torch.equal(a, minmax_normalize(x, mn, mx))
     assert a.tolist() == [[-1.0, -1.0, 1.0], [0.0, -1.0, 1.0]]  # zero range counts as 1; values are clamped
+
+
+def test_nvtx_annotation_is_off_by_default_and_wraps_on_request(monkeypatch):
+    import types
+
+    from wallx_b200.ops import functional as F_
+    from wallx_b200.utils import nvtx
+
+    assert not nvtx.enabled() and not getattr(F_.linear, "__wrapped_by_nvtx__", False)  # default: untouched call path
+    mod = types.SimpleNamespace(f=lambda x: x + 1, g=3)
+    assert nvtx.annotate_module(mod, ["f", "g"]) == 0
+    monkeypatch.setenv("WALLX_NVTX", "1")
+    assert nvtx.annotate_module(mod, ["f", "g", "missing"]) == 1
+    assert mod.f(1) == 2 and mod.f.__wrapped_by_nvtx__  # on a CPU box the range calls are skipped
+    assert nvtx.annotate_module(mod, ["f"]) == 0  # idempotent
+    for name in F_.NVTX_OPS:
+        assert callable(getattr(F_, name)), name
+
+
+def test_corrupt_or_missing_checkpoint_files_raise_cleanly(tmp_path):
+    """Host-side fault injection on checkpoint files: a truncated optimizer shard and an empty weights directory."""
+    from wallx_b200.parallel.reshard import load_optimizer_shards
+    from wallx_b200.train import checkpoint as CK
+
+    m = torch.nn.Sequential(torch.nn.Linear(8, 8))
+    eng = TrainEngine(m, lr=1e-3)
+    f = tmp_path / "optim_rank00000_of_00001.pt"
+    torch.save(eng.optimizer_state(), f)
+    load_optimizer_shards(eng, str(tmp_path), 1)  # intact: loads
+    data = f.read_bytes()
+    f.write_bytes(data[: len(data) // 2])
+    with pytest.raises(Exception):
+        load_optimizer_shards(eng, str(tmp_path), 1)
+    with pytest.raises(FileNotFoundError):
+        CK.load_safetensors_dir(str(tmp_path / "nothing_here"))
+    # a checkpoint of another model is refused instead of being half-loaded
+    m2 = torch.nn.Sequential(torch.nn.Linear(8, 9))
+    torch.save(TrainEngine(m2, lr=1e-3).optimizer_state(), f)
+    with pytest.raises(ValueError):
+        load_optimizer_shards(eng, str(tmp_path), 1)

@@ -792,3 +792,19 @@ class _GatherRowsFn(torch.autograd.Function):
 
 def gather_rows(x: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
     return x.index_select(0, idx)
+
+
+# ----------------------------------------------------------------------------- optional NVTX ranges
+NVTX_OPS = ("linear", "linear_gelu", "rms_norm", "swiglu_ffn", "gate_up_swiglu", "moe_ffn", "rope_qk", "attention",
+            "attention_packed", "lm_head_ce", "column_sum", "make_route_plan")
+
+
+def _annotate():
+    import sys
+
+    from ..utils import nvtx
+
+    return nvtx.annotate_module(sys.modules[__name__], NVTX_OPS)
+
+
+_annotate()
