@@ -129,3 +129,17 @@ def test_top1_permute_of_bf16_rows_uses_the_row_kernels_and_matches_indexing():
     g = _mk((T, C), 2)
     back.backward(g)
     assert torch.equal(xg.grad, g)  # permutation followed by its inverse
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+def test_gemm_bits_do_not_depend_on_the_tile_schedule(a_mn, b_mn):
+    """Race check by replay: every output element accumulates its k blocks in the same order whatever the tile
+    width, the CTA pairing or the raster, so all schedules must agree bit for bit (and with themselves)."""
+    from wallx_b200.ops import gemm as G
+
+    M, N, K = 1000, 1280, 1176
+    a = _mk((K, M) if a_mn else (M, K), 11)
+    b = _mk((K, N) if b_mn else (N, K), 12, 0.1)
+    outs = [G.gemm(a, b, a_mn=a_mn, b_mn=b_mn, force_bn=bn) for bn in (64, 128, 256, 512, 0, 256)]
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])
