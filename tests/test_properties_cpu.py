@@ -246,3 +246,61 @@ def test_missing_shard_is_reported(tmp_path):
     eng = _tiny_engine(1, 0)
     with pytest.raises(FileNotFoundError):
         load_optimizer_shards(eng, str(tmp_path), 2)
+
+
+# ----------------------------------------------------------------------------- data path
+@_FAST
+@given(st.integers(20, 2000), st.integers(20, 2000))
+def test_smart_resize_bounds_and_alignment(h, w):
+    from wallx_b200.data.synthetic import smart_resize
+
+    if max(h, w) / min(h, w) > 200:
+        return
+    lo, hi = 4 * 28 * 28, 1280 * 28 * 28
+    rh, rw = smart_resize(h, w, factor=28, min_pixels=lo, max_pixels=hi)
+    assert rh % 28 == 0 and rw % 28 == 0 and rh >= 28 and rw >= 28
+    assert lo <= rh * rw <= hi
+    if lo <= round(h / 28) * 28 * round(w / 28) * 28 <= hi:  # in range: plain rounding, at most half a factor per side
+        assert abs(rh - h) <= 14 and abs(rw - w) <= 14
+
+
+@_FAST
+@given(st.integers(1, 32), st.integers(1, 14), st.integers(0, 2 ** 31 - 1))
+def test_dct_action_tokenizer_roundtrip_error_is_bounded(T, D, seed):
+    import numpy as np
+
+    from wallx_b200.data.fast_tokenizer import DctActionTokenizer
+
+    rng = np.random.default_rng(seed)
+    tok = DctActionTokenizer(2048, scale=10.0)
+    a = rng.uniform(-1, 1, size=(2, T, D))
+    ids = tok(a)
+    assert len(ids) == 2 and all(0 < len(x) <= T * D and all(0 <= i < 2048 for i in x) for x in ids)
+    back = tok.decode(ids, T, D)
+    # an orthonormal transform with coefficients rounded to 1 / scale: per-element error <= sqrt(T) * 0.5 / scale
+    assert np.abs(back - a).max() <= 0.5 / 10.0 * np.sqrt(T) + 1e-6
+    assert np.sqrt(((back - a) ** 2).mean()) <= 0.5 / 10.0 + 1e-6  # Parseval: the RMS error is that of the rounding
+    assert tok.decode([[5000]], T, D).any() == False  # noqa: E712  invalid ids decode to zeros
+
+
+@_FAST
+@given(st.lists(st.floats(-5, 5, allow_nan=False), min_size=3, max_size=3), st.lists(st.floats(0.125, 4), min_size=3, max_size=3),
+       st.integers(0, 2 ** 31 - 1))
+def test_normalizer_roundtrip_inside_the_range_and_clamp_outside(mins, deltas, seed):
+    from wallx_b200.models.action_head import Normalizer
+
+    stats = {"robot": {"arm": {"min": mins, "delta": deltas}}}
+    nz = Normalizer(stats, {"arm": 3, "extra": 2})  # a key without statistics maps [0, 1] to [-1, 1]
+    g = torch.Generator().manual_seed(seed)
+    mn = torch.tensor(mins + [0.0, 0.0])
+    dl = torch.tensor(deltas + [1.0, 1.0])
+    x = mn + dl * torch.rand(1, 4, 5, generator=g)
+    y = nz.normalize_data(x, ["robot"])
+    assert y.min() >= -1 and y.max() <= 1
+    assert torch.allclose(nz.unnormalize_data(y, ["robot"]), x, atol=1e-4)
+    far = nz.normalize_data(x + 10 * dl, ["robot"])
+    assert (far == 1).all()
+    # masked unnormalize keeps the selected degrees of freedom only
+    mask = torch.tensor([[1, 1, 1, 0, 0]]).expand(1, 5).unsqueeze(0)
+    sel = nz.unnormalize_data(y[..., :3], ["robot"], dof_mask=mask)
+    assert torch.allclose(sel, x[..., :3], atol=1e-4)
