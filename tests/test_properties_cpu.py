@@ -16,7 +16,7 @@ from hypothesis import strategies as st
 
 from wallx_b200.ops import ref
 
-_FAST = settings(max_examples=40, deadline=None, suppress_health_check=list(HealthCheck))
+_FAST = settings(max_examples=40, deadline=None, suppress_health_check=list(HealthCheck), derandomize=True, database=None)
 
 
 # ----------------------------------------------------------------------------- routing
