@@ -107,3 +107,27 @@ def test_collator_and_dataset_end_to_end():
     item["action"][0, 0] = float("nan")
     b2 = col([item])
     assert b2["dof_mask"][0, 0, 0] == 0 and b2["action_chunk"][0, 0, 0] == minmax_normalize(torch.zeros(1), [-3.0], [3.0])
+
+
+def test_distributed_dataloader_helper_shards_without_overlap():
+    """``get_distributed_dataloader`` (the reference's helper name): two ranks see disjoint halves of the training
+    split, the validation loader is not shuffled."""
+    from wall_x.data.load_lerobot_dataset import get_distributed_dataloader
+
+    cfg = tiny_config()
+    proc = make_processor(cfg, 16)
+    conf = {"batch_size_per_gpu": 2, "num_workers": 0,
+            "data": {"action_horizon": 16, "resolution": {"face_view": 112, "left_wrist_view": 112, "right_wrist_view": 112}}}
+    dc = get_data_configs(conf["data"])
+    pre = PreprocessedDataset(SyntheticEpisodeDataset(n=40, horizon=16), conf, dc, processor=proc, model_config=cfg)
+    seen = []
+    for rank in range(2):
+        loader, sampler = get_distributed_dataloader(pre, conf, rank=rank, world_size=2, seed=7, is_train=True)
+        sampler.set_epoch(0)
+        seen.append(list(iter(sampler)))
+        assert len(loader) == len(seen[-1]) // 2
+    assert not set(seen[0]) & set(seen[1]) and len(seen[0]) == len(seen[1]) == 19
+    vloader, vsampler = get_distributed_dataloader(pre, conf, rank=0, world_size=1, is_train=False)
+    assert list(iter(vsampler)) == list(range(len(vsampler)))
+    batch = next(iter(vloader))
+    assert batch["input_ids"].shape[0] <= 2
