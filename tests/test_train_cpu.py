@@ -294,3 +294,46 @@ def test_corrupt_or_missing_checkpoint_files_raise_cleanly(tmp_path):
     torch.save(TrainEngine(m2, lr=1e-3).optimizer_state(), f)
     with pytest.raises(ValueError):
         load_optimizer_shards(eng, str(tmp_path), 1)
+
+
+def _sharded_linear_worker(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    torch.distributed.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    from wallx_b200.parallel.ag_linear import AgLinear
+
+    g = torch.Generator().manual_seed(0)
+    full_w = torch.randn(8, 16, generator=g)
+    bias = torch.randn(8, generator=g)
+    lin = AgLinear(16, 8, None, "cpu", bias=True)
+    lin.weight.load_full(full_w)
+    with torch.no_grad():
+        lin.bias.copy_(bias)
+    assert lin.weight.shard.shape == (8 // world, 16)
+    assert torch.equal(lin.weight.gather_full(), full_w)
+    x = torch.randn(5, 16, generator=torch.Generator().manual_seed(10 + rank), requires_grad=True)
+    y = lin(x)
+    want = torch.nn.functional.linear(x.detach(), full_w, bias)
+    assert torch.allclose(y, want, atol=1e-5)
+    gy = torch.randn(5, 8, generator=torch.Generator().manual_seed(20 + rank))
+    y.backward(gy)
+    assert torch.allclose(x.grad, gy @ full_w, atol=1e-5)
+    assert torch.allclose(lin.bias.grad, gy.sum(0), atol=1e-5)
+    local_dw = gy.t() @ x.detach()
+    shard_grad = lin.reduce_scatter_grad()
+    torch.save({"local_dw": local_dw, "shard_grad": shard_grad}, os.path.join(tmp, f"agl_{rank}.pt"))
+    torch.distributed.barrier()
+    torch.distributed.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("world", [2, 4])
+def test_sharded_weight_linear_over_gloo(tmp_path, world):
+    """Shard arithmetic of the gathered-weight linear layer (rows per rank, gather, full-gradient accumulation,
+    averaged reduce-scatter) with the collective stand-in that replaces the fused NVLink gather on CPU."""
+    mp.spawn(_sharded_linear_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    parts = [torch.load(tmp_path / f"agl_{r}.pt") for r in range(world)]
+    mean_dw = sum(p["local_dw"] for p in parts) / world
+    rows = 8 // world
+    for r, p in enumerate(parts):
+        assert torch.allclose(p["shard_grad"], mean_dw[r * rows:(r + 1) * rows], atol=1e-5)

@@ -53,6 +53,13 @@ class ShardedWeight:
             raise ValueError("weight row length must be a multiple of 8 elements (16 bytes)")
         self.rows, self.cols = int(rows), int(cols)
         self.rows_per_rank = rows // self.world
+        self.group = group
+        if torch.device(device).type == "cpu":
+            # CPU stand-in (tests of the shard arithmetic over gloo): same row split, the gather is a collective
+            self.shard = torch.zeros(self.rows_per_rank, cols, dtype=torch.float32)
+            self.peer_ptrs, self.flags, self.epoch, self.workspace = [], None, 0, None
+            self.grad = self.full_grad = None
+            return
         self.shard = symm_mem.empty(self.rows_per_rank, cols, dtype=torch.bfloat16, device=device)
         self.shard.zero_()
         hdl = symm_mem.rendezvous(self.shard, group)
@@ -66,7 +73,16 @@ class ShardedWeight:
     def load_full(self, full: torch.Tensor) -> None:
         """Keep this rank's rows of a replicated full weight."""
         r0 = self.rank * self.rows_per_rank
-        self.shard.copy_(full[r0:r0 + self.rows_per_rank].to(torch.bfloat16))
+        self.shard.copy_(full[r0:r0 + self.rows_per_rank].to(self.shard.dtype))
+
+    def gather_full(self) -> torch.Tensor:
+        """The whole weight by a plain collective (CPU stand-in and debugging; the GPU path never materialises it
+        outside the GEMM's staging buffer)."""
+        import torch.distributed as dist
+
+        parts = [torch.empty_like(self.shard) for _ in range(self.world)]
+        dist.all_gather(parts, self.shard.contiguous(), group=self.group)
+        return torch.cat(parts, dim=0)
 
     def staging(self, slot: int = 0) -> torch.Tensor:
         return self.workspace.view(self.rows, self.cols, slot)
@@ -89,6 +105,22 @@ def ag_launch(specs: Sequence[G.GemmSpec], weights: Sequence[ShardedWeight], n_p
 def ag_gemm(x: torch.Tensor, w: ShardedWeight, *, transpose_w: bool = False, bias=None, residual=None, flags: int = 0,
             out: Optional[torch.Tensor] = None, n_pullers: int = 0) -> torch.Tensor:
     """``x @ W.T`` (``transpose_w=False``, x ``[M, cols]``) or ``x @ W`` (``True``, x ``[M, rows]``)."""
+    if not x.is_cuda:  # CPU stand-in: gather by collective, then the oracle's matmul and epilogue
+        full = w.gather_full().to(torch.float32)
+        y = x.float() @ (full if transpose_w else full.t())
+        if bias is not None:
+            y = y + bias.float()
+        if flags & G.ACT_SWIGLU:
+            from ..ops import ref
+
+            y = ref.swiglu_interleaved(y)
+        if residual is not None:
+            y = y + residual.float()
+        y = y.to(torch.float32 if (flags & G.OUT_FP32) else x.dtype)
+        if out is not None:
+            out.copy_(y)
+            return out
+        return y
     M = x.shape[0]
     N = w.cols if transpose_w else w.rows
     if out is None:
@@ -117,7 +149,10 @@ class _AgLinearFn(torch.autograd.Function):
         # full weight gradient, fp32, accumulated over micro-batches; reduce-scattered by the owner
         if w.full_grad is None:
             w.full_grad = torch.zeros(w.rows, w.cols, dtype=torch.float32, device=dy.device)
-        G.launch([G.GemmSpec(dy2, x2, w.full_grad, a_mn=True, b_mn=True, flags=G.OUT_FP32 | G.ACCUMULATE)])
+        if dy2.is_cuda:
+            G.launch([G.GemmSpec(dy2, x2, w.full_grad, a_mn=True, b_mn=True, flags=G.OUT_FP32 | G.ACCUMULATE)])
+        else:
+            w.full_grad += dy2.float().t() @ x2.float()
         dbias = dy2.float().sum(0).to(dy.dtype) if ctx.has_bias else None
         return dx.view(*dy.shape[:-1], w.cols), None, None, dbias, None
 
@@ -131,7 +166,8 @@ class AgLinear(torch.nn.Module):
         self.weight = ShardedWeight(out_features, in_features, group, device, workspace)
         self.group = group
         self.n_pullers = n_pullers
-        self.bias = torch.nn.Parameter(torch.zeros(out_features, dtype=torch.bfloat16, device=device)) if bias else None
+        bdt = torch.bfloat16 if torch.device(device).type == "cuda" else torch.float32
+        self.bias = torch.nn.Parameter(torch.zeros(out_features, dtype=bdt, device=device)) if bias else None
         # autograd needs one differentiable input even when x does not require grad
         self._anchor = torch.nn.Parameter(torch.zeros((), device=device))
 
@@ -144,7 +180,12 @@ class AgLinear(torch.nn.Module):
 
         w = self.weight
         out = torch.empty(w.rows_per_rank, w.cols, dtype=torch.float32, device=w.shard.device)
-        dist.reduce_scatter_tensor(out, w.full_grad, op=dist.ReduceOp.AVG, group=self.group)
+        if w.full_grad.is_cuda:
+            dist.reduce_scatter_tensor(out, w.full_grad, op=dist.ReduceOp.AVG, group=self.group)
+        else:  # gloo has no reduce-scatter: all-reduce and keep this rank's rows
+            dist.all_reduce(w.full_grad, op=dist.ReduceOp.SUM, group=self.group)
+            r0 = w.rank * w.rows_per_rank
+            out.copy_(w.full_grad[r0:r0 + w.rows_per_rank] / w.world)
         w.full_grad = None
         w.grad = out
         return out
