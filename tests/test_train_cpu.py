@@ -337,3 +337,29 @@ def test_sharded_weight_linear_over_gloo(tmp_path, world):
     rows = 8 // world
     for r, p in enumerate(parts):
         assert torch.allclose(p["shard_grad"], mean_dw[r * rows:(r + 1) * rows], atol=1e-5)
+
+
+def test_typed_training_config_accepts_the_example_and_names_bad_keys():
+    import yaml
+
+    from wallx_b200.train.config import TrainConfig
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with open(os.path.join(root, "workspace", "lerobot_example", "finetune_flow.yml")) as f:
+        raw = yaml.safe_load(f)
+    tc = TrainConfig.from_dict(raw).validate(require_paths=True)
+    assert tc.unknown_keys == [] and tc.learning_rate == 9e-5 and tc.transport == "auto" and tc.FSDP2 is True
+    assert sum(tc.dof_config.values()) == 20 and tc.data["action_horizon"] == 32
+    for key, bad, word in [("learning_rate", -1.0, "learning_rate"), ("min_lr", 1.0, "min_lr"), ("batch_size_per_gpu", 0, "batch_size_per_gpu"),
+                           ("gradient_accumulation_steps", 1.5, "gradient_accumulation_steps"), ("transport", "tcp", "transport"),
+                           ("optimizer_dtype", "fp8", "optimizer_dtype"), ("use_fast_tokenizer", "yes", "use_fast_tokenizer"),
+                           ("dof_config", {"arm": 21}, "dof_config"), ("padding_side", "top", "padding_side"),
+                           ("resume", {"ckpt": "", "load_ckpt_only": True}, "resume"), ("resume", {"ckpt": "x", "oops": 1}, "resume")]:
+        cfg = dict(raw)
+        cfg[key] = bad
+        with pytest.raises(ValueError, match=word):
+            TrainConfig.from_dict(cfg).validate()
+    extra = dict(raw, my_note="run 7")
+    assert TrainConfig.from_dict(extra).validate().unknown_keys == ["my_note"]
+    with pytest.raises(ValueError, match="pretrained_wallx_path"):
+        TrainConfig.from_dict(dict(raw, pretrained_wallx_path=None)).validate(require_paths=True)

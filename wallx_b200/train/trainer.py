@@ -93,6 +93,11 @@ class QwenVlAct_Trainer:
         for key in ("learning_rate", "num_epoch"):
             if key not in config:
                 raise ValueError(f"config is missing required key '{key}'")
+        from .config import TrainConfig
+
+        self.typed_config = TrainConfig.from_dict(config).validate()  # wrong values fail here, by key name
+        if self.typed_config.unknown_keys:
+            print_rank_last(f"config: keys this trainer does not read: {self.typed_config.unknown_keys}")
         self.config = config
         self.logger = logger
         self.accelerator = accelerator  # accepted for signature compatibility; not used
