@@ -111,6 +111,10 @@ def main():
     import torch
     import torch.distributed as dist
 
+    if not torch.cuda.is_available():  # the training step is CUDA kernels only: no CPU fallback is timed
+        print(json.dumps({"impl": "ours", "unavailable": "no CUDA device: this benchmark needs a B200"}), flush=True)
+        sys.exit(1)
+
     from wallx_b200.config import wall_oss_config
     from wallx_b200.data.collator import add_pack_info, pin_batch, to_device
     from wallx_b200.data.synthetic import images_to_patches, make_batch, make_processor
