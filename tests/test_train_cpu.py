@@ -363,3 +363,106 @@ def test_typed_training_config_accepts_the_example_and_names_bad_keys():
     assert TrainConfig.from_dict(extra).validate().unknown_keys == ["my_note"]
     with pytest.raises(ValueError, match="pretrained_wallx_path"):
         TrainConfig.from_dict(dict(raw, pretrained_wallx_path=None)).validate(require_paths=True)
+
+
+class _FakeSymm:
+    """Stand-in for the NVLink transport: rank 0 of 2 whose peer always contributes the same gradients, so a step must
+    equal a single-rank step on the doubled gradient. Records when each unit is reduced."""
+
+    def __init__(self):
+        self.calls, self.buffers = [], []
+        self.local_sumsq = torch.zeros(1)
+        self._shards = {}
+
+    def reserve(self, total, dtype=torch.float32):
+        self.reserved = total
+
+    def alloc_param(self, n, dtype):
+        return torch.zeros(n, dtype=dtype)
+
+    def alloc_grad(self, n, dtype):
+        return torch.zeros(n, dtype=dtype)
+
+    def register_buffers(self, buffers):
+        self.buffers = list(buffers)
+
+    def begin_step(self):
+        self.calls.append("begin")
+        self.local_sumsq.zero_()
+        self._shards = {}
+
+    def reduce_scatter_unit(self, k):
+        b = self.buffers[k]
+        s0, s1 = b.shard_range
+        g = 2.0 * b.grad[s0:s1].float()  # own + identical peer
+        self._shards[k] = g
+        self.local_sumsq += (g ** 2).sum()
+        self.calls.append(k)
+
+    def reduce_scatter_grads(self, buffers):
+        self.begin_step()
+        for k in reversed(range(len(buffers))):
+            self.reduce_scatter_unit(k)
+        return self.grad_shards()
+
+    def grad_shards(self):
+        return [self._shards[k] for k in range(len(self.buffers))]
+
+    def all_reduce_scalar(self, t):
+        return t * 2.0  # the peer's shard carries the same squared norm
+
+    def all_reduce_vector(self, t):
+        return t * 2.0
+
+    def all_gather_params(self, buffers):
+        self.calls.append("push")
+
+
+def test_overlap_schedule_learns_triggers_and_reduces_units_during_backward(monkeypatch):
+    """Host logic of the reduce-scatter overlap: the first step records each unit's gradient order, later steps
+    reduce a unit as soon as its last gradient arrived (before backward returns), a unit that was not triggered is
+    reduced after backward, and every unit is reduced exactly once per step."""
+    torch.manual_seed(0)
+    m = torch.nn.Sequential(torch.nn.Linear(6, 6), torch.nn.Tanh(), torch.nn.Linear(6, 3))
+
+    class Wrapper(torch.nn.Module):  # two "decoder layers" + a root unit, as default_units expects
+        def __init__(self):
+            super().__init__()
+            self.model = torch.nn.Module()
+            self.model.layers = torch.nn.ModuleList([m[0], m[2]])
+            self.scale = torch.nn.Parameter(torch.ones(3))
+
+        def forward(self, x):
+            return self.model.layers[1](torch.tanh(self.model.layers[0](x))) * self.scale
+
+    net = Wrapper()
+    fake = _FakeSymm()
+    eng = TrainEngine(net, lr=1e-2, weight_decay=0.0, max_grad_norm=1e9, world=2, rank=0, transport="symm", symm=fake)
+    assert len(eng.buffers) == 3 and fake.buffers == eng.buffers
+    eng.overlap_reduce = True
+    eng.check_touched = False
+    early = []
+    monkeypatch.setattr(eng, "_early_reduce", lambda k: (early.append(k), fake.reduce_scatter_unit(k), eng._early.add(k)))
+    x = torch.randn(4, 6)
+    # step 1: nothing is known yet -> every unit is reduced after backward
+    eng.backward(net(x).sum())
+    assert fake.calls == ["begin"] and not early
+    eng.optimizer_step(1e-2)
+    assert sorted(c for c in fake.calls if isinstance(c, int)) == [0, 1, 2] and fake.calls[-1] == "push"
+    assert eng._learned and set(eng._trigger) == {0, 1, 2} and all(eng._expected[k] >= 1 for k in range(3))
+    # step 2: units whose last gradient is an autograd hook are reduced during backward, in backward order
+    fake.calls.clear()
+    eng.backward(net(x).sum())
+    during = [c for c in fake.calls if isinstance(c, int)]
+    assert during == early and len(during) >= 2 and during.index(1) < during.index(0)  # the later layer finishes first
+    eng.optimizer_step(1e-2)
+    ints = [c for c in fake.calls if isinstance(c, int)]
+    assert sorted(ints) == [0, 1, 2]  # each unit exactly once, the rest after backward
+    # a step whose backward bypasses engine.backward() is still reduced, just without overlap
+    fake.calls.clear()
+    early.clear()
+    net(x).sum().backward()
+    eng.optimizer_step(1e-2)
+    assert not early and sorted(c for c in fake.calls if isinstance(c, int)) == [0, 1, 2] and fake.calls[0] == "begin"
+    for p in net.parameters():
+        assert torch.isfinite(p).all()
