@@ -61,3 +61,22 @@ def test_no_legacy_tensor_core_paths_or_compat_layers_in_kernels():
     assert not bad, bad
     py_bad = _offenders(r"^\s*(import|from)\s+(tri" + r"ton|tile" + r"lang)\b|torch\.comp" + r"ile\(")
     assert not py_bad, py_bad
+
+
+def test_bench_contract_keys_and_entry_points_exist():
+    """The benchmark line and the build / smoke entry points other tooling depends on."""
+    text = (ROOT / "bench.py").read_text()
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling", "vs_baseline",
+                "dtype", "data", "config", "global_batch", "seq_len", "parallelism", "clocks", "sm_mhz", "sm_max_mhz", "reasons", "e2e",
+                "h2d_bytes_per_step", "d2h_bytes_per_step", "gpu_launches", "impl", "unavailable"):
+        assert f'"{key}"' in text, key
+    for flag in ("--gpus", "--steps", "--warmup", "--impl"):
+        assert flag in text, flag
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("graft_entry_check", ROOT / "__graft_entry__.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert callable(mod.build) and callable(mod.smoke)
+    entry = (ROOT / "__graft_entry__.py").read_text() + (ROOT / "wallx_b200" / "ops" / "_ext.py").read_text() + (ROOT / "setup.py").read_text()
+    assert "arch=compute_100a,code=sm_100a" in entry and "-lineinfo" in entry
