@@ -18,7 +18,8 @@ def _tracked_sources():
     out = []
     for n in names:
         p = ROOT / n
-        if n and p.suffix in SOURCE_SUFFIXES and p.is_file() and p.name not in ("BASELINE.json",) and not n.startswith("profiles/"):
+        # records at the repository root (*.json written by the test harness, not by this project) are not sources
+        if n and p.suffix in SOURCE_SUFFIXES and p.is_file() and not ("/" not in n and p.suffix == ".json") and not n.startswith("profiles/"):
             out.append(p)
     return out
 
