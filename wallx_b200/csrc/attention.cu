@@ -90,14 +90,6 @@ __device__ __forceinline__ bool key_allowed(int kk, const int4& qi, int kflag) {
   return kk >= qi.x && kk < qi.y && (kk <= qi.z || (qi.w != 0 && kflag != 0));
 }
 
-// Optional stage timestamps of one CTA (debug builds with -DWX_ATTN_TRACE only).
-#ifdef WX_ATTN_TRACE
-__device__ long long g_attn_trace[16 * 16];
-#define TRACE_AS(t, slot) do { if (blockIdx.x == 3 && blockIdx.y == 0 && tid == (t) && j < 16) g_attn_trace[j * 16 + (slot)] = clock64(); } while (0)
-#else
-#define TRACE_AS(t, slot) do {} while (0)
-#endif
-
 // ================================================================================ forward
 // 160 threads: warps 0..3 own one query row per thread (softmax, O rescale, epilogue); warp 4 is
 // the issue warp (one lane drives TMA loads and tcgen05.mma). The two roles talk through mbarriers
@@ -191,12 +183,9 @@ attn_fwd_kernel(const __grid_constant__ AttnArgs a, int* __restrict__ status) {
       for (int j = 0; j < nblk && ok; ++j) {
         const int st = j & 1;
         const uint32_t ka = smem_u32(sKV + st * 32768), va = ka + 16384;
-        TRACE_AS(128, 0);
         ok = mbar_wait(&kv_full[st], (j >> 1) & 1, abort_flag);
-        TRACE_AS(128, 1);
         if (ok && j > 0) ok = mbar_wait(s_free, (j - 1) & 1, abort_flag);  // S(j-1) is in registers
         if (!ok) break;
-        TRACE_AS(128, 2);
         tc_fence_after();
         for (int k = 0; k < D / 16; ++k) {
           const uint64_t da = make_smem_desc_sw128(qa + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
@@ -204,17 +193,14 @@ attn_fwd_kernel(const __grid_constant__ AttnArgs a, int* __restrict__ status) {
           tc_mma_bf16(tS, da, db, idesc_s, k != 0);
         }
         tc_commit(s_bar);
-        TRACE_AS(128, 3);
         // stage (j+1)&1 was last read by PV(j-1): refill it once that is done
         if (j > 0 && j + 1 < nblk) {
           ok = mbar_wait(pv_bar, (j - 1) & 1, abort_flag);
           if (!ok) break;
           load_kv(j + 1);
         }
-        TRACE_AS(128, 4);
         ok = mbar_wait(p_ready, j & 1, abort_flag);
         if (!ok) break;
-        TRACE_AS(128, 5);
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -223,7 +209,6 @@ attn_fwd_kernel(const __grid_constant__ AttnArgs a, int* __restrict__ status) {
           tc_mma_bf16(tO, da, db, idesc_o, (j | k) != 0);
         }
         tc_commit(pv_bar);
-        TRACE_AS(128, 6);
       }
     }
   } else {
@@ -238,10 +223,8 @@ attn_fwd_kernel(const __grid_constant__ AttnArgs a, int* __restrict__ status) {
         s_kflag[st][tid] = (kk < a.Tk) ? (a.ktab[kk].w & 1) : 0;
       }
       if (a.has_bidir) asm volatile("bar.sync 1, 128;" ::: "memory");  // flags visible to the 4 row warps
-      TRACE_AS(0, 8);
       if (ok) ok = mbar_wait(s_bar, j & 1, abort_flag);
       tc_fence_after();
-      TRACE_AS(0, 9);
       float sc[64];
       {
         uint32_t r[32];
@@ -256,7 +239,6 @@ attn_fwd_kernel(const __grid_constant__ AttnArgs a, int* __restrict__ status) {
       }
       tc_fence_before();
       mbar_arrive(s_free);  // the issue warp may overwrite S with the next block's scores
-      TRACE_AS(0, 10);
       // Interior blocks (every key visible to every row of the warp) skip the per-element mask.
       const bool fast = __all_sync(0xffffffffu, kbase >= qi.x && kbase + 63 <= qi.z && kbase + 63 < qi.y);
       float raw_max = -INFINITY;
@@ -288,12 +270,10 @@ attn_fwd_kernel(const __grid_constant__ AttnArgs a, int* __restrict__ status) {
       l_run = l_run * alpha + psum;
       const bool changed = m_new > m_run;
       m_run = m_new;
-      TRACE_AS(0, 11);
       // PV(j-1) must be done before O is rescaled; P(j) goes to the other stage, which PV(j-2) freed
       if (j > 0) {
         if (ok) ok = mbar_wait(pv_bar, (j - 1) & 1, abort_flag);
         tc_fence_after();
-        TRACE_AS(0, 12);
         if (__any_sync(0xffffffffu, changed)) {
           for (int c = 0; c < D; c += 32) {
             uint32_t r[32];
@@ -313,7 +293,6 @@ attn_fwd_kernel(const __grid_constant__ AttnArgs a, int* __restrict__ status) {
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(p_ready);
-      TRACE_AS(0, 13);
     }
     if (ok && nblk > 0) ok = mbar_wait(pv_bar, (nblk - 1) & 1, abort_flag);
     tc_fence_after();
@@ -889,12 +868,6 @@ bool shape_ok(const AttnShape& s) {
 }
 
 }  // namespace
-
-#ifdef WX_ATTN_TRACE
-int attn_trace_read(long long* dst) {
-  return static_cast<int>(cudaMemcpyFromSymbol(dst, g_attn_trace, sizeof(long long) * 256));
-}
-#endif
 
 int attn_fwd(const AttnShape& s, const void* q, const void* k, const void* v, const void* qtab, const void* ktab,
              void* out, long ld_out, float* lse, cudaStream_t stream, int* status) {

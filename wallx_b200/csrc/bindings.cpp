@@ -231,22 +231,13 @@ void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, 
 
 void register_kernel_bindings(pybind11::module_& m);
 
-#ifdef WX_ATTN_TRACE
-namespace wx { int attn_trace_read(long long* dst); }
-at::Tensor attn_trace() {
-  at::Tensor t = at::zeros({16, 16}, at::kLong);
-  wx::attn_trace_read(reinterpret_cast<long long*>(t.data_ptr<int64_t>()));
-  return t;
-}
-#endif
-
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
-#ifdef WX_ATTN_TRACE
-  m.def("attn_trace", &attn_trace);
-#endif
   m.def("gemm_ag", &gemm_ag, "GEMM with the weight all-gather fused in (peer loads over NVLink)");
   m.def("gemm_grouped", &gemm_grouped, "tcgen05 GEMM: one or two problems in one launch");
   m.def("read_status", &read_status, "read and clear the device-side wait-timeout status");
+  m.def("status_tensor", [](int64_t device_index) {
+    return status_tensor(at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(device_index)));
+  }, "the device-side status words themselves (int32[4]; word 0 non-zero after a wait ran out)");
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
   register_kernel_bindings(m);

@@ -5,9 +5,10 @@
 //
 // NVSwitch gives every peer full bandwidth, so each rank pulls its shard from all peers at once
 // (one-shot reduce-scatter) and pushes its updated shard to all peers at once (one-shot
-// all-gather); there is no ring. Waits on peer flags are bounded: after 2 s the kernel records an
-// error status and returns.
+// all-gather); there is no ring. Waits on peer flags are bounded: after the caller's limit (2 s by
+// default, ten minutes at most) the kernel records an error status and returns.
 #include "comm.h"
+#include "devinfo.h"
 
 #include <cuda_bf16.h>
 
@@ -29,7 +30,7 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   return v;
 }
 
-__global__ void symm_barrier_kernel(PeerPtrs flags, int rank, int world, int epoch, int* status) {
+__global__ void symm_barrier_kernel(PeerPtrs flags, int rank, int world, int epoch, int* status, uint64_t limit_ns) {
   const int p = threadIdx.x;
   if (p >= world) return;
   __threadfence_system();
@@ -38,7 +39,7 @@ __global__ void symm_barrier_kernel(PeerPtrs flags, int rank, int world, int epo
   const uint64_t t0 = gtimer_ns();
   unsigned it = 0;
   while (ld_acquire_sys(mine) < epoch) {
-    if (((++it) & 1023u) == 0u && gtimer_ns() - t0 > 2000000000ull) {
+    if (((++it) & 1023u) == 0u && gtimer_ns() - t0 > limit_ns) {
       atomicExch(status, 16 + p);  // peer p never arrived
       return;
     }
@@ -203,9 +204,11 @@ __global__ void adamw_f32g_kernel(__nv_bfloat16* __restrict__ p16, float* __rest
 
 }  // namespace
 
-int symm_barrier(const PeerPtrs& flags, int rank, int world, int epoch, int* status, cudaStream_t s) {
+int symm_barrier(const PeerPtrs& flags, int rank, int world, int epoch, int* status, cudaStream_t s, long timeout_ms) {
   if (world < 1 || world > kMaxPeers) return -1;
-  symm_barrier_kernel<<<1, 32, 0, s>>>(flags, rank, world, epoch, status);
+  if (timeout_ms < 1) timeout_ms = 1;
+  if (timeout_ms > 600000) timeout_ms = 600000;  // always bounded: ten minutes at most
+  symm_barrier_kernel<<<1, 32, 0, s>>>(flags, rank, world, epoch, status, static_cast<uint64_t>(timeout_ms) * 1000000ull);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -213,7 +216,7 @@ int rs_reduce(const PeerPtrs& grads, const ShardDesc* table_dev, int nbuf, int w
               cudaStream_t s) {
   if (nbuf == 0) return 0;
   // about 16 resident blocks per SM in total, whatever the number of buffers
-  int gx = (148 * 16 + nbuf - 1) / nbuf;
+  int gx = (sm_count() * 16 + nbuf - 1) / nbuf;
   gx = gx < 8 ? 8 : gx;
   if (static_cast<long>(gx) * nbuf > kRsMaxBlocks) gx = kRsMaxBlocks / nbuf;
   if (gx < 1) return -1;
@@ -223,7 +226,7 @@ int rs_reduce(const PeerPtrs& grads, const ShardDesc* table_dev, int nbuf, int w
 
 int ag_push(const PeerPtrs& params, const ShardDesc* table_dev, int nbuf, int rank, int world, cudaStream_t s) {
   if (nbuf == 0 || world == 1) return 0;
-  int gx = (148 * 16 + nbuf - 1) / nbuf;
+  int gx = (sm_count() * 16 + nbuf - 1) / nbuf;
   gx = gx < 8 ? 8 : gx;
   ag_push_kernel<<<dim3(gx, nbuf), 256, 0, s>>>(params, table_dev, rank, world);
   return static_cast<int>(cudaGetLastError());
@@ -242,7 +245,7 @@ int adamw_step_f32g(void* p16, float* p32, float* m, float* v, const float* g, l
                     const float* norm_sq, cudaStream_t s) {
   if (n == 0) return 0;
   long b = (n + 255) / 256;
-  if (b > 148 * 16) b = 148 * 16;
+  if (b > static_cast<long>(sm_count()) * 16) b = static_cast<long>(sm_count()) * 16;
   adamw_f32g_kernel<<<static_cast<unsigned>(b), 256, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(p16), p32, m, v, g, n,
                                                              hyper, norm_sq);
   return static_cast<int>(cudaGetLastError());

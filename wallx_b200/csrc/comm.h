@@ -24,8 +24,11 @@ struct ShardDesc {
 };
 
 // Every rank signals every peer and waits (bounded) until all peers signalled `epoch`.
-// flags.p[r] points at rank r's int[kMaxPeers] flag array. Sets *status non-zero on time-out.
-int symm_barrier(const PeerPtrs& flags, int rank, int world, int epoch, int* status, cudaStream_t s);
+// flags.p[r] points at rank r's int[kMaxPeers] flag array. Sets *status non-zero on time-out
+// (`timeout_ms`, clamped to [1 ms, 10 min]: training barriers must tolerate a rank that is late by a
+// data-loader hiccup, failure tests want a short limit).
+int symm_barrier(const PeerPtrs& flags, int rank, int world, int epoch, int* status, cudaStream_t s,
+                 long timeout_ms = 2000);
 
 // out[out_off + i] = sum_r bf16(grads.p[r][arena_off + i]) in fp32, for every table entry; adds the
 // sum of squares of the results into *sumsq.

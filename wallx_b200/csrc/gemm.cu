@@ -15,6 +15,7 @@
 // Reference parity: csrc/dual_asym_grouped_gemm.cu:49-136 (two problems, four layouts) and the
 // cuBLAS calls behind every nn.Linear in wall_x/model.
 #include "gemm.h"
+#include "devinfo.h"
 #include "ptx.cuh"
 
 #include <cstdlib>
@@ -705,16 +706,7 @@ bool make_tmap(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer
   return r == CUDA_SUCCESS;
 }
 
-int num_sms() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
-}
+int num_sms() { return sm_count(); }
 
 template <int BN, bool A_MN, bool B_MN, bool AG = false>
 int launch_t(const GemmArgs& args, int grid, cudaStream_t stream, int* status) {

@@ -171,8 +171,10 @@ wx::PeerPtrs peer_ptrs(const std::vector<int64_t>& ptrs) {
   return pp;
 }
 
-void symm_barrier(const std::vector<int64_t>& flag_ptrs, int64_t rank, int64_t epoch, at::Tensor& status) {
-  WX_CHECK_RC(wx::symm_barrier(peer_ptrs(flag_ptrs), rank, flag_ptrs.size(), epoch, status.data_ptr<int>(), cur_stream()),
+void symm_barrier(const std::vector<int64_t>& flag_ptrs, int64_t rank, int64_t epoch, at::Tensor& status,
+                  int64_t timeout_ms) {
+  WX_CHECK_RC(wx::symm_barrier(peer_ptrs(flag_ptrs), rank, flag_ptrs.size(), epoch, status.data_ptr<int>(), cur_stream(),
+                               static_cast<long>(timeout_ms)),
               "symm_barrier");
 }
 
@@ -279,7 +281,8 @@ void register_kernel_bindings(pybind11::module_& m) {
   m.def("rope_index", &rope_index);
   m.def("vit_rot_pos", &vit_rot_pos);
   m.def("vit_window_index", &vit_window_index);
-  m.def("symm_barrier", &symm_barrier);
+  m.def("symm_barrier", &symm_barrier, pybind11::arg("flag_ptrs"), pybind11::arg("rank"), pybind11::arg("epoch"),
+        pybind11::arg("status"), pybind11::arg("timeout_ms") = 2000);
   m.def("rs_reduce", &rs_reduce);
   m.def("ag_push", &ag_push);
   m.def("small_allreduce_write", &small_allreduce_write);

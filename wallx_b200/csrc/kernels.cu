@@ -7,6 +7,7 @@
 // ATen chains behind Qwen2RMSNorm (modeling_qwen2_5_vl.py:122-139), SiLU*mul, CrossEntropyLoss
 // and torch.optim.AdamW (qwen_vl_act_trainer.py:577-581).
 #include "kernels.h"
+#include "devinfo.h"
 
 #include <cuda_bf16.h>
 #include <math.h>
@@ -680,7 +681,7 @@ ce_bwd_kernel(__nv_bfloat16* __restrict__ logits, const long* __restrict__ label
 
 // ------------------------------------------------------------------------------ optimizer
 // sum of squares of a bf16 buffer accumulated (atomically) into out[0].
-constexpr int kSumsqMaxBlocks = 148 * 8;
+constexpr int kSumsqMaxBlocks = 4096;  // scratch slots of the deterministic grid reduction
 __device__ float g_sumsq_scratch[kSumsqMaxBlocks];
 __device__ unsigned g_sumsq_counter = 0;
 
@@ -781,7 +782,8 @@ __global__ void adamw_kernel(__nv_bfloat16* __restrict__ p16, float* __restrict_
   }
 }
 
-inline int blocks_for(long n, int threads, int cap = 148 * 16) {
+inline int blocks_for(long n, int threads, int cap = 0) {
+  if (cap <= 0) cap = sm_count() * 16;
   long b = (n + threads - 1) / threads;
   if (b > cap) b = cap;
   if (b < 1) b = 1;
@@ -796,7 +798,7 @@ int rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, const int* 
   if (C % 8 != 0 || C > NORM_THREADS * 8 * NORM_MAX_CHUNKS) return -1;
   if (T == 0) return 0;
   if (C % 256 == 0 && C <= 2048) {  // one warp per row
-    const int g = (T + 7) / 8 < 148 * 8 ? (T + 7) / 8 : 148 * 8;
+    const int g = (T + 7) / 8 < sm_count() * 8 ? (T + 7) / 8 : sm_count() * 8;
     const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
     const __nv_bfloat16* wb = reinterpret_cast<const __nv_bfloat16*>(w);
     __nv_bfloat16* yb = reinterpret_cast<__nv_bfloat16*>(y);
@@ -807,14 +809,14 @@ int rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, const int* 
     }
     return static_cast<int>(cudaGetLastError());
   }
-  const int grid = T < 148 * 8 ? T : 148 * 8;
+  const int grid = T < sm_count() * 8 ? T : sm_count() * 8;
   rms_norm_fwd_kernel<<<grid, NORM_THREADS, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x),
                                                      reinterpret_cast<const __nv_bfloat16*>(w),
                                                      reinterpret_cast<__nv_bfloat16*>(y), rstd, dest, T, C, eps);
   return static_cast<int>(cudaGetLastError());
 }
 
-int rms_norm_bwd_blocks(int T) { return T < 148 * 2 ? (T > 0 ? T : 1) : 148 * 2; }
+int rms_norm_bwd_blocks(int T) { return T < sm_count() * 2 ? (T > 0 ? T : 1) : sm_count() * 2; }
 
 int rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const int* dest, void* dx,
                  float* dw_partial, void* dw, int T, int C, cudaStream_t s) {
@@ -846,7 +848,7 @@ int swiglu_bwd(const void* dh, const void* gu, void* dgu, int R, int width_gu, l
   const int nblk = width_gu / 32;
   const long total = static_cast<long>(R) * nblk * 2;
   if (total == 0) return 0;
-  swiglu_bwd_kernel<<<blocks_for(total, 256, 148 * 32), 256, 0, s>>>(
+  swiglu_bwd_kernel<<<blocks_for(total, 256, sm_count() * 32), 256, 0, s>>>(
       reinterpret_cast<const __nv_bfloat16*>(dh), reinterpret_cast<const __nv_bfloat16*>(gu),
       reinterpret_cast<__nv_bfloat16*>(dgu), R, nblk, ld_dh, ld_gu);
   return static_cast<int>(cudaGetLastError());
@@ -859,7 +861,7 @@ int rope_qk(const void* in, void* out, const float* cos_t, const float* sin_t, i
   if (total == 0) return 0;
   // few tokens: too little parallelism with one thread per 8-channel column; head dims that are not a
   // multiple of 128 (ViT: 80): a token's threads would read 80-byte pieces
-  if (total < 148 * 256 || D % 128 != 0) {
+  if (total < static_cast<long>(sm_count()) * 256 || D % 128 != 0) {
     const long per_row = static_cast<long>(n_rot) * (D / 16) + (W - n_rot * D) / 8;
     rope_qk_chunk_kernel<<<static_cast<unsigned>((per_row * T + 255) / 256), 256, 0, s>>>(
         reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(out), cos_t, sin_t, T, W, n_rot, D,
@@ -881,7 +883,7 @@ int route_plan(const int* types, int T, int E, int rows, int* dest, int* seg, in
 int permute_rows(const void* x, const int* dest, void* out, int T, int C, cudaStream_t s) {
   if (C % 8 != 0) return -1;
   if (T == 0) return 0;
-  permute_rows_kernel<<<T < 148 * 16 ? T : 148 * 16, 128, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), dest,
+  permute_rows_kernel<<<T < sm_count() * 16 ? T : sm_count() * 16, 128, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), dest,
                                                                   reinterpret_cast<__nv_bfloat16*>(out), T, C);
   return static_cast<int>(cudaGetLastError());
 }
@@ -889,7 +891,7 @@ int permute_rows(const void* x, const int* dest, void* out, int T, int C, cudaSt
 int gather_rows(const void* x, const int* idx, void* out, int T, int C, cudaStream_t s) {
   if (C % 8 != 0) return -1;
   if (T == 0) return 0;
-  gather_rows_kernel<<<T < 148 * 16 ? T : 148 * 16, 128, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), idx,
+  gather_rows_kernel<<<T < sm_count() * 16 ? T : sm_count() * 16, 128, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), idx,
                                                                  reinterpret_cast<__nv_bfloat16*>(out), T, C);
   return static_cast<int>(cudaGetLastError());
 }
@@ -934,7 +936,7 @@ int ce_bwd(void* logits, const long* labels, const float* lse, const float* dlos
 
 int sumsq_bf16(const void* g, long n, float* out, cudaStream_t s) {
   if (n == 0) return 0;
-  sumsq_bf16_kernel<<<blocks_for(n / 8 + 1, 256, 148 * 8), 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(g), n,
+  sumsq_bf16_kernel<<<blocks_for(n / 8 + 1, 256, sm_count() * 8 < kSumsqMaxBlocks ? sm_count() * 8 : kSumsqMaxBlocks), 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(g), n,
                                                                         out);
   return static_cast<int>(cudaGetLastError());
 }
@@ -942,7 +944,7 @@ int sumsq_bf16(const void* g, long n, float* out, cudaStream_t s) {
 int adamw_step(void* p16, float* p32, float* m, float* v, const void* g, long n, const float* hyper,
                const float* norm_sq, cudaStream_t s) {
   if (n == 0) return 0;
-  adamw_kernel<<<blocks_for(n, 256, 148 * 16), 256, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(p16), p32, m, v,
+  adamw_kernel<<<blocks_for(n, 256, sm_count() * 16), 256, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(p16), p32, m, v,
                                                             reinterpret_cast<const __nv_bfloat16*>(g), n, hyper,
                                                             norm_sq, nullptr);
   return static_cast<int>(cudaGetLastError());

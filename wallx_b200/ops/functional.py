@@ -33,28 +33,63 @@ def _C():
 # Gradient sinks: when a weight lives in a flat gradient buffer, its weight-gradient GEMM adds
 # straight into that buffer (GEMM epilogue with the accumulate flag) instead of producing a
 # temporary that autograd then adds: one kernel and one pass over the gradient less per weight.
-# Keyed by the weight's data pointer; the value is (gradient view, callback marking it as used).
-_GRAD_SINKS = {}
+# The sink is an attribute of the parameter object: ``(gradient view, callback, data pointer at
+# registration)``. Row-sharded parameters share a staging buffer, so an address cannot name them;
+# for them the pointer entry is None.
+_SINK_OWNERS = None
 
 
 def register_grad_sink(weight: torch.Tensor, grad_view: torch.Tensor, mark) -> None:
     import weakref
 
-    _GRAD_SINKS[weight.data_ptr()] = (grad_view, mark, weakref.ref(weight))
+    global _SINK_OWNERS
+    if _SINK_OWNERS is None:
+        _SINK_OWNERS = weakref.WeakSet()
+    weight._wx_sink = (grad_view, mark, weight.data_ptr())
+    _SINK_OWNERS.add(weight)
 
 
 def _sink_of(w: torch.Tensor):
-    s = _GRAD_SINKS.get(w.data_ptr())
+    s = getattr(w, "_wx_sink", None)
     if s is None:
         return None
-    owner = s[2]()
-    if owner is None or owner.data_ptr() != w.data_ptr() or s[0].shape != w.shape or not _pitch_ok(s[0]):
+    moved = getattr(w, "_wx_shard", None) is None and s[2] != w.data_ptr()  # .to() / .data re-pointed since registration
+    if moved or s[0].shape != w.shape or s[0].device != w.device or not _pitch_ok(s[0]):
         return None
     return s
 
 
 def clear_grad_sinks() -> None:
-    _GRAD_SINKS.clear()
+    if _SINK_OWNERS is not None:
+        for w in list(_SINK_OWNERS):
+            if hasattr(w, "_wx_sink"):
+                del w._wx_sink
+        _SINK_OWNERS.clear()
+
+
+def _shard_of(w: torch.Tensor):
+    """The fused-gather record of a row-sharded weight (``parallel/zero3.py``), or None for a resident one."""
+    return getattr(w, "_wx_shard", None)
+
+
+def _launch(specs, weights) -> None:
+    """Launch one or two problems whose B operands are ``weights``. Resident weights take the plain GEMM; a
+    row-sharded weight is gathered from its owners inside the launch (two sharded weights share a launch when
+    they sit in different staging slots)."""
+    shards = [_shard_of(w) for w in weights]
+    if all(s is None for s in shards):
+        G.launch(specs)
+        return
+    from ..parallel.ag_linear import ag_launch
+
+    if all(s is not None for s in shards) and (len(shards) == 1 or shards[0].slot != shards[1].slot):
+        ag_launch(specs, shards)
+        return
+    for spec, s in zip(specs, shards):
+        if s is None:
+            G.launch([spec])
+        else:
+            ag_launch([spec], [s])
 
 
 def _wgrad(a: torch.Tensor, b: torch.Tensor, w: torch.Tensor, **spec_kw):
@@ -92,7 +127,7 @@ class _LinearFn(torch.autograd.Function):
         x2 = _aligned2d(x)
         w2 = _aligned2d(w)
         out = torch.empty((x.shape[0], w.shape[0]), device=x.device, dtype=torch.bfloat16)
-        G.launch([G.GemmSpec(x2, w2, out, bias=b, residual=residual)])
+        _launch([G.GemmSpec(x2, w2, out, bias=b, residual=residual)], [w2])
         ctx.save_for_backward(x, w)
         ctx.has_bias = b is not None
         ctx.has_res = residual is not None
@@ -107,7 +142,8 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = torch.empty_like(x)
             # dx[m, k] = sum_n dy[m, n] w[n, k]: B(n'=k, k'=n) is w read as MN-major
-            G.launch([G.GemmSpec(dy2, _aligned2d(w), dx, b_mn=True)])
+            w2 = _aligned2d(w)
+            _launch([G.GemmSpec(dy2, w2, dx, b_mn=True)], [w2])
         if ctx.needs_input_grad[1]:
             # dw[n, k] = sum_m dy[m, n] x[m, k]: both operands MN-major over the token axis
             dw = _wgrad(dy2, _aligned2d(x), w)
@@ -149,7 +185,8 @@ def linear_gelu(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor]) -> 
     if _is_cuda(x) and not (torch.is_grad_enabled() and (x.requires_grad or w.requires_grad)):
         x2 = _aligned2d(x.reshape(-1, x.shape[-1]))
         out = torch.empty((x2.shape[0], w.shape[0]), device=x.device, dtype=torch.bfloat16)
-        G.launch([G.GemmSpec(x2, _aligned2d(w), out, bias=b, flags=G.ACT_GELU)])
+        w2 = _aligned2d(w)
+        _launch([G.GemmSpec(x2, w2, out, bias=b, flags=G.ACT_GELU)], [w2])
         return out.reshape(*x.shape[:-1], w.shape[0])
     return torch.nn.functional.gelu(linear(x, w, b))
 
@@ -200,7 +237,7 @@ class _GateUpFn(torch.autograd.Function):
         # the raw gate/up values are only needed by the backward pass
         gu = torch.empty((M, N), device=x.device, dtype=torch.bfloat16) if any(ctx.needs_input_grad) else None
         h = torch.empty((M, N // 2), device=x.device, dtype=torch.bfloat16)
-        G.launch([G.GemmSpec(x, w_gu, h, out2=gu, bias=b_gu, flags=G.ACT_SWIGLU)])
+        _launch([G.GemmSpec(x, w_gu, h, out2=gu, bias=b_gu, flags=G.ACT_SWIGLU)], [w_gu])
         if gu is not None:
             ctx.save_for_backward(x, w_gu, gu)
         ctx.has_bias = b_gu is not None
@@ -213,7 +250,7 @@ class _GateUpFn(torch.autograd.Function):
         dx = dw = db = None
         if ctx.needs_input_grad[0]:
             dx = torch.empty_like(x)
-            G.launch([G.GemmSpec(dgu, w_gu, dx, b_mn=True)])
+            _launch([G.GemmSpec(dgu, w_gu, dx, b_mn=True)], [w_gu])
         if ctx.needs_input_grad[1]:
             dw = _wgrad(dgu, x, w_gu)
         if ctx.has_bias and ctx.needs_input_grad[2]:
@@ -238,9 +275,9 @@ class _SwiGLUFfnFn(torch.autograd.Function):
         need_bwd = any(ctx.needs_input_grad)
         gu = torch.empty((M, N), device=x.device, dtype=torch.bfloat16) if need_bwd else None
         h = torch.empty((M, N // 2), device=x.device, dtype=torch.bfloat16)
-        G.launch([G.GemmSpec(x, w_gu, h, out2=gu, bias=b_gu, flags=G.ACT_SWIGLU)])
+        _launch([G.GemmSpec(x, w_gu, h, out2=gu, bias=b_gu, flags=G.ACT_SWIGLU)], [w_gu])
         out = torch.empty((M, w_dn.shape[0]), device=x.device, dtype=torch.bfloat16)
-        G.launch([G.GemmSpec(h, w_dn, out, bias=b_dn, residual=residual)])
+        _launch([G.GemmSpec(h, w_dn, out, bias=b_dn, residual=residual)], [w_dn])
         if need_bwd:
             ctx.save_for_backward(x, w_gu, w_dn, gu, h)
         ctx.has_bgu, ctx.has_bdn, ctx.has_res = b_gu is not None, b_dn is not None, residual is not None
@@ -253,10 +290,10 @@ class _SwiGLUFfnFn(torch.autograd.Function):
         if FUSE_SWIGLU_BWD:
             dgu = torch.empty_like(gu)
             # dL/dh = dy @ w_dn, turned into dL/d(gate|up) in the epilogue
-            G.launch([G.GemmSpec(dy, w_dn, dgu, b_mn=True, out2=gu, flags=G.SWIGLU_BWD)])
+            _launch([G.GemmSpec(dy, w_dn, dgu, b_mn=True, out2=gu, flags=G.SWIGLU_BWD)], [w_dn])
         else:
             dh = torch.empty_like(h)
-            G.launch([G.GemmSpec(dy, w_dn, dh, b_mn=True)])
+            _launch([G.GemmSpec(dy, w_dn, dh, b_mn=True)], [w_dn])
             dgu = _C().swiglu_bwd(dh, gu)
         dx = dw_gu = db_gu = dw_dn = db_dn = dres = None
         if ctx.needs_input_grad[3]:
@@ -265,7 +302,7 @@ class _SwiGLUFfnFn(torch.autograd.Function):
             db_dn = column_sum(dy)
         if ctx.needs_input_grad[0]:
             dx = torch.empty_like(x)
-            G.launch([G.GemmSpec(dgu, w_gu, dx, b_mn=True)])
+            _launch([G.GemmSpec(dgu, w_gu, dx, b_mn=True)], [w_gu])
         if ctx.needs_input_grad[1]:
             dw_gu = _wgrad(dgu, x, w_gu)
         if ctx.has_bgu and ctx.needs_input_grad[2]:
@@ -361,14 +398,14 @@ class _MoeFfnFn(torch.autograd.Function):
         specs = [G.GemmSpec(xp, weights[2 * e], h, out2=gu, M=rows, dyn=seg[e],
                             flags=G.ACT_SWIGLU | G.ZERO_PAD_ROWS) for e in range(n_exp)]
         for i in range(0, n_exp, 2):
-            G.launch(specs[i:i + 2])
+            _launch(specs[i:i + 2], [weights[2 * e] for e in range(i, min(i + 2, n_exp))])
         specs = []
         for e in range(n_exp):
             w_dn = weights[2 * e + 1]
             specs.append(G.GemmSpec(h[:, : w_dn.shape[1]], w_dn, out, M=rows, dyn=seg[e], row_map=inv,
                                     residual=residual))
         for i in range(0, n_exp, 2):
-            G.launch(specs[i:i + 2])
+            _launch(specs[i:i + 2], [weights[2 * e + 1] for e in range(i, min(i + 2, n_exp))])
         if gu is not None:
             ctx.save_for_backward(xp, dest, seg, segk, gu, h, *weights)
         ctx.n_exp = n_exp
@@ -392,7 +429,7 @@ class _MoeFfnFn(torch.autograd.Function):
                 specs.append(G.GemmSpec(dyp, w_dn, dgu, M=rows, dyn=seg[e], b_mn=True, out2=gu,
                                         flags=G.SWIGLU_BWD | G.ZERO_PAD_ROWS))
             for i in range(0, n_exp, 2):
-                G.launch(specs[i:i + 2])
+                _launch(specs[i:i + 2], [weights[2 * e + 1] for e in range(i, min(i + 2, n_exp))])
         else:
             dh = torch.empty((rows, wmax // 2), device=xp.device, dtype=torch.bfloat16)
             for e in range(n_exp):
@@ -400,17 +437,18 @@ class _MoeFfnFn(torch.autograd.Function):
                 specs.append(G.GemmSpec(dyp, w_dn, dh[:, : w_dn.shape[1]], M=rows, dyn=seg[e], b_mn=True,
                                         flags=G.ZERO_PAD_ROWS))
             for i in range(0, n_exp, 2):
-                G.launch(specs[i:i + 2])
+                _launch(specs[i:i + 2], [weights[2 * e + 1] for e in range(i, min(i + 2, n_exp))])
             dgu = _C().swiglu_bwd(dh, gu)
         grads = [None] * (2 * n_exp)
         specs = []
+        marks = []  # sink callbacks run once the GEMM that adds into the sink has been enqueued
         for e in range(n_exp):
             w_dn = weights[2 * e + 1]
             I = w_dn.shape[1]
             sink = _sink_of(w_dn)
             if sink is not None:  # accumulate straight into the flat gradient buffer
                 dw, fl = sink[0], G.ACCUMULATE
-                sink[1]()
+                marks.append(sink[1])
             else:
                 dw, fl = torch.zeros_like(w_dn), 0  # stays zero when the expert has no tokens
                 grads[2 * e + 1] = dw
@@ -418,27 +456,32 @@ class _MoeFfnFn(torch.autograd.Function):
             specs.append(G.GemmSpec(dyp, h[:, :I], dw, a_mn=True, b_mn=True, M=H, N=I, K=rows, dyn=segk[e], flags=fl))
         for i in range(0, n_exp, 2):
             G.launch(specs[i:i + 2])
+        for mark in marks:
+            mark()
         dxp = torch.empty((rows, H), device=xp.device, dtype=torch.bfloat16)
         specs = []
         for e in range(n_exp):
             w_gu = weights[2 * e]
             specs.append(G.GemmSpec(dgu[:, : w_gu.shape[0]], w_gu, dxp, M=rows, dyn=seg[e], b_mn=True))
         for i in range(0, n_exp, 2):
-            G.launch(specs[i:i + 2])
+            _launch(specs[i:i + 2], [weights[2 * e] for e in range(i, min(i + 2, n_exp))])
         specs = []
+        marks = []
         for e in range(n_exp):
             w_gu = weights[2 * e]
             W = w_gu.shape[0]
             sink = _sink_of(w_gu)
             if sink is not None:
                 dw, fl = sink[0], G.ACCUMULATE
-                sink[1]()
+                marks.append(sink[1])
             else:
                 dw, fl = torch.zeros_like(w_gu), 0
                 grads[2 * e] = dw
             specs.append(G.GemmSpec(dgu[:, :W], xp, dw, a_mn=True, b_mn=True, M=W, N=H, K=rows, dyn=segk[e], flags=fl))
         for i in range(0, n_exp, 2):
             G.launch(specs[i:i + 2])
+        for mark in marks:
+            mark()
         dres = dout if ctx.has_res else None
         return (dxp, dres, None, None, None, None, None, *grads)
 

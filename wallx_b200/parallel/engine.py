@@ -13,6 +13,15 @@ resident parameter copy.
 Transports: ``"local"`` (one rank), ``"dist"`` (torch.distributed collectives: NCCL on GPUs, gloo
 on CPU -- the plain baseline and the CPU test path), ``"symm"`` (hand-written peer-memory kernels
 over NVLink, :mod:`wallx_b200.parallel.symm`).
+
+Two parameter plans. Resident (default): every rank keeps all bf16 parameters, only the fp32 master
+weights and Adam moments are sharded (ZeRO-1/2), and the updated shard is pushed to the peers after
+AdamW. ``shard_params=True`` (ZeRO-3, the reference's ``FSDP2: True`` with ``reshard_after_forward``,
+train_qact.py:42-49): the 2-D weights of every decoder layer and vision block are stored as rows per
+rank (:mod:`wallx_b200.parallel.zero3`); on the NVLink transport the forward and dgrad GEMMs pull the
+peers' rows inside the kernel, the wgrad GEMMs write a local bf16 gradient that each rank reduces for
+its rows, and AdamW updates the owner's rows in place -- no all-gather or push of those weights exists
+as a separate step.
 """
 from __future__ import annotations
 
@@ -21,8 +30,11 @@ from typing import Callable, Dict, List, Optional, Tuple
 import torch
 import torch.nn as nn
 
+import contextlib
+
 from ..train.optim import FlatAdamW
 from .flat import FlatBuffer
+from .zero3 import GatherWorkspace, RowShardedBuffer, zero3_units
 
 
 def default_units(model: nn.Module) -> List[Tuple[str, List[Tuple[str, nn.Parameter]]]]:
@@ -55,28 +67,58 @@ class TrainEngine:
     def __init__(self, model: nn.Module, lr: float, weight_decay: float = 0.1, betas=(0.9, 0.999), eps: float = 1e-8,
                  max_grad_norm: float = 1.0, grad_accum: int = 1, world: int = 1, rank: int = 0,
                  transport: str = "local", group=None, param_group_fn: Optional[Callable[[str], Tuple[str, float, float]]] = None,
-                 master_dtype=torch.float32, symm=None):
+                 master_dtype=torch.float32, symm=None, shard_params: bool = False):
         self.model = model
         self.world, self.rank = world, rank
         self.transport = transport if world > 1 else "local"
         self.group = group
         self.symm = symm
         self.grad_accum = grad_accum
+        self.shard_params = bool(shard_params)
         pg = param_group_fn or (lambda name: ("default", 1.0, weight_decay))
         self.buffers: List[FlatBuffer] = []
-        units = default_units(model)
+        if self.shard_params:
+            units = zero3_units(model, world)
+        else:
+            units = [(n, ps, "flat") for n, ps in default_units(model)]
         alloc = None
+        align = FlatBuffer.ALIGN * world
         if self.transport == "symm" and symm is not None:
-            align = FlatBuffer.ALIGN * world
-            total = sum((sum(p.numel() for _, p in ps) + align - 1) // align * align for _, ps in units)
-            symm.reserve(total, dtype=units[0][1][0][1].dtype)
+            p_total = g_total = 0
+            for _, ps, kind in units:
+                if kind == "rows":
+                    a, b = RowShardedBuffer.sizes([p for _, p in ps], world)
+                else:
+                    a = b = (sum(p.numel() for _, p in ps) + align - 1) // align * align
+                p_total += a
+                g_total += b
+            symm.reserve(p_total, dtype=units[0][1][0][1].dtype, grad_elems=g_total)
             alloc = (symm.alloc_param, symm.alloc_grad)
-        for uname, ps in units:
+        row_mode = "gathered" if self.transport == "symm" else "materialized"
+        for uname, ps, kind in units:
             groups = [pg(n) for n, _ in ps]
-            self.buffers.append(FlatBuffer(ps, world, rank, groups, name=uname, alloc=alloc, master_dtype=master_dtype))
+            if kind == "rows":
+                self.buffers.append(RowShardedBuffer(ps, world, rank, groups, name=uname, alloc=alloc,
+                                                     master_dtype=master_dtype, mode=row_mode))
+            else:
+                self.buffers.append(FlatBuffer(ps, world, rank, groups, name=uname, alloc=alloc, master_dtype=master_dtype))
+        self.workspace = None
+        rows_units = [b for b in self.buffers if b.kind == "rows" and b.mode == "gathered"]
+        if rows_units:  # NVLink mode: two staging slots for the weight a GEMM is gathering (two for a dual-expert launch)
+            dev = rows_units[0].device
+            biggest = max(R * C for b in rows_units for R, C in b.shapes)
+            self.workspace = GatherWorkspace(biggest, dev, slots=2, dtype=rows_units[0].dtype)
+            self._ag_flags = torch.zeros(sum(b.flag_words() for b in rows_units), dtype=torch.int32, device=dev)
+            ebytes = symm.param_arena.element_size()
+            used = 0
+            for b in rows_units:
+                off = b.param.data_ptr() - symm.param_arena.data_ptr()
+                assert off % ebytes == 0
+                used += b.attach_gather([p + off for p in symm.param_ptrs], self.workspace, self._ag_flags[used:])
         self.optimizer = FlatAdamW(self.buffers, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
                                    max_grad_norm=max_grad_norm, grad_accum=grad_accum * world)
         self.last_norm_sq: Optional[torch.Tensor] = None
+        self.last_bad: Optional[torch.Tensor] = None  # device float: some rank's device-side wait ran out in the last step
         # ranks agree on which parameters were used unless batches differ in modality; the merge
         # costs one host read per step, so it can be switched off for homogeneous data
         self.check_touched = True
@@ -121,14 +163,21 @@ class TrainEngine:
             if not self._learned and self._order:
                 for k, order in self._order.items():
                     self._expected[k] = len({i for i, _ in order})
-                    last_i, last_kind = order[-1]
-                    self._trigger[k] = last_i if last_kind == "accumulate" else None
+                    self._trigger[k] = tuple(order[-1])
                 self._learned = True
             return self.symm.grad_shards()
         import torch.distributed as dist
 
         shards = []
         for b in reversed(self.buffers):
+            if b.kind == "rows":  # whole-gradient all-reduce, then this rank's rows of every weight
+                tmp = b.grad if b.grad.is_cuda else b.grad.float()
+                dist.all_reduce(tmp, op=dist.ReduceOp.SUM, group=self.group)
+                out = torch.zeros(b.shard_size, device=b.device, dtype=b.grad.dtype)
+                for goff, n, ooff in b.rs_segments():
+                    out[ooff:ooff + n] = tmp[goff:goff + n].to(out.dtype)
+                shards.append(out)
+                continue
             out = torch.empty(b.shard_size, device=b.device, dtype=b.grad.dtype)
             if b.grad.is_cuda:
                 dist.reduce_scatter_tensor(out, b.grad, op=dist.ReduceOp.SUM, group=self.group)
@@ -148,6 +197,11 @@ class TrainEngine:
         import torch.distributed as dist
 
         for b in self.buffers:
+            if b.kind == "rows":  # materialized mode: refresh the whole parameters from the owners' rows
+                with torch.no_grad():
+                    for i, p in enumerate(b.params):
+                        p.data.copy_(b.gather_full(i, self.group).to(p.dtype))
+                continue
             s0, s1 = b.shard_range
             if b.param.is_cuda:
                 dist.all_gather_into_tensor(b.param, b.param[s0:s1].clone(), group=self.group)
@@ -182,8 +236,16 @@ class TrainEngine:
         if shards is None:
             return opt.local_grad_sumsq(shard_only=False)
         if self.transport == "symm":  # the reduce-scatter kernel already summed the squares of its shard
-            opt.norm_sq.copy_(self.symm.local_sumsq)
-            return self.symm.all_reduce_scalar(opt.norm_sq)
+            bad = self._local_bad()
+            if bad is None:
+                opt.norm_sq.copy_(self.symm.local_sumsq)
+                return self.symm.all_reduce_scalar(opt.norm_sq)
+            # the same small all-reduce carries "a bounded wait ran out on some rank": every rank then sees a
+            # non-finite norm, which makes the AdamW kernel skip the update on all ranks alike
+            v = self.symm.all_reduce_vector(torch.cat([self.symm.local_sumsq.reshape(1), bad.reshape(1)]))
+            self.last_bad = v[1:2]
+            opt.norm_sq.copy_(torch.where(v[1:2] > 0, torch.full_like(v[0:1], float("nan")), v[0:1]))
+            return opt.norm_sq
         opt.norm_sq.zero_()
         for g in shards:
             if g.is_cuda and g.dtype == torch.bfloat16:
@@ -207,8 +269,8 @@ class TrainEngine:
             return
         seen = self._seen.setdefault(k, set())
         seen.add(i)
-        if kind == "accumulate" and self._trigger.get(k) == i and len(seen) == self._expected.get(k, -1) \
-                and k not in self._early:
+        # both kinds fire after the kernel that produces the gradient was enqueued on the current stream
+        if self._trigger.get(k) == (i, kind) and len(seen) == self._expected.get(k, -1) and k not in self._early:
             self._early_reduce(k)
 
     def _early_reduce(self, k: int) -> None:
@@ -222,10 +284,20 @@ class TrainEngine:
             self.symm.reduce_scatter_unit(k)
         self._early.add(k)
 
-    def backward(self, loss: torch.Tensor) -> None:
+    def backward(self, loss: torch.Tensor, last: Optional[bool] = None) -> None:
+        """Backward of one micro-batch. ``last`` says whether the optimizer step follows (its gradients are then
+        final and units may be reduced while backward still runs); None = the ``grad_accum``-th micro-batch since the
+        last step. A caller whose accumulation can end early (end of an epoch) passes it explicitly."""
         self._micro += 1
         overlap = self.overlap_reduce and self.transport == "symm"
-        if overlap and self._micro == self.grad_accum:  # last micro-step: gradients become final
+        if last is None:
+            last = self._micro == self.grad_accum
+        if self._step_begun:
+            # units were already reduced for this step and another backward arrives (the caller announced the last
+            # micro-batch too early): their gradients change again, so every unit is reduced again after backward
+            self._step_begun = False
+            self._early = set()
+        if overlap and last:
             self.symm.begin_step()
             self._step_begun = True
             self._armed = True
@@ -234,28 +306,120 @@ class TrainEngine:
         loss.backward()
         self._armed = False
 
+    def _local_bad(self) -> Optional[torch.Tensor]:
+        """Device float, 1.0 when one of this rank's bounded device-side waits ran out since the last host check
+        (a peer stalled past the barrier limit, a GEMM gave up on an mbarrier or a gathered tile)."""
+        dev = self.buffers[0].device
+        if dev.type != "cuda":
+            return None
+        flags = []
+        st = getattr(self.symm, "status", None) if self.symm is not None else None
+        if st is not None:
+            flags.append(st[:1] != 0)
+        from ..ops import _ext
+
+        C = _ext.get(required=False)
+        if C is not None and hasattr(C, "status_tensor"):
+            flags.append(C.status_tensor(dev.index or 0)[:1] != 0)
+        if not flags:
+            return None
+        bad = flags[0]
+        for f in flags[1:]:
+            bad = bad | f
+        return bad.float()
+
+    def check_status(self) -> None:
+        """Host check (synchronises): raise if any rank's device-side wait ran out in a step since the last check.
+        Such a step was skipped on every rank (non-finite norm), so parameters are intact and ranks agree."""
+        bad = self.last_bad
+        if bad is not None and float(bad.item()) > 0:
+            self.last_bad = None
+            if self.symm is not None and hasattr(self.symm, "status"):
+                self.symm.status.zero_()
+            from ..ops import gemm as G
+
+            try:
+                G.check_status(self.buffers[0].device)
+            except RuntimeError:
+                pass
+            raise RuntimeError("a device-side wait timed out on some rank (stalled or failed peer); the affected "
+                               "optimizer step was skipped on every rank")
+
     def optimizer_step(self, lr: float) -> torch.Tensor:
         """Reduce gradients, clip by global norm, update shards, refresh parameters, clear grads.
-        Returns the squared global gradient norm *before* scaling by 1/(accum*world) (device)."""
+        Returns the squared global gradient norm *before* scaling by 1/(accum*world) (device).
+        The gradient is averaged over the micro-batches actually accumulated since the last step."""
         if self.check_touched:
             self._merge_touched()
+        if self._micro > 0:
+            self.optimizer.grad_accum = self._micro * self.world
+        self._last_micro = self._micro or self.grad_accum
         shards = self._reduce_scatter()
         norm_sq = self._global_norm_sq(shards)
+        if self.transport != "symm":
+            bad = self._local_bad()
+            if bad is not None:
+                norm_sq.copy_(torch.where(bad > 0, torch.full_like(norm_sq, float("nan")), norm_sq))
+                self.last_bad = bad
         self.optimizer.step(lr=lr, norm_sq=norm_sq, grad_shards=shards)
         self._all_gather_params()
         self.optimizer.zero_grad()
         self._micro = 0
+        self._step_begun = False
         self.last_norm_sq = norm_sq
         return norm_sq
 
     def grad_norm(self) -> torch.Tensor:
         """Global gradient norm of the last step in the units of the averaged gradient."""
-        return self.last_norm_sq.sqrt() / float(self.grad_accum * self.world)
+        return self.last_norm_sq.sqrt() / float(getattr(self, "_last_micro", self.grad_accum) * self.world)
+
+    # ------------------------------------------------------------------ whole parameters of a sharded model
+    @contextlib.contextmanager
+    def gathered_parameters(self, writeback: bool = False):
+        """Inside the block every row-sharded parameter holds its whole, current value (checkpoint export,
+        ``state_dict()``, graph-captured inference). Collective: every rank must enter. With ``writeback`` the
+        values found at exit (e.g. after ``load_state_dict``) replace the owners' rows and their fp32 masters, and
+        the resident flat buffers' masters are refreshed too."""
+        swapped = []
+        for b in self.buffers:
+            if b.kind != "rows":
+                continue
+            if b.mode == "gathered":
+                for i, p in enumerate(b.params):
+                    swapped.append((b, i, p, p.data))
+                    p.data = b.gather_full(i, self.group)
+            elif b.mode == "materialized" and not writeback:
+                pass  # the whole parameters are kept current after every step
+        try:
+            yield self
+        finally:
+            with torch.no_grad():
+                if writeback:
+                    for b in self.buffers:
+                        if b.kind == "rows":
+                            for i, p in enumerate(b.params):
+                                b.load_rows_from_full(i, p.data)
+                for b, i, p, old in swapped:
+                    p.data = old
+                if writeback:
+                    self.refresh_master()
+
+    def refresh_master(self) -> None:
+        """fp32 master shards := current bf16 parameter shards (after loading weights into the model)."""
+        for b in self.buffers:
+            s0, s1 = b.shard_range
+            b.master.copy_(b.param[s0:s1].to(b.master.dtype))
 
     # ------------------------------------------------------------------ state
     def optimizer_state(self) -> Dict:
-        return {"opt": self.optimizer.state_dict(), "world": self.world, "rank": self.rank,
-                "layout": [(b.name, b.numel, b.padded, list(zip(b.names, b.offsets))) for b in self.buffers]}
+        layout = []
+        for b in self.buffers:
+            if b.kind == "rows":
+                layout.append((b.name, b.numel, b.shard_size, list(zip(b.names, b.offsets)), "rows", list(b.shapes)))
+            else:
+                layout.append((b.name, b.numel, b.padded, list(zip(b.names, b.offsets)), "flat",
+                               [tuple(p.shape) for p in b.params]))
+        return {"opt": self.optimizer.state_dict(), "world": self.world, "rank": self.rank, "layout": layout}
 
     def load_optimizer_state(self, sd: Dict) -> None:
         self.optimizer.load_state_dict(sd["opt"])

@@ -35,6 +35,7 @@ class FlatBuffer:
     this rank's shard of the optimizer state."""
 
     ALIGN = 1024  # elements; keeps every shard 2 KB aligned for vector and bulk accesses
+    kind = "flat"
 
     def __init__(self, named_params: Sequence[Tuple[str, nn.Parameter]], world: int = 1, rank: int = 0,
                  groups: Optional[Sequence[Tuple[str, float, float]]] = None, name: str = "",
@@ -100,7 +101,7 @@ class FlatBuffer:
 
     def _make_hook(self, i: int, kind: str = "accumulate"):
         # kind "accumulate": fired by autograd after the gradient kernel was enqueued; kind "sink":
-        # fired just before the weight-gradient GEMM that writes into the flat buffer is enqueued
+        # fired right after the weight-gradient GEMM that adds into the flat buffer was enqueued
         def hook(_p=None):
             self.touched[i] = True
             cb = self.on_touch
@@ -156,3 +157,12 @@ class FlatBuffer:
 
     def state_dict(self) -> Dict[str, torch.Tensor]:
         return {"master": self.master, "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq}
+
+    # ------------------------------------------------------------------ transport tables
+    def rs_segments(self) -> List[Tuple[int, int, int]]:
+        """``(offset in the gradient buffer, length, offset in the shard)`` of the pieces this rank reduces."""
+        return [(self.shard_range[0], self.shard_size, 0)]
+
+    def push_segments(self) -> List[Tuple[int, int]]:
+        """``(offset in the parameter buffer, length)`` of what this rank writes into the peers' copies."""
+        return [(self.shard_range[0], self.shard_size)]

@@ -22,12 +22,17 @@ import torch
 from ..ops import _ext
 
 MAX_VEC = 4096  # floats per rank in the small all-reduce scratch
-FLAG_WORDS = 8 * 128  # int32 flag slots: 8 for the global barrier, then 8 per unit (up to 127 units)
+FLAG_WORDS = 8 * 256  # int32 flag slots: 8 for the global barrier, then 8 per unit (up to 255 units)
 
 
 class SymmComm:
-    def __init__(self, group, device):
+    def __init__(self, group, device, barrier_timeout_s: float = 30.0):
+        """``barrier_timeout_s`` bounds every wait on a peer (clamped to 10 min by the kernel). Ranks are not
+        synchronised by the host, so the limit has to cover the longest time one rank may lag behind another
+        between two barriers (a data-loader stall, a first-step lazy initialisation), not just network latency."""
         import torch.distributed as dist
+
+        self.timeout_ms = max(1, int(barrier_timeout_s * 1000))
         import torch.distributed._symmetric_memory as symm_mem
 
         self.symm_mem = symm_mem
@@ -55,10 +60,12 @@ class SymmComm:
         dist.barrier(group)
 
     # ------------------------------------------------------------------ allocation
-    def reserve(self, total_elems: int, dtype=torch.bfloat16) -> None:
+    def reserve(self, total_elems: int, dtype=torch.bfloat16, grad_elems: int = 0) -> None:
+        """Allocate the two arenas. With row-sharded parameters the parameter arena holds shards and the gradient
+        arena whole gradients, so their sizes differ (``grad_elems``)."""
         sm = self.symm_mem
         self.param_arena = sm.empty(total_elems, dtype=dtype, device=self.device)
-        self.grad_arena = sm.empty(total_elems, dtype=dtype, device=self.device)
+        self.grad_arena = sm.empty(grad_elems or total_elems, dtype=dtype, device=self.device)
         self.param_arena.zero_()
         self.grad_arena.zero_()
         self.param_ptrs = [int(p) for p in sm.rendezvous(self.param_arena, self.group).buffer_ptrs]
@@ -83,22 +90,32 @@ class SymmComm:
         return self._take("grad", n, dtype)
 
     def register_buffers(self, buffers) -> None:
-        rows, out_off = [], 0
+        """Build the device tables: per unit the pieces of the gradient arena this rank reduces (one for a flat
+        buffer, one per weight for a row-sharded unit) and the pieces of the parameter arena it pushes to its peers
+        (none for row-sharded units: their rows are read in place by the peers' GEMMs)."""
+        rows, push, out_off = [], [], 0
         elem = self.param_arena.element_size()
-        base = self.param_arena.data_ptr()
-        self.views = []
+        pbase, gbase = self.param_arena.data_ptr(), self.grad_arena.data_ptr()
+        self.views, self.unit_rows = [], []
         for b in buffers:
-            arena_off = (b.param.data_ptr() - base) // elem + self.rank * b.shard_size
-            rows.append([arena_off, b.shard_size, out_off])
+            g0 = (b.grad.data_ptr() - gbase) // elem
+            p0 = (b.param.data_ptr() - pbase) // elem
+            first = len(rows)
+            for goff, n, ooff in b.rs_segments():
+                rows.append([g0 + goff, n, out_off + ooff])
+            self.unit_rows.append((first, len(rows)))
+            for poff, n in b.push_segments():
+                push.append([p0 + poff, n, 0])
             self.views.append((out_off, b.shard_size))
             out_off += b.shard_size
-        self.table = torch.tensor(rows, dtype=torch.int64, device=self.device)
+        self.table = torch.tensor(rows, dtype=torch.int64, device=self.device).reshape(-1, 3)
+        self.push_table = torch.tensor(push, dtype=torch.int64, device=self.device).reshape(-1, 3)
         self.gshard = torch.zeros(out_off, dtype=torch.float32, device=self.device)
 
     # ------------------------------------------------------------------ collectives
     def barrier(self) -> None:
         self.epoch += 1
-        _ext.get().symm_barrier(self.flag_ptrs, self.rank, self.epoch, self.status)
+        _ext.get().symm_barrier(self.flag_ptrs, self.rank, self.epoch, self.status, self.timeout_ms)
 
     def check(self) -> None:
         """Raise if a barrier wait ran out (a peer died or stalled); synchronises."""
@@ -126,8 +143,9 @@ class SymmComm:
         if 8 * (k + 2) > FLAG_WORDS:
             raise ValueError("too many units for the per-unit flag block")
         C = _ext.get()
-        C.symm_barrier([p + 32 * (k + 1) for p in self.flag_ptrs], self.rank, self.unit_step, self.status)
-        C.rs_reduce(self.grad_ptrs, self.table[k:k + 1], self.gshard, self.local_sumsq)
+        C.symm_barrier([p + 32 * (k + 1) for p in self.flag_ptrs], self.rank, self.unit_step, self.status, self.timeout_ms)
+        a, b = self.unit_rows[k]
+        C.rs_reduce(self.grad_ptrs, self.table[a:b], self.gshard, self.local_sumsq)
 
     def grad_shards(self) -> List[torch.Tensor]:
         return [self.gshard[o:o + n] for o, n in self.views]
@@ -149,5 +167,7 @@ class SymmComm:
         return t
 
     def all_gather_params(self, buffers) -> None:
-        _ext.get().ag_push(self.param_ptrs, self.table, self.rank)
-        self.barrier()  # all pushes have landed before anyone reads the parameters
+        if self.push_table.shape[0] > 0:
+            _ext.get().ag_push(self.param_ptrs, self.push_table, self.rank)
+        # all pushes have landed, and every owner has updated its rows, before anyone reads the parameters
+        self.barrier()

@@ -62,6 +62,9 @@ class TrainConfig:
     transport: str = "auto"
     overlap_reduce: bool = True
     optimizer_dtype: str = "fp32"
+    shard_params: Optional[bool] = None  # ZeRO-3 rows per rank; unset = follow FSDP2 on more than one GPU
+    barrier_timeout_s: float = 30.0      # bound of every device-side wait on a peer (own transport)
+    status_check_interval: int = 1       # optimizer steps between host reads of the device status words (0 = never)
     step_timeout_s: Optional[float] = None
     # profiler window
     profile: bool = False
@@ -141,6 +144,12 @@ class TrainConfig:
                     "use_wandb"):
             if not isinstance(getattr(self, key), bool):
                 fail(key, "must be true or false")
+        if self.shard_params is not None and not isinstance(self.shard_params, bool):
+            fail("shard_params", "must be true or false")
+        if not (isinstance(self.barrier_timeout_s, (int, float)) and 0 < self.barrier_timeout_s <= 600):
+            fail("barrier_timeout_s", "must be a number of seconds in (0, 600]")
+        if isinstance(self.status_check_interval, bool) or not isinstance(self.status_check_interval, int) or self.status_check_interval < 0:
+            fail("status_check_interval", "must be a non-negative integer")
         if self.transport not in _TRANSPORTS:
             fail("transport", f"must be one of {_TRANSPORTS}")
         if str(self.optimizer_dtype) not in _OPT_DTYPES:

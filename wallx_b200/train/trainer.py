@@ -112,6 +112,7 @@ class QwenVlAct_Trainer:
         self.epoch = 0
         self.global_step = 0
         self.initial_step = 0
+        self.step_in_epoch = 0  # batches of the current epoch consumed at the last optimizer step
         self.grad_accum = int(config.get("gradient_accumulation_steps", 1))
         self.use_fast_tokenizer = bool(config.get("use_fast_tokenizer", False))
         self.processor = processor
@@ -190,16 +191,26 @@ class QwenVlAct_Trainer:
         if transport == "symm":
             from ..parallel.symm import SymmComm
 
-            symm = SymmComm(torch.distributed.group.WORLD, self.device)
+            symm = SymmComm(torch.distributed.group.WORLD, self.device,
+                            barrier_timeout_s=float(cfg.get("barrier_timeout_s", 30.0)))
         master = torch.float32
         if str(cfg.get("optimizer_dtype", "fp32")) in ("bf16", "bfloat16"):
-            # the reference keeps bf16 Adam states; the fused CUDA update works on fp32 shards (they are
-            # sharded over the GPUs, so the memory cost is 12 bytes per parameter divided by the world size)
-            print_rank_last("optimizer_dtype=bf16 requested: this engine keeps fp32 master weights and moments")
+            # the reference keeps bf16 Adam states; the fused CUDA update works on fp32 shards only (they are
+            # sharded over the GPUs: 12 bytes per parameter divided by the world size). The CPU path honours bf16.
+            if self.device.type == "cuda":
+                raise ValueError("optimizer_dtype: bf16 is not available on CUDA: the fused AdamW kernel keeps fp32 "
+                                 "master weights and moments; use optimizer_dtype: fp32")
+            master = torch.bfloat16
+        # parameter plan: `shard_params` (true = ZeRO-3 rows per rank, gather fused into the GEMMs; false = resident
+        # bf16 parameters). Unset, it follows the reference's `FSDP2` key (train_qact.py:42-49), default off.
+        shard = cfg.get("shard_params")
+        if shard is None:
+            shard = bool(cfg.get("FSDP2", False)) and self.world > 1
         self.engine = TrainEngine(model, lr=float(cfg["learning_rate"]), weight_decay=float(cfg.get("weight_decay", 0.1)),
                                   max_grad_norm=float(cfg.get("max_grad_norm", 1.0)), grad_accum=self.grad_accum,
                                   world=self.world, rank=self.rank, transport=transport, symm=symm,
-                                  param_group_fn=self._param_group_fn(), master_dtype=master)
+                                  param_group_fn=self._param_group_fn(), master_dtype=master, shard_params=bool(shard))
+        self.status_check_interval = int(cfg.get("status_check_interval", 1))
         # per-unit reduce-scatter during backward (own transport only; YAML key `overlap_reduce`, default on)
         self.engine.overlap_reduce = transport == "symm" and bool(cfg.get("overlap_reduce", True))
         self.lr_scheduler = CosineWithMinLR(float(cfg["learning_rate"]), int(cfg.get("num_warmup_steps", 0)),
@@ -269,7 +280,11 @@ class QwenVlAct_Trainer:
         t = torch.stack([vals[k].detach().float().reshape(()) for k in keys]).to(self.device)
         d = _dist()
         if d and self.world > 1:
-            d.all_reduce(t)
+            symm = getattr(self.engine, "symm", None) if getattr(self, "engine", None) is not None else None
+            if symm is not None and self.engine.transport == "symm":
+                t = symm.all_reduce_vector(t)  # own small all-reduce over NVLink: no NCCL call on the step path
+            else:
+                d.all_reduce(t)
         return dict(zip(keys, t.cpu().tolist()))
 
     def train_loop(self, epoch: int):
@@ -283,7 +298,11 @@ class QwenVlAct_Trainer:
         acc: Dict[str, torch.Tensor] = {}
         t_iter = time.time()
         self.timers("interval-time", 0).start()
-        for i, batch in enumerate(loader, self.initial_step):
+        n_batches = len(loader) if hasattr(loader, "__len__") else None
+        skip = self.initial_step  # resuming inside an epoch: the first `skip` batches were already trained on
+        for i, batch in enumerate(loader):
+            if i < skip:
+                continue
             self.watchdog.check()
             self.timers("data-load", 0).start()
             batch = to_device(self._fit_action_dims(batch), self.device, self.dtype)
@@ -292,7 +311,9 @@ class QwenVlAct_Trainer:
             out = model(mode="train", **batch)
             self.timers("forward-compute", 0).stop()
             self.timers("backward-compute", 0).start()
-            engine.backward(out.loss)
+            # the optimizer step follows this micro-batch: at every accumulation boundary and at the end of the loader
+            steps_now = (i + 1) % self.grad_accum == 0 or (n_batches is not None and i + 1 == n_batches)
+            engine.backward(out.loss, last=steps_now)
             self.timers("backward-compute", 0).stop()
 
             def add(name, v):
@@ -308,14 +329,22 @@ class QwenVlAct_Trainer:
                     elif out.channel_loss_count_dict and k in out.channel_loss_count_dict:
                         acc[f"_sum_{k}"] = acc.get(f"_sum_{k}", 0) + v.detach().float()
                         acc[f"_cnt_{k}"] = acc.get(f"_cnt_{k}", 0) + out.channel_loss_count_dict[k].detach().float()
-            if (i + 1) % self.grad_accum == 0:
+            if steps_now:
+                # (a remainder at the end of the loader is stepped on with the gradient averaged over the
+                # micro-batches actually accumulated, as accelerate does for the reference at the end of its dataloader)
                 self.timers("optimizer", 0).start()
                 lr = self.lr_scheduler.get_lr()
+                n_micro = engine._micro
                 engine.optimizer_step(lr)
                 self.lr_scheduler.step()
                 self.global_step += 1
+                self.step_in_epoch = i + 1
                 self.timers("optimizer", 0).stop()
                 self.watchdog.kick()
+                if n_micro != self.grad_accum:
+                    acc = {k: (v * (self.grad_accum / max(n_micro, 1)) if not k.startswith("_") else v) for k, v in acc.items()}
+                if self.status_check_interval and self.global_step % self.status_check_interval == 0:
+                    engine.check_status()  # raises on every rank alike when some rank's device-side wait ran out
                 if self.global_step % log_every == 0:
                     acc["total_norm"] = engine.grad_norm() * self.world  # averaged below
                     red = self._reduce_metrics(acc)
@@ -342,6 +371,7 @@ class QwenVlAct_Trainer:
         if prof is not None:
             prof.__exit__(None, None, None)
         self.initial_step = 0
+        self.step_in_epoch = 0
 
     def _profiler(self):
         cfg = self.config
@@ -389,10 +419,8 @@ class QwenVlAct_Trainer:
         ``distribute_tensor`` per parameter). Here parameters are resident on every rank, so the file is loaded
         as is and each rank refreshes its fp32 master shard from it."""
         state = CK.strip_prefixes(CK.load_safetensors_dir(ckpt_path))
-        self.model.load_state_dict(state, strict=False)
-        for b in self.engine.buffers:
-            s0, s1 = b.shard_range
-            b.master.copy_(b.param[s0:s1].to(b.master.dtype))
+        with self.engine.gathered_parameters(writeback=True):
+            self.model.load_state_dict(state, strict=False)
 
     def training_log(self, epoch, iteration, logd, seconds):
         msg = (f"epoch {epoch} iter {iteration} step {self.global_step} loss {logd.get('train_loss', float('nan')):.5f} "
@@ -425,10 +453,13 @@ class QwenVlAct_Trainer:
         name = f"{epoch}_{step}" if step else f"{epoch}"
         path = os.path.join(root, name)
         os.makedirs(path, exist_ok=True)
+        with self.engine.gathered_parameters():  # collective when parameters are row-sharded
+            if self.is_main:
+                self.model.save_pretrained(path)
         if self.is_main:
-            self.model.save_pretrained(path)
             with open(os.path.join(path, "trainer_state.json"), "w", encoding="utf-8") as f:
                 json.dump({"epoch": epoch, "global_step": self.global_step, "world": self.world,
+                           "step_in_epoch": self.step_in_epoch if step else 0, "mid_epoch": bool(step),
                            "scheduler": self.lr_scheduler.state_dict(), "seed": self.seed}, f)
         state = self.engine.optimizer_state()
         state["rng"] = {"torch": torch.get_rng_state(), "cuda": torch.cuda.get_rng_state() if torch.cuda.is_available() else None}
@@ -442,11 +473,9 @@ class QwenVlAct_Trainer:
         r = self.config["resume"]
         path = r["ckpt"]
         state = CK.strip_prefixes(CK.load_safetensors_dir(path))
-        missing, unexpected = self.model.load_state_dict(state, strict=False)
-        # refresh fp32 master shards from the loaded bf16 weights
-        for b in self.engine.buffers:
-            s0, s1 = b.shard_range
-            b.master.copy_(b.param[s0:s1].to(b.master.dtype))
+        # the loaded bf16 weights replace the owners' shards and refresh the fp32 masters on exit
+        with self.engine.gathered_parameters(writeback=True):
+            missing, unexpected = self.model.load_state_dict(state, strict=False)
         print_rank_last(f"resume: loaded weights from {path} ({len(missing)} missing, {len(unexpected)} unexpected)")
         if r.get("load_ckpt_only", False):
             return
@@ -454,7 +483,11 @@ class QwenVlAct_Trainer:
         if os.path.exists(ts):
             with open(ts, "r", encoding="utf-8") as f:
                 st = json.load(f)
-            self.epoch = int(st["epoch"]) + 1
+            if st.get("mid_epoch"):  # a step checkpoint: continue the same epoch after the batches already seen
+                self.epoch = int(st["epoch"])
+                self.initial_step = self.step_in_epoch = int(st.get("step_in_epoch", 0))
+            else:
+                self.epoch = int(st["epoch"]) + 1
             self.global_step = int(st["global_step"])
             self.lr_scheduler.load_state_dict(st["scheduler"])
             from ..parallel.reshard import load_optimizer_shards
