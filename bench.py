@@ -239,7 +239,8 @@ class Arm:
         from wallx_b200.ops import functional as F_
 
         F_.clear_grad_sinks()
-        self.engine = self.model = self.resident = self.pool = None
+        self.engine.close()
+        self.engine = self.model = self.resident = self.pool = self.stage = None
         gc.collect()
         torch.cuda.empty_cache()
 
@@ -322,10 +323,14 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
 
-    def symm_factory():
+    comm = []
+
+    def symm_factory():  # one transport object for all arms: its symmetric arenas are reused, not re-allocated
         from wallx_b200.parallel.symm import SymmComm
 
-        return SymmComm(dist.group.WORLD, dev)
+        if not comm:
+            comm.append(SymmComm(dist.group.WORLD, dev))
+        return comm[0]
 
     arm = Arm(args, args.mode, args.shard_params, world, rank, dev, symm_factory)
     # ---- warm-up, then timed: device-resident inputs

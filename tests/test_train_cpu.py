@@ -612,3 +612,26 @@ def test_overlap_schedule_learns_triggers_and_reduces_units_during_backward(monk
     assert not early and sorted(c for c in fake.calls if isinstance(c, int)) == [0, 1, 2] and fake.calls[0] == "begin"
     for p in net.parameters():
         assert torch.isfinite(p).all()
+
+
+def test_timers_gather_through_a_transport_object():
+    """With a transport set, the per-rank timer table is built by its small all-reduce (no torch.distributed call)."""
+    from wallx_b200.utils.timers import Timers
+
+    class _Comm:
+        rank, world, device = 1, 4, "cpu"
+        calls = 0
+
+        def all_reduce_vector(self, t):
+            _Comm.calls += 1
+            out = t.clone()
+            out[0] = 0.5  # what rank 0 contributed
+            return out
+
+    t = Timers(log_level=0)
+    t("a", 0).start()
+    t("a", 0).stop()
+    t.set_comm(_Comm())
+    table = t._get_elapsed_time_all_ranks(["a", "missing"], reset=False)
+    assert table.shape == (4, 2) and _Comm.calls == 1
+    assert table[1, 0] > 0 and table[0, 0] == 0.5 and float(table[:, 1].sum()) == 0.5  # row 0 is what the fake peer sent

@@ -44,6 +44,32 @@ def test_no_alloc_column_sum_matches_regular_entry_point_twice():
     assert torch.equal(out2, out) or torch.allclose(out2.float(), out.float(), atol=0.3, rtol=2e-2)
 
 
+def test_no_alloc_odd_shapes_pitched_rows_and_empty_input():
+    """The scalar path (odd width, odd pitch), a pitched view (row pitch larger than the width) and zero rows."""
+    from wallx_b200.ops import no_alloc
+
+    lib = no_alloc.load()
+    torch.manual_seed(1)
+    base = torch.randn(5, 9, device="cuda").to(torch.bfloat16)
+    x = base[:, :7]  # 5 x 7, pitch 9: odd width and odd pitch
+    out = torch.full((7,), 3.0, device="cuda", dtype=torch.bfloat16)
+    assert _call(lib, x, out) == 0
+    torch.cuda.synchronize()
+    assert torch.allclose(out.float(), x.float().sum(0), atol=2e-2, rtol=2e-2)
+    wide = torch.randn(300, 64, device="cuda").to(torch.bfloat16)
+    v = wide[:, 8:40]  # 300 x 32 view with pitch 64 (paired loads, pitch > width)
+    out = torch.empty(32, device="cuda", dtype=torch.bfloat16)
+    assert _call(lib, v, out) == 0
+    torch.cuda.synchronize()
+    assert torch.allclose(out.float(), v.float().sum(0), atol=0.2, rtol=2e-2)
+    empty = torch.empty(0, 8, device="cuda", dtype=torch.bfloat16)
+    out = torch.full((8,), 5.0, device="cuda", dtype=torch.bfloat16)
+    assert lib.wx_column_sum_bf16_noalloc(ctypes.c_void_p(wide.data_ptr()), 8, ctypes.c_void_p(out.data_ptr()), 0, 8,
+                                          ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)) == 0
+    torch.cuda.synchronize()
+    assert empty.shape[0] == 0 and torch.equal(out.float(), torch.zeros(8, device="cuda"))  # a sum over no rows is zero
+
+
 def test_no_alloc_rejects_too_wide_and_bad_arguments():
     from wallx_b200.ops import no_alloc
 

@@ -56,38 +56,20 @@ def _build_model(args, dev):
     return ours, proc, model
 
 
-def main(args) -> None:
-    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-    ref_dir = os.path.join(root, "baseline", "_ref")
-    if not os.path.isdir(os.path.join(ref_dir, "wall_x")):
-        return unavailable("baseline/_ref/wall_x is not installed on this box")
+def _train_arm(args, mode, world, rank, local, dev, steps, warmup, do_e2e):
+    """Build the reference model for ``mode`` and time ``steps`` training steps. Returns a dict of raw numbers."""
     import torch
-
-    if not torch.cuda.is_available():
-        return unavailable("no CUDA device (the reference's action head and fused ops are CUDA-only)")
     import torch.distributed as dist
-
-    from . import ref_shims
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    try:
-        ref_shims.install(ref_dir)
-        if world > 1:
-            dist.init_process_group("nccl", device_id=dev)
-        torch.manual_seed(1234)
-        ours_cfg, proc, model = _build_model(args, dev)
-    except Exception as e:  # the reference could not be brought up on this software stack
-        import traceback
-
-        traceback.print_exc(file=sys.stderr)
-        return unavailable(f"reference could not be constructed: {type(e).__name__}: {str(e)[:200]}")
 
     from wallx_b200.data.synthetic import make_batch
 
+    class _A:
+        pass
+
+    a = _A()
+    a.action_ffn, a.layers, a.mode = args.action_ffn, args.layers, mode
+    torch.manual_seed(1234)
+    ours_cfg, proc, model = _build_model(a, dev)
     model.train()
     accum = max(1, args.per_gpu_batch // args.micro_batch)
     micro = args.per_gpu_batch // accum
@@ -107,7 +89,7 @@ def main(args) -> None:
     for _ in range(2):
         mbs = []
         for _a in range(accum):
-            b = make_batch(ours_cfg, proc, micro, views=3, image_hw=(256, 256), prompt_len=64, horizon=32, mode=args.mode,
+            b = make_batch(ours_cfg, proc, micro, views=3, image_hw=(256, 256), prompt_len=64, horizon=32, mode=mode,
                            fast_tokens=48, generator=gen)
             b = {k: (v.pin_memory() if isinstance(v, torch.Tensor) else v) for k, v in b.items()}
             mbs.append(b)
@@ -131,7 +113,7 @@ def main(args) -> None:
         for mb in mbs:
             out = model(**mb, mode="train")
             (out.loss / accum).backward()
-            loss = out.loss
+            loss = out.loss.detach()
         torch.nn.utils.clip_grad_norm_(params, 1.0)
         opt.step()
         opt.zero_grad()
@@ -142,18 +124,12 @@ def main(args) -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    try:
-        resident = [[stage(b) for b in mbs] for mbs in pool]
-        for i in range(args.warmup):
-            train_step(resident[i % len(resident)])
-        barrier()
-    except Exception as e:
-        import traceback
+    resident = [[stage(b) for b in mbs] for mbs in pool]
+    for i in range(warmup):
+        train_step(resident[i % len(resident)])
+    barrier()
 
-        traceback.print_exc(file=sys.stderr)
-        return unavailable(f"reference training step failed: {type(e).__name__}: {str(e)[:200]}")
-
-    sys.path.insert(0, root)
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
     from bench import ClockSampler
 
     sampler = ClockSampler(local)
@@ -162,7 +138,7 @@ def main(args) -> None:
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
-    for i in range(args.steps):
+    for i in range(steps):
         loss = train_step(resident[i % len(resident)])
     e1.record()
     barrier()
@@ -172,39 +148,160 @@ def main(args) -> None:
 
     ms_e2e = 0.0
     bi = 0
-    if not args.no_e2e:
+    if do_e2e:
         train_step([stage(b) for b in pool[0]])
         barrier()
         e0.record()
-        for i in range(args.steps):
+        for i in range(steps):
             l = train_step([stage(b) for b in pool[i % len(pool)]])
             _ = l.float().cpu()
         e1.record()
         barrier()
         ms_e2e = e0.elapsed_time(e1)
         bi = sum(h2d_bytes(b) for b in pool[0])
-    t = torch.tensor([ms_dev, ms_e2e], device=dev, dtype=torch.float64)
+    t = torch.tensor([ms_dev, ms_e2e, torch.cuda.max_memory_allocated(dev) / 2 ** 30], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_dev, ms_e2e = float(t[0]), float(t[1])
+    res = {"ms_dev": float(t[0]), "ms_e2e": float(t[1]), "peak_gb": float(t[2]), "clocks": clocks, "loss": loss_val,
+           "h2d": int(bi), "accum": accum, "micro": micro, "seq_len": int(pool[0][0]["input_ids"].shape[1])}
+    del model, opt, params, resident, pool
+    import gc
+
+    gc.collect()
+    torch.cuda.empty_cache()
+    return res
+
+
+def _latency_block(args, world, rank, dev, chunks):
+    """p50 / p99 of the reference's own ``model(mode="predict", predict_mode="diffusion")`` per action chunk, H2D of
+    the observation to D2H of the chunk, with ``num_inference_timesteps=11`` (10 evaluations on its linspace grid;
+    every evaluation re-runs the whole sequence, modeling_qwen2_5_vl_act.py:1906-1962)."""
+    import torch
+    import torch.distributed as dist
+
+    from wallx_b200.bench.flow_latency import _h2d, _percentile, _pin
+    from wallx_b200.data.synthetic import make_batch
+
+    class _A:
+        pass
+
+    a = _A()
+    a.action_ffn, a.layers, a.mode = args.action_ffn, args.layers, "flow"
+    torch.manual_seed(1234)
+    ours_cfg, proc, model = _build_model(a, dev)
+    model.eval()
+    out = {"unit": "ms per chunk", "euler_evaluations": 10, "chunks": chunks,
+           "path": "reference predict(diffusion), num_inference_timesteps=11; timed H2D of the observation to D2H of the chunk"}
+    for B in (1, 32):
+        gen = torch.Generator().manual_seed(100 + rank)
+        pool = []
+        for _ in range(3):
+            b = make_batch(ours_cfg, proc, B, views=3, image_hw=(256, 256), prompt_len=64, horizon=32, mode="flow", generator=gen)
+            b.pop("action_chunk", None)
+            b.pop("labels", None)
+            pool.append(_pin(b))
+
+        def chunk(i):
+            batch, _ = _h2d(pool[i % 3], dev, torch.bfloat16)
+            with torch.no_grad():
+                o = model(mode="predict", predict_mode="diffusion", num_inference_timesteps=11, pred_horizon=32,
+                          action_dim=20, **batch)
+            return o["predict_action"].float().cpu()
+
+        for i in range(2):
+            chunk(i)
+        torch.cuda.synchronize()
+        times = []
+        for i in range(chunks):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            chunk(i)
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        p = torch.tensor([_percentile(times, 0.5), _percentile(times, 0.99)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(p, op=dist.ReduceOp.MAX)
+        out[f"batch{B}"] = {"p50_ms": round(float(p[0]), 3), "p99_ms": round(float(p[1]), 3)}
+    return out
+
+
+def main(args) -> None:
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    ref_dir = os.path.join(root, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "wall_x")):
+        return unavailable("baseline/_ref/wall_x is not installed on this box")
+    import torch
+
+    if not torch.cuda.is_available():
+        return unavailable("no CUDA device (the reference's action head and fused ops are CUDA-only)")
+    import torch.distributed as dist
+
+    from . import ref_shims
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    try:
+        ref_shims.install(ref_dir)
+        if world > 1:
+            dist.init_process_group("nccl", device_id=dev)
+    except Exception as e:  # the reference could not be brought up on this software stack
+        import traceback
+
+        traceback.print_exc(file=sys.stderr)
+        return unavailable(f"reference could not be constructed: {type(e).__name__}: {str(e)[:200]}")
+    try:
+        r = _train_arm(args, args.mode, world, rank, local, dev, args.steps, args.warmup, not args.no_e2e)
+    except Exception as e:
+        import traceback
+
+        traceback.print_exc(file=sys.stderr)
+        return unavailable(f"reference training step failed: {type(e).__name__}: {str(e)[:200]}")
     gb = args.per_gpu_batch * world
+    rec = {
+        "metric": f"train samples/s, WALL-OSS-{args.mode.upper()}-size fine-tune (max over ranks, device-timed)",
+        "value": round(gb * args.steps / (r["ms_dev"] / 1e3), 3), "unit": "samples/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(r["ms_dev"] / args.steps, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
+        "config": {"model": f"WALL-OSS-{args.mode.upper()} (reference classes, flash_attention_2, action expert FFN {args.action_ffn})"
+                            + (f" DEBUG layers={args.layers}" if args.layers else ""),
+                   "global_batch": gb, "per_gpu_batch": args.per_gpu_batch, "micro_batch": r["micro"], "grad_accum": r["accum"],
+                   "seq_len": r["seq_len"],
+                   "parallelism": ("fsdp2 fully_shard per layer/block, reshard_after_forward, NCCL" if world > 1 else "single GPU"),
+                   "optimizer": "torch.optim.AdamW on bf16 params (bf16 states), clip 1.0", "loss": r["loss"],
+                   "peak_device_memory_gb": round(r["peak_gb"], 1)},
+        "clocks": r["clocks"],
+    }
+    if not args.no_e2e:
+        rec["e2e"] = {"value": round(gb * args.steps / (r["ms_e2e"] / 1e3), 3), "unit": "samples/s",
+                      "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": 4, "ms_per_step": round(r["ms_e2e"] / args.steps, 3)}
+
+    def extra(name, fn):
+        try:
+            rec[name] = fn()
+        except Exception as e:
+            import traceback
+
+            traceback.print_exc(file=sys.stderr)
+            rec[name] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+        if world > 1:
+            dist.barrier()
+
+    def fast_block():
+        torch.cuda.reset_peak_memory_stats(dev)
+        k = max(2, min(args.steps, getattr(args, "extra_steps", 4)))
+        f = _train_arm(args, "fast", world, rank, local, dev, k, 2, False)
+        return {"value": round(gb * k / (f["ms_dev"] / 1e3), 3), "unit": "samples/s", "ms_per_step": round(f["ms_dev"] / k, 3),
+                "steps": k, "warmup": 2, "n_gpus": world, "peak_device_memory_gb": round(f["peak_gb"], 1), "loss": f["loss"]}
+
+    if not getattr(args, "no_extras", False):
+        if args.mode == "flow":
+            extra("fast", fast_block)
+        extra("latency", lambda: _latency_block(args, world, rank, dev, max(5, getattr(args, "latency_chunks", 20) // 2)))
     if rank == 0:
-        rec = {
-            "metric": f"train samples/s, WALL-OSS-{args.mode.upper()}-size fine-tune (max over ranks, device-timed)",
-            "value": round(gb * args.steps / (ms_dev / 1e3), 3), "unit": "samples/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": round(ms_dev / args.steps, 3), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
-            "config": {"model": f"WALL-OSS-{args.mode.upper()} (reference classes, flash_attention_2, action expert FFN {args.action_ffn})"
-                                + (f" DEBUG layers={args.layers}" if args.layers else ""),
-                       "global_batch": gb, "per_gpu_batch": args.per_gpu_batch, "micro_batch": micro, "grad_accum": accum,
-                       "seq_len": int(pool[0][0]["input_ids"].shape[1]),
-                       "parallelism": ("fsdp2 fully_shard per layer/block, reshard_after_forward, NCCL" if world > 1 else "single GPU"),
-                       "optimizer": "torch.optim.AdamW on bf16 params (bf16 states), clip 1.0", "loss": loss_val},
-            "clocks": clocks,
-        }
-        if not args.no_e2e:
-            rec["e2e"] = {"value": round(gb * args.steps / (ms_e2e / 1e3), 3), "unit": "samples/s",
-                          "h2d_bytes_per_step": int(bi), "d2h_bytes_per_step": 4, "ms_per_step": round(ms_e2e / args.steps, 3)}
         print(json.dumps(rec), flush=True)
     if world > 1:
         dist.destroy_process_group()

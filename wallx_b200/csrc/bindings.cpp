@@ -12,12 +12,11 @@
 #include <vector>
 
 #include "attention.h"
+#include "bind_common.h"
 #include "gemm.h"
 #include "kernels.h"
 
-namespace {
-
-using OptT = c10::optional<at::Tensor>;
+namespace wxb {
 
 // Launch-failure report formatted with snprintf (no iostream on the error path).
 [[noreturn]] void fail_code(const char* what, int rc) {
@@ -43,9 +42,6 @@ int64_t read_status(int64_t device_index) {
   if (v != 0) t.zero_();
   return v;
 }
-
-using GemmTuple = std::tuple<at::Tensor, bool, at::Tensor, bool, at::Tensor, int64_t, int64_t, int64_t, OptT, OptT,
-                             OptT, OptT, OptT, int64_t, int64_t, int64_t>;
 
 const void* opt_ptr(const OptT& t) { return (t.has_value() && t->defined()) ? t->data_ptr() : nullptr; }
 
@@ -108,6 +104,16 @@ void fill_call(wx::GemmCall& c, const GemmTuple& g) {
     if (c.D2) TORCH_CHECK((c.ldd2 % 8) == 0 && (reinterpret_cast<uintptr_t>(c.D2) % 16) == 0, "gemm: swiglu raw output");
   }
 }
+
+}  // namespace wxb
+
+namespace {
+
+using wxb::fail_code;
+using wxb::fill_call;
+using wxb::GemmTuple;
+using wxb::OptT;
+using wxb::status_tensor;
 
 void gemm_grouped(const std::vector<GemmTuple>& calls, int64_t force_bn) {
   TORCH_CHECK(calls.size() >= 1 && calls.size() <= 2, "gemm: one or two problems per launch");
@@ -230,15 +236,17 @@ void attn_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, 
 }  // namespace
 
 void register_kernel_bindings(pybind11::module_& m);
+void register_block_bindings(pybind11::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_ag", &gemm_ag, "GEMM with the weight all-gather fused in (peer loads over NVLink)");
   m.def("gemm_grouped", &gemm_grouped, "tcgen05 GEMM: one or two problems in one launch");
-  m.def("read_status", &read_status, "read and clear the device-side wait-timeout status");
+  m.def("read_status", &wxb::read_status, "read and clear the device-side wait-timeout status");
   m.def("status_tensor", [](int64_t device_index) {
-    return status_tensor(at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(device_index)));
+    return wxb::status_tensor(at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(device_index)));
   }, "the device-side status words themselves (int32[4]; word 0 non-zero after a wait ran out)");
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
   register_kernel_bindings(m);
+  register_block_bindings(m);
 }

@@ -15,6 +15,8 @@
 //   * `cols` above WX_NOALLOC_MAX_COLS is refused with WX_NOALLOC_ERR_TOO_WIDE; nothing is launched.
 //   * The first call on a device looks up the scratch array's device address (once per device,
 //     with that device current). Make that first call before any stream capture begins.
+//   * Row slices are added into the scratch with float atomics, so the last bits of a sum can differ
+//     from run to run (the regular entry point reduces in a fixed order and is bit-reproducible).
 //   * All calls share the one scratch array and it keeps the last call's contents, so every call
 //     starts by clearing the part it uses. Two calls that overlap on the GPU (different streams,
 //     or different host threads) race on it: serialise them.
@@ -24,7 +26,7 @@
 #define WX_NOALLOC_MAX_COLS 65536
 
 #define WX_NOALLOC_OK 0
-#define WX_NOALLOC_ERR_BAD_ARG (-1)    // null pointer, negative size, or misaligned input
+#define WX_NOALLOC_ERR_BAD_ARG (-1)    // null pointer, negative size, ld < cols, or input not 4-byte aligned
 #define WX_NOALLOC_ERR_TOO_WIDE (-2)   // cols > WX_NOALLOC_MAX_COLS
 #define WX_NOALLOC_ERR_SETUP (-3)      // the scratch address could not be resolved on this device
 // Positive return values are cudaError_t codes from the launches.

@@ -18,6 +18,7 @@ import torch
 import torch.nn as nn
 
 from ..config import Qwen2_5_VLConfig
+from ..ops import blocks as BK
 from ..ops import functional as F_
 from ..ops import ref
 from .generation import MoEModelMaskMixin
@@ -119,7 +120,29 @@ class DecoderLayer(nn.Module):
             self.moe = None
             self.mlp = SwiGLUFFN(config.hidden_size, config.intermediate_size, bias=False)
 
+    def _plain_modules(self) -> bool:
+        """True when every projection is this package's own module (LoRA wrappers and the like take the
+        operator-by-operator path)."""
+        a = self.self_attn
+        ok = type(a.qkv_proj) is FusedQKV and type(a.o_proj) is Linear
+        if self.moe is not None:
+            return ok and all(type(e) is SwiGLUFFN for e in self.moe.experts)
+        return ok and type(self.mlp) is SwiGLUFFN
+
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        if BK.usable(x) and (ctx.cache is None or ctx.cache_mode == "none") and self._plain_modules():
+            # the whole layer, forward or backward, is one host call (csrc/blocks.cpp)
+            a = self.self_attn
+            if self.moe is not None:
+                ffn_w = [w for e in self.moe.experts for w in e.weights()]
+                plan = ctx.plan
+            else:
+                ffn_w, plan = list(self.mlp.weights()), None
+            return BK.transformer_block(
+                x, self.input_layernorm.weight, a.qkv_proj.weight, a.qkv_proj.bias, a.o_proj.weight, a.o_proj.bias,
+                self.post_attention_layernorm.weight, ffn_w, None, None, meta=ctx.meta, cos=ctx.cos, sin=ctx.sin,
+                n_rot=a.num_heads + a.num_kv_heads, hq=a.num_heads, hkv=a.num_kv_heads, d=a.head_dim,
+                eps=self.input_layernorm.variance_epsilon, plan=plan)
         x = self.self_attn(self.input_layernorm(x), ctx, residual=x)
         if self.moe is not None:
             xp = self.post_attention_layernorm(x, dest=ctx.plan.dest, out_rows=ctx.plan.rows)

@@ -16,6 +16,7 @@ import torch
 import torch.nn as nn
 
 from ..config import Qwen2_5_VLVisionConfig
+from ..ops import blocks as BK
 from ..ops import functional as F_
 from ..ops import ref
 from ..ops import index as IX
@@ -61,6 +62,13 @@ class VisionBlock(nn.Module):
         self.mlp = SwiGLUFFN(config.hidden_size, config.intermediate_size, bias=True)
 
     def forward(self, x, meta, cos, sin):
+        a, f = self.attn, self.mlp
+        if BK.usable(x) and type(a.qkv) is Linear and type(a.proj) is Linear and type(f) is SwiGLUFFN:
+            # the whole block, forward or backward, is one host call (csrc/blocks.cpp)
+            return BK.transformer_block(x, self.norm1.weight, a.qkv.weight, a.qkv.bias, a.proj.weight, a.proj.bias,
+                                        self.norm2.weight, list(f.weights()), f.gate_up_bias, f.down_bias, meta=meta,
+                                        cos=cos, sin=sin, n_rot=2 * a.num_heads, hq=a.num_heads, hkv=a.num_heads,
+                                        d=a.head_dim, eps=self.norm1.variance_epsilon)
         x = self.attn(self.norm1(x), meta, cos, sin, residual=x)
         return self.mlp(self.norm2(x), residual=x)
 

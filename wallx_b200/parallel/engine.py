@@ -404,6 +404,15 @@ class TrainEngine:
                 if writeback:
                     self.refresh_master()
 
+    def close(self) -> None:
+        """Detach the engine from the model (hooks, gradient sinks, gather records) so that both can be freed."""
+        for b in self.buffers:
+            b.release()
+        self.buffers = []
+        self.optimizer.buffers = []
+        self.workspace = None
+        self.symm = None
+
     def refresh_master(self) -> None:
         """fp32 master shards := current bf16 parameter shards (after loading weights into the model)."""
         for b in self.buffers:

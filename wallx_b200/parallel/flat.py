@@ -81,9 +81,10 @@ class FlatBuffer:
         # whose grad is None untouched -- no decay, no moment update -- e.g. the LM head in flow-only
         # training); filled by post-accumulate hooks, merged across ranks by the engine
         self.touched = [False] * len(self.params)
+        self._hook_handles = []
         self.on_touch = None  # optional callback(buffer, param_index, kind) used by the engine to overlap the reduction
         for i, p in enumerate(self.params):
-            p.register_post_accumulate_grad_hook(self._make_hook(i, "accumulate"))
+            self._hook_handles.append(p.register_post_accumulate_grad_hook(self._make_hook(i, "accumulate")))
         if self.param.is_cuda:  # weight-gradient GEMMs add straight into the flat gradient buffer
             from ..ops import functional as F_
 
@@ -112,6 +113,20 @@ class FlatBuffer:
 
     def clear_touched(self) -> None:
         self.touched = [False] * len(self.params)
+
+    def release(self) -> None:
+        """Undo the hooks and gradient sinks on the parameters. The hooks are held by the tensors on the C++ side and
+        refer back to this buffer, a cycle the garbage collector cannot see: without this call neither the
+        parameters nor the optimizer state of a discarded engine are ever freed."""
+        for h in self._hook_handles:
+            h.remove()
+        self._hook_handles = []
+        for p in self.params:
+            for attr in ("_wx_sink", "_wx_shard"):
+                if hasattr(p, attr):
+                    delattr(p, attr)
+            p.grad = None
+        self.on_touch = None
 
     def update_ranges(self, touched=None) -> List[Tuple[int, int, ParamSegment]]:
         """Shard-local ``(lo, hi, segment)`` ranges to update: touched parameters only, adjacent

@@ -64,12 +64,19 @@ class SymmComm:
         """Allocate the two arenas. With row-sharded parameters the parameter arena holds shards and the gradient
         arena whole gradients, so their sizes differ (``grad_elems``)."""
         sm = self.symm_mem
-        self.param_arena = sm.empty(total_elems, dtype=dtype, device=self.device)
-        self.grad_arena = sm.empty(grad_elems or total_elems, dtype=dtype, device=self.device)
+        grad_elems = grad_elems or total_elems
+        # symmetric allocations are not returned to the caching allocator, so an engine that replaces another one
+        # (same transport object) takes over the arenas when they are large enough
+        if self.param_arena is None or self.param_arena.numel() < total_elems or self.param_arena.dtype != dtype:
+            self.param_arena = None
+            self.param_arena = sm.empty(total_elems, dtype=dtype, device=self.device)
+            self.param_ptrs = [int(p) for p in sm.rendezvous(self.param_arena, self.group).buffer_ptrs]
+        if self.grad_arena is None or self.grad_arena.numel() < grad_elems or self.grad_arena.dtype != dtype:
+            self.grad_arena = None
+            self.grad_arena = sm.empty(grad_elems, dtype=dtype, device=self.device)
+            self.grad_ptrs = [int(p) for p in sm.rendezvous(self.grad_arena, self.group).buffer_ptrs]
         self.param_arena.zero_()
         self.grad_arena.zero_()
-        self.param_ptrs = [int(p) for p in sm.rendezvous(self.param_arena, self.group).buffer_ptrs]
-        self.grad_ptrs = [int(p) for p in sm.rendezvous(self.grad_arena, self.group).buffer_ptrs]
         self._cursor = {"param": 0, "grad": 0}
 
     def _take(self, which: str, n: int, dtype) -> torch.Tensor:

@@ -161,9 +161,10 @@ class RowShardedBuffer:
                     p.data = self.param[o:o + R * C].view(R, C)
                 p.grad = self.grad[go:go + R * C].view(R, C)
         self.touched = [False] * len(self.params)
+        self._hook_handles = []
         self.on_touch = None
         for i, p in enumerate(self.params):
-            p.register_post_accumulate_grad_hook(self._make_hook(i, "accumulate"))
+            self._hook_handles.append(p.register_post_accumulate_grad_hook(self._make_hook(i, "accumulate")))
         if self.param.is_cuda:  # weight-gradient GEMMs add straight into the unit's gradient buffer
             from ..ops import functional as F_
 
@@ -189,6 +190,20 @@ class RowShardedBuffer:
 
     def clear_touched(self) -> None:
         self.touched = [False] * len(self.params)
+
+    def release(self) -> None:
+        """Undo the hooks and gradient sinks on the parameters. The hooks are held by the tensors on the C++ side and
+        refer back to this buffer, a cycle the garbage collector cannot see: without this call neither the
+        parameters nor the optimizer state of a discarded engine are ever freed."""
+        for h in self._hook_handles:
+            h.remove()
+        self._hook_handles = []
+        for p in self.params:
+            for attr in ("_wx_sink", "_wx_shard"):
+                if hasattr(p, attr):
+                    delattr(p, attr)
+            p.grad = None
+        self.on_touch = None
 
     def rows_per_rank(self, i: int) -> int:
         return self.shapes[i][0] // self.world

@@ -131,6 +131,8 @@ class QwenVlAct_Trainer:
         tok = self.model.processor.tokenizer if self.model.processor is not None else None
         self.action_token_id = tok.convert_tokens_to_ids("<|action|>") if tok is not None else None
         self.timers = Timers(log_level=0, log_option="minmax")
+        if self.engine.transport == "symm":
+            self.timers.set_comm(self.engine.symm)  # per-rank timer table over the own small all-reduce
         self.watchdog = StepWatchdog(config.get("step_timeout_s"))
 
     # ------------------------------------------------------------------ model / optimizer

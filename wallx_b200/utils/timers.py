@@ -141,6 +141,13 @@ class Timers:
         self._dummy = DummyTimer()
         self._max_log_level = 2
         self._nvtx = nvtx
+        self._comm = None
+
+    def set_comm(self, comm) -> None:
+        """Gather the per-rank times with this transport's small all-reduce (an object with ``rank``, ``world``,
+        ``device`` and ``all_reduce_vector``, e.g. :class:`wallx_b200.parallel.symm.SymmComm`) instead of a
+        ``torch.distributed`` all-gather: with the NVLink transport the logging path then makes no NCCL call."""
+        self._comm = comm
 
     def __call__(self, name: str, log_level: Optional[int] = None):
         if name in self._timers:
@@ -158,6 +165,11 @@ class Timers:
     def _gather(self, names: List[str], reset: bool, barrier: bool):
         local = torch.tensor([self._timers[n].elapsed(reset=reset, barrier=barrier) if n in self._timers else 0.0
                               for n in names], dtype=torch.float32)
+        comm = self._comm
+        if comm is not None and comm.world > 1 and comm.world * len(names) <= 4096:
+            table = torch.zeros((comm.world, len(names)), dtype=torch.float32)
+            table[comm.rank] = local  # every rank fills its own row: the sum over ranks is the gathered table
+            return comm.all_reduce_vector(table.to(comm.device)).cpu()
         if torch.distributed.is_available() and torch.distributed.is_initialized():
             world = torch.distributed.get_world_size()
             dev = torch.device("cuda", torch.cuda.current_device()) if torch.distributed.get_backend() == "nccl" else "cpu"
