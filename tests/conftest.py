@@ -23,3 +23,23 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _range_checks_stay_clean():
+    """With the debug build of the kernels (WALLX_CHECKED=1) every test must leave the range-check records empty."""
+    yield
+    if os.environ.get("WALLX_CHECKED", "0") != "1":
+        return
+    import torch
+
+    if not torch.cuda.is_available():
+        return
+    from wallx_b200.ops import _ext
+
+    mod = _ext.get(required=False)
+    if mod is None or not mod.checked_build():
+        return
+    report = mod.check_report(True)
+    bad = {k: v for k, v in report.items() if v[1] != 0}
+    assert not bad, f"range checks of the debug build fired (unit: [site, count, value, value]): {bad}"

@@ -81,3 +81,24 @@ def test_bench_contract_keys_and_entry_points_exist():
     assert callable(mod.build) and callable(mod.smoke)
     entry = (ROOT / "__graft_entry__.py").read_text() + (ROOT / "wallx_b200" / "ops" / "_ext.py").read_text() + (ROOT / "setup.py").read_text()
     assert "arch=compute_100a,code=sm_100a" in entry and "-lineinfo" in entry
+
+
+def test_release_build_contains_no_range_check_code():
+    """The debug-build checks (csrc/check.cuh) must cost nothing in the product: preprocessed without -DWX_CHECK no kernel
+    source refers to the recorder, with it they do; and the release extension reports itself as unchecked."""
+    import shutil
+
+    nvcc = shutil.which("nvcc")
+    csrc = ROOT / "wallx_b200" / "csrc"
+    if nvcc is not None:
+        for unit in ("kernels.cu", "index.cu", "comm.cu"):
+            base = [nvcc, "-E", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I", str(csrc), str(csrc / unit)]
+            plain = subprocess.run(base, capture_output=True, text=True, check=True).stdout
+            checked = subprocess.run(base + ["-DWX_CHECK"], capture_output=True, text=True, check=True).stdout
+            assert "chk::fail" not in plain and "g_record" not in plain, unit
+            assert "chk::fail" in checked, unit
+    from wallx_b200.ops import _ext
+
+    mod = _ext.get(required=False)
+    if mod is not None and not _ext.CHECKED:
+        assert mod.checked_build() is False

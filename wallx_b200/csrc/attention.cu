@@ -127,6 +127,8 @@ attn_fwd_kernel(const __grid_constant__ AttnArgs a, int* __restrict__ status) {
 
   int4 qi = make_int4(0, 0, -1, 0);
   if (row_ok) qi = a.qtab[row];
+  // debug build: the row's key range lies inside the key buffer and its causal limit inside that range
+  if (row_ok && !WX_CHK(qi.x >= 0 && qi.x <= qi.y && qi.y <= a.Tk && qi.z < qi.y, 3001, qi.x, qi.y)) qi = make_int4(0, 0, -1, 0);
   if (tid == 0) {
     for (int i = 0; i < 5; ++i) mbar_init(&ctl.bar[i], 1);
     mbar_init(s_free, 128);
@@ -390,6 +392,7 @@ attn_dq_kernel(const __grid_constant__ AttnArgs a, int* __restrict__ status) {
   float lse2 = 0.f, dlt_s = 0.f;
   if (row_ok) {
     qi = a.qtab[row];
+    if (!WX_CHK(qi.x >= 0 && qi.x <= qi.y && qi.y <= a.Tk && qi.z < qi.y, 3002, qi.x, qi.y)) qi = make_int4(0, 0, -1, 0);
     lse2 = a.lse[static_cast<long>(h) * a.Tq + row] * LOG2E;
     dlt_s = a.delta[static_cast<long>(h) * a.Tq + row] * a.scale;
   }
@@ -591,6 +594,8 @@ attn_dkdv_kernel(const __grid_constant__ AttnArgs a, int* __restrict__ status) {
 
   int4 ki = make_int4(0, 0, 0x7fffffff, 0);  // (q_lo, q_hi, first causal viewer, flag | first viewer << 1)
   if (key_ok) ki = a.ktab[key];
+  // debug build: the key's query range lies inside the query buffer
+  if (key_ok && !WX_CHK(ki.x >= 0 && ki.x <= ki.y && ki.y <= a.Tq, 3003, ki.x, ki.y)) ki = make_int4(0, 0, 0x7fffffff, 0);
   const int kflag = ki.w & 1;
   if (tid == 0) {
     for (int i = 0; i < 5; ++i) mbar_init(&ctl.bar[i], 1);
@@ -868,6 +873,8 @@ bool shape_ok(const AttnShape& s) {
 }
 
 }  // namespace
+
+WX_CHK_DEFINE_READER(attn_check_read)
 
 int attn_fwd(const AttnShape& s, const void* q, const void* k, const void* v, const void* qtab, const void* ktab,
              void* out, long ld_out, float* lse, cudaStream_t stream, int* status) {

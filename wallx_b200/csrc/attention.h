@@ -30,4 +30,8 @@ int attn_bwd(const AttnShape& s, const void* q, const void* k, const void* v, co
              void* dq, long ld_dq, void* dk, long ld_dk, void* dv, long ld_dv, float* part_k, float* part_v,
              cudaStream_t stream, int* status);
 
+// Debug build (-DWX_CHECK): this translation unit's range-check record {first violating site, violation count, two
+// values}, cleared when `clear`; all zeros in a release build. Returns a CUDA error code.
+int attn_check_read(long long* out4, int clear);
+
 }  // namespace wx

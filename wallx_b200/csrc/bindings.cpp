@@ -13,6 +13,7 @@
 
 #include "attention.h"
 #include "bind_common.h"
+#include "comm.h"
 #include "gemm.h"
 #include "kernels.h"
 
@@ -72,6 +73,7 @@ void fill_call(wx::GemmCall& c, const GemmTuple& g) {
   c.K = static_cast<int>(std::get<7>(g));
   c.D = D.data_ptr();
   c.ldd = D.stride(0);
+  c.d_rows = D.size(0);
   const OptT& bias = std::get<8>(g);
   const OptT& residual = std::get<9>(g);
   const OptT& row_map = std::get<10>(g);
@@ -241,6 +243,22 @@ void register_block_bindings(pybind11::module_& m);
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_ag", &gemm_ag, "GEMM with the weight all-gather fused in (peer loads over NVLink)");
   m.def("gemm_grouped", &gemm_grouped, "tcgen05 GEMM: one or two problems in one launch");
+  m.def("checked_build", []() { return wx::gemm_checked_build() != 0; }, "true when the kernels were compiled with -DWX_CHECK");
+  m.def("check_report", [](bool clear) {
+    // one record per translation unit: {unit: [first violating site, violations, value, value]} (synchronises)
+    cudaDeviceSynchronize();
+    pybind11::dict out;
+    long long r[4];
+    struct Unit { const char* name; int (*read)(long long*, int); };
+    const Unit units[] = {{"gemm", &wx::gemm_check_read}, {"attention", &wx::attn_check_read}, {"kernels", &wx::kernels_check_read},
+                          {"index", &wx::index_check_read}, {"comm", &wx::comm_check_read}};
+    for (const Unit& u : units) {
+      const int rc = u.read(r, clear ? 1 : 0);
+      if (rc != 0) wxb::fail_code("check_report", rc);
+      out[u.name] = std::vector<long long>{r[0], r[1], r[2], r[3]};
+    }
+    return out;
+  }, pybind11::arg("clear") = true, "range-check records of the debug build (all zeros in a release build)");
   m.def("read_status", &wxb::read_status, "read and clear the device-side wait-timeout status");
   m.def("status_tensor", [](int64_t device_index) {
     return wxb::status_tensor(at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(device_index)));

@@ -344,7 +344,7 @@ std::vector<Tensor> block_bwd(const Tensor& dout_in, const Tensor& x, const Tens
   // ---- FFN half
   if (moe) {
     Tensor dyp = at::zeros({rows, H}, x.options());  // grouped order, zero padding rows
-    WX_RC(wx::permute_rows(dout.data_ptr(), dest->data_ptr<int>(), dyp.data_ptr(), T, H, cur()), "permute_rows");
+    WX_RC(wx::permute_rows(dout.data_ptr(), dest->data_ptr<int>(), dyp.data_ptr(), T, H, cur(), static_cast<int>(rows)), "permute_rows");
     const int64_t wmax = gu.size(1);
     Tensor dgu = empty_bf16(rows, wmax, x);
     for (int e0 = 0; e0 < n_exp; e0 += 2) {  // dL/dh = dy @ w_down, turned into dL/d(gate|up) in the epilogue

@@ -8,6 +8,7 @@
 // all-gather); there is no ring. Waits on peer flags are bounded: after the caller's limit (2 s by
 // default, ten minutes at most) the kernel records an error status and returns.
 #include "comm.h"
+#include "check.cuh"
 #include "devinfo.h"
 
 #include <cuda_bf16.h>
@@ -33,6 +34,10 @@ __device__ __forceinline__ int ld_acquire_sys(const int* p) {
 __global__ void symm_barrier_kernel(PeerPtrs flags, int rank, int world, int epoch, int* status, uint64_t limit_ns) {
   const int p = threadIdx.x;
   if (p >= world) return;
+  if (!WX_CHK(rank >= 0 && rank < world && world <= kMaxPeers && epoch > 0 && flags.p[p] != nullptr, 6003, rank, epoch)) {
+    atomicExch(status, 15);
+    return;
+  }
   __threadfence_system();
   st_release_sys(reinterpret_cast<int*>(flags.p[p]) + rank, epoch);
   const int* mine = reinterpret_cast<const int*>(flags.p[rank]) + p;
@@ -59,7 +64,9 @@ rs_reduce_kernel(PeerPtrs grads, const ShardDesc* __restrict__ table, int world,
                  float* __restrict__ sumsq) {
   __shared__ float red[8];
   const ShardDesc d = table[blockIdx.y];
-  const long n8 = d.n >> 3;
+  // 16-byte vector loads and stores: offsets and lengths in whole groups of eight bf16 / four fp32
+  const long n8 = WX_CHK(d.n >= 0 && ((d.n | d.arena_off) & 7) == 0 && (d.out_off & 3) == 0 && world >= 1 && world <= kMaxPeers,
+                         6001, d.arena_off, d.n) ? d.n >> 3 : 0;
   float ss = 0.f;
   for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
        i += static_cast<long>(gridDim.x) * blockDim.x) {
@@ -123,7 +130,8 @@ rs_reduce_kernel(PeerPtrs grads, const ShardDesc* __restrict__ table, int world,
 __global__ void __launch_bounds__(256)
 ag_push_kernel(PeerPtrs params, const ShardDesc* __restrict__ table, int rank, int world) {
   const ShardDesc d = table[blockIdx.y];
-  const long n8 = d.n >> 3;
+  const long n8 = WX_CHK(d.n >= 0 && ((d.n | d.arena_off) & 7) == 0 && rank >= 0 && rank < world && world <= kMaxPeers, 6002,
+                         d.arena_off, d.n) ? d.n >> 3 : 0;
   const BF8* src = reinterpret_cast<const BF8*>(reinterpret_cast<const __nv_bfloat16*>(params.p[rank]) + d.arena_off);
   for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
        i += static_cast<long>(gridDim.x) * blockDim.x) {
@@ -203,6 +211,8 @@ __global__ void adamw_f32g_kernel(__nv_bfloat16* __restrict__ p16, float* __rest
 }
 
 }  // namespace
+
+WX_CHK_DEFINE_READER(comm_check_read)
 
 int symm_barrier(const PeerPtrs& flags, int rank, int world, int epoch, int* status, cudaStream_t s, long timeout_ms) {
   if (world < 1 || world > kMaxPeers) return -1;

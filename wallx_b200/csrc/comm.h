@@ -47,4 +47,7 @@ int small_allreduce_sum(const float* my_scratch, float* out, int n, int world, c
 int adamw_step_f32g(void* p16, float* p32, float* m, float* v, const float* g, long n, const float* hyper,
                     const float* norm_sq, cudaStream_t s);
 
+// Debug build (-DWX_CHECK): this translation unit's range-check record (see kernels.h); zeros in a release build.
+int comm_check_read(long long* out4, int clear);
+
 }  // namespace wx

@@ -40,7 +40,7 @@ struct Problem {
   const __nv_bfloat16* residual;
   const int* row_map;
   const int* dyn;
-  long ldd, ldd2, ldr;
+  long ldd, ldd2, ldr, d_rows;
   int M, N, K, m0, k0, flags;
 };
 
@@ -177,6 +177,8 @@ __device__ __forceinline__ void epilogue_rows(const Problem& p, int M, int m0, i
     store_ok = r >= 0;
     drow = r;
   }
+  // debug build: the destination row lies inside D (after the row map, with zero-filled pad rows included)
+  if (store_ok && !WX_CHK(drow >= 0 && (p.d_rows == 0 || drow < p.d_rows), 2005, drow, p.d_rows)) store_ok = false;
   const int flags = p.flags;
   const bool swiglu = (flags & GEMM_ACT_SWIGLU) != 0;
   const bool out_fp32 = (flags & GEMM_OUT_FP32) != 0;
@@ -375,6 +377,10 @@ __device__ bool ag_pull(const AgDev& ag, int q, uint8_t* ring, uint64_t* bars, v
         break;
       }
       const size_t off = (static_cast<size_t>(S.nt) * ag.cpt + S.i) * cb;
+      if (!WX_CHK(S.nt >= 0 && S.nt < ag.ntiles && off + cb <= static_cast<size_t>(ag.total_bytes), 2001, S.nt, off)) {
+        ok = false;
+        break;
+      }
       bulk_store(ag.staging + off, ring + sbuf * kAgChunkMax, cb);
       tma_store_commit();
       ++stored;
@@ -418,6 +424,10 @@ __device__ bool ag_pull(const AgDev& ag, int q, uint8_t* ring, uint64_t* bars, v
     if (issued - seq >= kAgRing) bulk_store_wait_read<2>();  // the store that last read this buffer is 2+ groups back
     const uint32_t g = static_cast<uint32_t>(L.nt) * ag.cpt + L.i;  // chunk index in the whole weight
     const uint32_t r = g / static_cast<uint32_t>(ag.cps);
+    if (!WX_CHK(r < 8u && ag.peer[r] != nullptr && static_cast<long>(g - r * ag.cps + 1) * cb <= ag.shard_bytes, 2002, g, r)) {
+      ok = false;
+      break;
+    }
     const uint8_t* src = ag.peer[r] + static_cast<size_t>(g - r * ag.cps) * cb;
     mbar_arrive_expect_tx(&bars[lbuf], cb);
     bulk_load(ring + lbuf * kAgChunkMax, src, cb, &bars[lbuf]);
@@ -446,6 +456,10 @@ __device__ bool ag_pull(const AgDev& ag, int q, uint8_t* ring, uint64_t* bars, v
 
 // Bounded wait of a GEMM producer for a gathered tile.
 __device__ __forceinline__ bool ag_wait(const int* flag, int target, volatile int* abort_flag) {
+  if (!WX_CHK(flag != nullptr && target > 0, 2003, target, 0)) {
+    *abort_flag = 1;
+    return false;
+  }
   if (ld_acquire_gpu(flag) < target) {
     const long long t0 = clock64();
     while (ld_acquire_gpu(flag) < target) {
@@ -541,6 +555,11 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
         const int n_base = ti.nt * BN;
         const int k_base = d.k0[ti.prob];
         const int nkb = (d.K[ti.prob] + BK - 1) / BK;
+        if (!WX_CHK(ti.mt >= 0 && ti.mt < d.tiles_m[ti.prob] && ti.nt >= 0 && ti.nt < d.tiles_n[ti.prob] && (k_base & 7) == 0,
+                    2004, ti.mt, ti.nt)) {
+          *abort_flag = 1;
+          break;
+        }
         for (int kb = 0; kb < nkb; ++kb) {
           if (AG) {
             if (!B_MN) {
@@ -762,6 +781,7 @@ int fill_args(GemmArgs& args, const GemmCall* calls, int ncalls, int bn) {
     p.row_map = c.row_map;
     p.dyn = c.dyn;
     p.ldd = c.ldd;
+    p.d_rows = c.d_rows;
     p.ldd2 = c.ldd2;
     p.ldr = c.ldr;
     p.M = c.M;
@@ -775,6 +795,9 @@ int fill_args(GemmArgs& args, const GemmCall* calls, int ncalls, int bn) {
 }
 
 }  // namespace
+
+WX_CHK_DEFINE_READER(gemm_check_read)
+int gemm_checked_build() { return WX_CHECKED_BUILD; }
 
 }  // namespace wx
 

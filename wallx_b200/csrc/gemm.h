@@ -46,6 +46,7 @@ struct GemmCall {
   const int* dyn;
   void* D;
   long ldd;
+  long d_rows;  // rows of D in memory (0: unknown); only the range checks of the debug build read it
   void* D2;  // optional raw pre-activation output (bf16), SWIGLU only: [*, ldd2], N wide
   long ldd2;
   const void* bias;      // bf16 [N] or nullptr
@@ -80,5 +81,10 @@ int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* sta
 // shard must be complete before any rank launches (a barrier between the optimizer step and the
 // first gather is the caller's job).
 int gemm_ag_launch(const GemmCall* calls, const AgInfo* ags, int ncalls, cudaStream_t stream, int* status);
+
+// Debug build (-DWX_CHECK): copies out {first violating site, violation count, two values} of this translation
+// unit's range checks and clears the record when `clear`; all zeros in a release build. Returns a CUDA error code.
+int gemm_check_read(long long* out4, int clear);
+int gemm_checked_build();  // 1 when the kernels were compiled with -DWX_CHECK
 
 }  // namespace wx

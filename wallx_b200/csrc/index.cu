@@ -6,6 +6,7 @@
 // syncs), csrc/window_index.cu (four kernels, two D2H copies, a cross-block scan race); Python
 // originals modeling_qwen2_5_vl_act.py:929-1149 and modeling_qwen2_5_vl.py:473-547.
 #include "kernels.h"
+#include "check.cuh"
 
 namespace wx {
 
@@ -184,6 +185,7 @@ rope_index_kernel(const long* __restrict__ ids, const int* __restrict__ mask, co
       }
     }
     const int s = cpos[c];
+    if (!WX_CHK(s >= 0 && s < S, 5001, s, S)) continue;
     p0[s] = pt;
     p0[plane + s] = ph;
     p0[2 * plane + s] = pw;
@@ -222,6 +224,7 @@ __global__ void vit_rot_pos_kernel(const float* __restrict__ inv_freq, int F, co
   const int hpos = brow * merge + within / merge;
   const int wpos = bcol * merge + within % merge;
   const float fr = inv_freq[f];
+  if (!WX_CHK(patch >= 0 && patch < N && hpos >= 0 && hpos < h && wpos >= 0 && wpos < w, 5002, patch, hpos)) return;
   out[patch * (2 * F) + f] = static_cast<float>(hpos) * fr;
   out[patch * (2 * F) + F + f] = static_cast<float>(wpos) * fr;
 }
@@ -267,12 +270,15 @@ vit_window_index_kernel(const int* __restrict__ grid, int G, int vw, int merge, 
     for (int e = 0; e < rows * cols; ++e) {
       const int rl = e / cols, cl = e - rl * cols;
       const int row = wr * vw + rl, col = wc * vw + cl;
+      if (!WX_CHK(row < gh && col < gw && excl + e < static_cast<long>(t) * gh * gw, 5003, row, col)) continue;
       window_index[s_tok_base + excl + e] = s_tok_base + (static_cast<long>(ti) * gh + row) * gw + col;
     }
   }
 }
 
 }  // namespace
+
+WX_CHK_DEFINE_READER(index_check_read)
 
 int rope_index(const long* ids, const int* mask, const int* img_grid, int n_img, const int* vid_grid, int n_vid,
                const float* sec_per_grid, int B, int S, int merge, long image_id, long video_id, long vstart_id,

@@ -99,7 +99,8 @@ at::Tensor permute_rows(const at::Tensor& x, const at::Tensor& dest, int64_t row
   check_bf16(x, "x");
   c10::cuda::CUDAGuard g(x.device());
   at::Tensor out = at::zeros({rows, x.size(1)}, x.options());
-  WX_CHECK_RC(wx::permute_rows(x.data_ptr(), dest.data_ptr<int>(), out.data_ptr(), x.size(0), x.size(1), cur_stream()),
+  WX_CHECK_RC(wx::permute_rows(x.data_ptr(), dest.data_ptr<int>(), out.data_ptr(), x.size(0), x.size(1), cur_stream(),
+                               static_cast<int>(rows)),
               "permute_rows");
   return out;
 }
@@ -109,7 +110,8 @@ at::Tensor gather_rows(const at::Tensor& x, const at::Tensor& idx) {
   TORCH_CHECK(idx.scalar_type() == at::kInt && idx.is_cuda() && idx.is_contiguous());
   c10::cuda::CUDAGuard g(x.device());
   at::Tensor out = at::empty({idx.numel(), x.size(1)}, x.options());
-  WX_CHECK_RC(wx::gather_rows(x.data_ptr(), idx.data_ptr<int>(), out.data_ptr(), idx.numel(), x.size(1), cur_stream()),
+  WX_CHECK_RC(wx::gather_rows(x.data_ptr(), idx.data_ptr<int>(), out.data_ptr(), idx.numel(), x.size(1), cur_stream(),
+                              static_cast<int>(x.size(0))),
               "gather_rows");
   return out;
 }

@@ -7,6 +7,7 @@
 // ATen chains behind Qwen2RMSNorm (modeling_qwen2_5_vl.py:122-139), SiLU*mul, CrossEntropyLoss
 // and torch.optim.AdamW (qwen_vl_act_trainer.py:577-581).
 #include "kernels.h"
+#include "check.cuh"
 #include "devinfo.h"
 
 #include <cuda_bf16.h>
@@ -481,6 +482,7 @@ route_plan_kernel(const int* __restrict__ types, int T, int E, int rows, int* __
   for (int base = 0; base < T; base += ROUTE_THREADS) {
     const int i = base + threadIdx.x;
     const int tt = (i < T) ? types[i] : -1;
+    if (i < T) (void)WX_CHK(tt >= 0 && tt < E, 4002, tt, E);  // a token type outside the expert range is dropped
     int my_rank = 0;
     for (int e = 0; e < E; ++e) {
       const unsigned bal = __ballot_sync(0xffffffffu, tt == e);
@@ -493,7 +495,7 @@ route_plan_kernel(const int* __restrict__ types, int T, int E, int rows, int* __
       for (int w2 = 0; w2 < warp; ++w2) off += warp_cnt[tt][w2];
       const int d = off + my_rank;
       dest[i] = d;
-      inv[d] = i;
+      if (WX_CHK(d >= 0 && d < rows, 4001, d, rows)) inv[d] = i;
     }
     __syncthreads();
     if (threadIdx.x < E) {
@@ -507,9 +509,10 @@ route_plan_kernel(const int* __restrict__ types, int T, int E, int rows, int* __
 
 // out[dest[t], :] = x[t, :]; out is zero-filled by the caller.
 __global__ void permute_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ dest,
-                                    __nv_bfloat16* __restrict__ out, int T, int C) {
+                                    __nv_bfloat16* __restrict__ out, int T, int C, int out_rows) {
   const int nchunk = C >> 3;
   for (int row = blockIdx.x; row < T; row += gridDim.x) {
+    if (!WX_CHK(dest[row] >= 0 && (out_rows <= 0 || dest[row] < out_rows) && (C & 7) == 0, 4003, dest[row], out_rows)) continue;
     const BF8* src = reinterpret_cast<const BF8*>(x + static_cast<size_t>(row) * C);
     BF8* dst = reinterpret_cast<BF8*>(out + static_cast<size_t>(dest[row]) * C);
     for (int i = threadIdx.x; i < nchunk; i += blockDim.x) dst[i] = src[i];
@@ -518,9 +521,10 @@ __global__ void permute_rows_kernel(const __nv_bfloat16* __restrict__ x, const i
 
 // out[t, :] = x[idx[t], :]
 __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ idx,
-                                   __nv_bfloat16* __restrict__ out, int T, int C) {
+                                   __nv_bfloat16* __restrict__ out, int T, int C, int src_rows) {
   const int nchunk = C >> 3;
   for (int row = blockIdx.x; row < T; row += gridDim.x) {
+    if (!WX_CHK(idx[row] >= 0 && (src_rows <= 0 || idx[row] < src_rows) && (C & 7) == 0, 4004, idx[row], src_rows)) continue;
     const BF8* src = reinterpret_cast<const BF8*>(x + static_cast<size_t>(idx[row]) * C);
     BF8* dst = reinterpret_cast<BF8*>(out + static_cast<size_t>(row) * C);
     for (int i = threadIdx.x; i < nchunk; i += blockDim.x) dst[i] = src[i];
@@ -657,6 +661,7 @@ ce_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const long* __restrict__
     const float lse = m + logf(se);
     lse_out[row] = lse;
     const long lab = labels[row];
+    (void)WX_CHK(lab == -100 || (lab >= 0 && lab < V), 4005, lab, V);  // neither a class nor the ignore index
     loss[row] = (lab >= 0 && lab < V) ? lse - __bfloat162float(lr[lab]) : 0.f;
   }
 }
@@ -880,19 +885,19 @@ int route_plan(const int* types, int T, int E, int rows, int* dest, int* seg, in
   return static_cast<int>(cudaGetLastError());
 }
 
-int permute_rows(const void* x, const int* dest, void* out, int T, int C, cudaStream_t s) {
+int permute_rows(const void* x, const int* dest, void* out, int T, int C, cudaStream_t s, int out_rows) {
   if (C % 8 != 0) return -1;
   if (T == 0) return 0;
   permute_rows_kernel<<<T < sm_count() * 16 ? T : sm_count() * 16, 128, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), dest,
-                                                                  reinterpret_cast<__nv_bfloat16*>(out), T, C);
+                                                                  reinterpret_cast<__nv_bfloat16*>(out), T, C, out_rows);
   return static_cast<int>(cudaGetLastError());
 }
 
-int gather_rows(const void* x, const int* idx, void* out, int T, int C, cudaStream_t s) {
+int gather_rows(const void* x, const int* idx, void* out, int T, int C, cudaStream_t s, int src_rows) {
   if (C % 8 != 0) return -1;
   if (T == 0) return 0;
   gather_rows_kernel<<<T < sm_count() * 16 ? T : sm_count() * 16, 128, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), idx,
-                                                                 reinterpret_cast<__nv_bfloat16*>(out), T, C);
+                                                                 reinterpret_cast<__nv_bfloat16*>(out), T, C, src_rows);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -949,5 +954,7 @@ int adamw_step(void* p16, float* p32, float* m, float* v, const void* g, long n,
                                                             norm_sq, nullptr);
   return static_cast<int>(cudaGetLastError());
 }
+
+WX_CHK_DEFINE_READER(kernels_check_read)
 
 }  // namespace wx

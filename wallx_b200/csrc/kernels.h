@@ -19,8 +19,10 @@ int swiglu_bwd(const void* dh, const void* gu, void* dgu, int R, int width_gu, l
 int rope_qk(const void* in, void* out, const float* cos_t, const float* sin_t, int T, int W, int n_rot, int D,
             int inverse, cudaStream_t s);
 int route_plan(const int* types, int T, int E, int rows, int* dest, int* seg, int* segk, int* inv, cudaStream_t s);
-int permute_rows(const void* x, const int* dest, void* out, int T, int C, cudaStream_t s);
-int gather_rows(const void* x, const int* idx, void* out, int T, int C, cudaStream_t s);
+// `out_rows` / `src_rows` (0: unknown) are the row counts of the scattered-into / gathered-from buffer; only the
+// range checks of the debug build read them.
+int permute_rows(const void* x, const int* dest, void* out, int T, int C, cudaStream_t s, int out_rows = 0);
+int gather_rows(const void* x, const int* idx, void* out, int T, int C, cudaStream_t s, int src_rows = 0);
 // `partials`: fp32 scratch of column_sum_slabs(R) * C elements (need not be cleared)
 int column_sum_slabs(int R);
 int column_sum(const void* x, float* partials, void* out_bf16, int R, int C, cudaStream_t s);
@@ -38,5 +40,10 @@ int rope_index(const long* ids, const int* mask, const int* img_grid, int n_img,
                float tokens_per_second, long* pos, long* deltas, int* status, cudaStream_t s);
 int vit_rot_pos(const float* inv_freq, int F, const int* grid, int G, int merge, float* out, long N, cudaStream_t s);
 int vit_window_index(const int* grid, int G, int vw, int merge, long* window_index, int* cu_seqlens, cudaStream_t s);
+
+// Debug build (-DWX_CHECK): {first violating site, violation count, two values} of each translation unit's range
+// checks, cleared when `clear`; all zeros in a release build. Return a CUDA error code.
+int kernels_check_read(long long* out4, int clear);
+int index_check_read(long long* out4, int clear);
 
 }  // namespace wx

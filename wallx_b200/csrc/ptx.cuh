@@ -11,6 +11,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "check.cuh"
+
 namespace wx {
 
 #ifndef WX_WAIT_LIMIT_NS
@@ -79,6 +81,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 #define WX_WAIT_LIMIT_CYCLES 4000000000ll  // about 2 s at 1.9 GHz
 #endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (!WX_CHK(parity <= 1u && (smem_u32(bar) & 7u) == 0u, 1001, parity, smem_u32(bar))) {  // a phase is one bit
+    *abort_flag = 1;
+    return false;
+  }
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = 0;
   uint32_t it = 0;
@@ -105,6 +111,8 @@ __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tmap) {
 // transaction bytes. c0 is the innermost coordinate (c0 * elemsize must be a multiple of 16 B).
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, uint64_t* bar,
                                             int c0, int c1) {
+  // bf16 tiles: the innermost coordinate must be a multiple of 8 elements (16 bytes), the destination 128-byte aligned
+  if (!WX_CHK((c0 & 7) == 0 && (smem_u32(smem_dst) & 127u) == 0u, 1002, c0, c1)) return;
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
@@ -113,18 +121,25 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* t
 }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, const void* smem_src, int c0,
                                              int c1) {
+  if (!WX_CHK((c0 & 7) == 0 && c0 >= 0 && c1 >= 0, 1003, c0, c1)) return;  // stores never start at a negative coordinate
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap),
                "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
                : "memory");
 }
 // Untiled bulk copies (both addresses 16-byte aligned, size a multiple of 16 bytes).
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  if (!WX_CHK(((reinterpret_cast<uintptr_t>(gsrc) | smem_u32(smem_dst) | bytes) & 15u) == 0u && bytes != 0u, 1004,
+              reinterpret_cast<uintptr_t>(gsrc), bytes))
+    return;
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                    smem_u32(smem_dst)),
                "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
 __device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  if (!WX_CHK(((reinterpret_cast<uintptr_t>(gdst) | smem_u32(smem_src) | bytes) & 15u) == 0u && bytes != 0u, 1005,
+              reinterpret_cast<uintptr_t>(gdst), bytes))
+    return;
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
                "r"(bytes)
                : "memory");
@@ -219,6 +234,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
 // CTA of the pair (no multicast: every CTA loads its own operands).
 __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* tmap, uint32_t bar_cluster_addr,
                                                  int c0, int c1) {
+  if (!WX_CHK((c0 & 7) == 0 && (smem_u32(smem_dst) & 127u) == 0u, 1006, c0, c1)) return;
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
@@ -261,6 +277,12 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane (base_lane + i),
 // columns [col, col+32).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  // tensor memory has 512 columns and 128 lanes; a warp reads the lane quarter that matches its index
+  if (!WX_CHK((taddr & 0xffffu) + 32u <= 512u && ((taddr >> 16) & 31u) == 0u && (taddr >> 16) < 128u, 1007, taddr & 0xffffu, taddr >> 16)) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) r[i] = 0u;
+    return;
+  }
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -286,6 +308,7 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
 
 
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  if (!WX_CHK((taddr & 0xffffu) + 32u <= 512u && ((taddr >> 16) & 31u) == 0u && (taddr >> 16) < 128u, 1008, taddr & 0xffffu, taddr >> 16)) return;
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
       "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "

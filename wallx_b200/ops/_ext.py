@@ -39,35 +39,45 @@ NVCC_FLAGS = [
     "-v",
 ]
 
+# Debug variant: the same sources with -DWX_CHECK (range checks in the kernels, csrc/check.cuh), built into its own
+# directory and loaded instead of the release build when WALLX_CHECKED=1.
+CHECKED = os.environ.get("WALLX_CHECKED", "0") == "1"
+CHECKED_NAME = "_wallx_C_checked"
+CHECKED_DIR = os.path.join(_PKG, "_build_checked")
+
 _lock = threading.Lock()
 _mod = None
 _tried = False
 
 
-def so_path() -> str:
-    return os.path.join(BUILD_DIR, EXT_NAME + ".so")
+def so_path(checked: bool = None) -> str:
+    checked = CHECKED if checked is None else checked
+    return os.path.join(CHECKED_DIR, CHECKED_NAME + ".so") if checked else os.path.join(BUILD_DIR, EXT_NAME + ".so")
 
 
-def build(verbose: bool = False):
-    """Compile every CUDA source for sm_100a (cross-compiles without a GPU) and load the result."""
+def build(verbose: bool = False, checked: bool = False):
+    """Compile every CUDA source for sm_100a (cross-compiles without a GPU) and load the result.
+    ``checked`` builds the debug variant with the kernels' range checks compiled in."""
     global _mod, _tried
     from torch.utils import cpp_extension
 
-    os.makedirs(BUILD_DIR, exist_ok=True)
+    out_dir = CHECKED_DIR if checked else BUILD_DIR
+    os.makedirs(out_dir, exist_ok=True)
     srcs = [os.path.join(CSRC, s) for s in SOURCES]
     mod = cpp_extension.load(
-        name=EXT_NAME,
+        name=CHECKED_NAME if checked else EXT_NAME,
         sources=srcs,
         extra_cflags=["-O3", "-std=c++17"],
-        extra_cuda_cflags=NVCC_FLAGS,
+        extra_cuda_cflags=NVCC_FLAGS + (["-DWX_CHECK"] if checked else []),
         extra_include_paths=[CSRC],
-        build_directory=BUILD_DIR,
+        build_directory=out_dir,
         verbose=verbose,
         with_cuda=True,
     )
-    with _lock:
-        _mod = mod
-        _tried = True
+    if checked == CHECKED:
+        with _lock:
+            _mod = mod
+            _tried = True
     return mod
 
 
@@ -83,10 +93,11 @@ def _load_prebuilt():
         path = tagged[-1]
     import torch  # noqa: F401  (libtorch symbols must be loaded first)
 
-    spec = importlib.util.spec_from_file_location(EXT_NAME, path)
+    name = CHECKED_NAME if CHECKED else EXT_NAME
+    spec = importlib.util.spec_from_file_location(name, path)
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
-    sys.modules[EXT_NAME] = mod
+    sys.modules[name] = mod
     return mod
 
 
