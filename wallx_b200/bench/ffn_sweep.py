@@ -90,6 +90,28 @@ def run_ours(args, dev, world, rank, barrier):
             sharded.append(pair)
         torch.cuda.synchronize()
         dist.barrier()
+        zero3 = None
+        if not args.no_bwd:
+            # the training-engine form of the same four weights: one row-sharded unit in symmetric memory
+            from wallx_b200.parallel.symm import SymmComm
+            from wallx_b200.parallel.zero3 import GatherWorkspace as GW, RowShardedBuffer
+
+            symm = SymmComm(dist.group.WORLD, dev)
+            named = []
+            for e, ex in enumerate(experts):
+                twin = SwiGLUFFN(HIDDEN, widths[e], bias=False).to(torch.bfloat16).to(dev)
+                twin.load_state_dict(ex.state_dict())
+                named += [(f"moe.experts.{e}.gate_up_weight", twin.gate_up_weight), (f"moe.experts.{e}.down_weight", twin.down_weight)]
+            a, b = RowShardedBuffer.sizes([p for _, p in named], world)
+            symm.reserve(a, dtype=torch.bfloat16, grad_elems=b)
+            buf = RowShardedBuffer(named, world, rank, name="ffn", alloc=(symm.alloc_param, symm.alloc_grad), mode="gathered")
+            symm.register_buffers([buf])
+            ws2 = GW(max(R * C for R, C in buf.shapes), dev, slots=2)
+            flags = torch.zeros(buf.flag_words(), dtype=torch.int32, device=dev)
+            buf.attach_gather(symm.param_ptrs, ws2, flags)
+            zero3 = {"symm": symm, "buf": buf, "weights": [(named[0][1], named[1][1]), (named[2][1], named[3][1])]}
+            torch.cuda.synchronize()
+            dist.barrier()
     out = []
     for T in args.tokens:
         for frac in args.fracs:
@@ -131,6 +153,20 @@ def run_ours(args, dev, world, rank, barrier):
                 ag_launch(sp, [sharded[e][1] for e in range(2)])
                 return y
 
+            def fwd_bwd_sharded():
+                # what one layer's FFN costs in a ZeRO-3 training step: forward and dgrad GEMMs gather the weights from
+                # their owners inside the kernels, the wgrad GEMMs add into local bf16 buffers, and every rank reduces its
+                # rows of those buffers by peer loads (csrc/comm.cu rs_reduce) behind a flag barrier
+                x = xs[it[0] & 1]
+                it[0] += 1
+                xp = _PermuteFn.apply(x, plan)
+                y = F_.moe_ffn(xp, None, plan, zero3["weights"])
+                y.backward(dy)
+                x.grad = None
+                zero3["symm"].begin_step()
+                zero3["symm"].reduce_scatter_unit(0)
+                zero3["buf"].grad.zero_()
+
             flops_f = 2.0 * HIDDEN * 3 * ((T - n_act) * widths[0] + n_act * widths[1])
             rec = {"impl": "ours", "tokens": T, "action_frac": frac, "n_gpus": world, "hidden": HIDDEN,
                    "ffn": list(widths), "dtype": "bf16"}
@@ -149,6 +185,10 @@ def run_ours(args, dev, world, rank, barrier):
                     rec["max_abs_diff_vs_unsharded"] = float((a.float() - b.float()).abs().max())
             if sharded is None and not args.no_bwd:
                 rec["fwd_bwd_ms"] = _time(fwd_bwd_local, args.iters, args.warmup, barrier)
+            if sharded is not None and not args.no_bwd:
+                rec["fwd_bwd_ms"] = _time(fwd_bwd_sharded, args.iters, args.warmup, barrier)
+                rec["fwd_bwd_path"] = "gathers fused into forward + dgrad GEMMs, bf16 wgrad, peer-load reduce-scatter of the owner's rows"
+                zero3["symm"].check()
             G.check_status()
             out.append((rec, flops_f))
     return out
@@ -189,6 +229,32 @@ def run_reference(args, dev, world, rank, barrier):
     blk = SparseMoeBlock(_Cfg(), 2).to(torch.bfloat16).to(dev)
     for p in blk.parameters():
         torch.nn.init.normal_(p, std=0.02)
+    if args.ref_path == "cutlass":
+        # The reference ships a CUTLASS grouped GEMM for the two experts (csrc/dual_asym_grouped_gemm.cu:308-366,
+        # wrapper wall_x/fusions/ops.py:147) that its model never calls. This is that kernel put where the expert loop
+        # is: the reference's own permute / unpermute ops around three asym_dual_gmm launches and an unfused SiLU * up.
+        from wall_x.fusions import ops as ref_ops  # reference
+
+        class CutlassMoe(torch.nn.Module):
+            def __init__(self, inner):
+                super().__init__()
+                self.experts = inner.experts
+
+            def forward(self, hidden_states, experts_indices, start, end):
+                b, s_, h = hidden_states.size()
+                x = hidden_states.view(-1, h)
+                idx = experts_indices.view(-1)
+                probs = torch.ones_like(idx, dtype=torch.float32).view(-1, 1)
+                xp, row_map = ref_ops.permute(x, idx)
+                e0, e1 = self.experts[0], self.experts[1]
+                x0, x1 = xp[start[0]:end[0]], xp[start[1]:end[1]]
+                g0, g1 = ref_ops.asym_dual_gmm(x0, x1, e0.gate_proj.weight, e1.gate_proj.weight, trans_b=True)
+                u0, u1 = ref_ops.asym_dual_gmm(x0, x1, e0.up_proj.weight, e1.up_proj.weight, trans_b=True)
+                h0, h1 = torch.nn.functional.silu(g0) * u0, torch.nn.functional.silu(g1) * u1
+                y0, y1 = ref_ops.asym_dual_gmm(h0, h1, e0.down_proj.weight, e1.down_proj.weight, trans_b=True)
+                return ref_ops.unpermute(torch.cat([y0, y1], dim=0), row_map, probs).view(b, s_, h)
+
+        blk = CutlassMoe(blk)
     if world > 1:
         from torch.distributed.fsdp import fully_shard
 
@@ -217,12 +283,13 @@ def run_reference(args, dev, world, rank, barrier):
                 blk.zero_grad(set_to_none=True)
 
             flops_f = 2.0 * HIDDEN * 3 * ((T - n_act) * VLM_FFN + n_act * args.action_ffn)
-            rec = {"impl": "reference", "tokens": T, "action_frac": frac, "n_gpus": world, "hidden": HIDDEN,
-                   "ffn": [VLM_FFN, args.action_ffn], "dtype": "bf16"}
+            rec = {"impl": "reference", "ref_path": args.ref_path, "tokens": T, "action_frac": frac, "n_gpus": world,
+                   "hidden": HIDDEN, "ffn": [VLM_FFN, args.action_ffn], "dtype": "bf16"}
             with torch.no_grad():
                 rec["fwd_ms"] = _time(fwd, args.iters, args.warmup, barrier)
             if world > 1:
-                rec["path"] = "torch FSDP2 fully_shard (NCCL all-gather) + reference permute/unpermute + cuBLAS"
+                rec["path"] = ("torch FSDP2 fully_shard (NCCL all-gather, reduce-scatter in backward) + reference permute/unpermute + "
+                               + ("cuBLAS" if args.ref_path == "cublas" else "CUTLASS asym_dual_gmm"))
             if not args.no_bwd:
                 rec["fwd_bwd_ms"] = _time(fwd_bwd, args.iters, args.warmup, barrier)
             out.append((rec, flops_f))
@@ -238,6 +305,8 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--no-bwd", action="store_true")
+    ap.add_argument("--ref-path", default="cublas", choices=["cublas", "cutlass"],
+                    help="reference arm: its shipped model path (per-expert cuBLAS loop) or its dormant CUTLASS grouped GEMM")
     ap.add_argument("--out", default="")
     args = ap.parse_args(argv)
     args.tokens = [int(t) for t in args.tokens.split(",")]
