@@ -60,7 +60,13 @@ def case_gemm(M, N, K, a_mn=False, b_mn=False, flags=0, extra=None, force_bn=0):
             nbytes += M * N * 2
         spec = G.GemmSpec(a, b, out, a_mn=a_mn, b_mn=b_mn, flags=flags, **kw)
         name = "gemm_pair_kernel" if force_bn == 512 else "gemm_kernel"
-        return (lambda: G.launch([spec], force_bn)), name, nbytes, 2.0 * M * N * K, f"M={M} N={N} K={K} a_mn={a_mn} b_mn={b_mn}"
+        # library twin: the bare product through torch.matmul (cuBLAS), without this kernel's epilogue work
+        aa = a.t() if a_mn else a
+        bb = b if b_mn else b.t()
+        lib_out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        lib = lambda: torch.matmul(aa, bb, out=lib_out)
+        return ((lambda: G.launch([spec], force_bn)), name, nbytes, 2.0 * M * N * K,
+                f"M={M} N={N} K={K} a_mn={a_mn} b_mn={b_mn}", lib, "torch.matmul (cuBLAS), bare product")
     return build
 
 
@@ -117,11 +123,37 @@ def _attn(cu, hq, hkv, D, causal, bidir_n, which):
     meta = F_.AttnMeta(cu, "cuda", causal, bid)
     meta.device_tables("cuda")
     fl = sum(4.0 * (cu[i + 1] - cu[i]) ** 2 * D * hq * (0.5 if causal else 1.0) for i in range(len(cu) - 1))
+    # library twin: flash-attn 2 on the same tensors, the call the reference makes (flash_attn_varlen_func; plain
+    # causal for the LLM, i.e. without the bidirectional action block, as its flash path runs it)
+    lib_fwd = lib_bwd = None
+    try:
+        from flash_attn import flash_attn_varlen_func
+
+        q3 = qkv.detach()[:, : hq * D].reshape(T, hq, D).contiguous().requires_grad_(which != "fwd")
+        k3 = qkv.detach()[:, hq * D:(hq + hkv) * D].reshape(T, hkv, D).contiguous().requires_grad_(which != "fwd")
+        v3 = qkv.detach()[:, (hq + hkv) * D:].reshape(T, hkv, D).contiguous().requires_grad_(which != "fwd")
+        cu_t = torch.tensor(cu, dtype=torch.int32, device="cuda")
+        mx = max(cu[i + 1] - cu[i] for i in range(len(cu) - 1))
+
+        def lib_fwd():
+            with torch.no_grad():
+                flash_attn_varlen_func(q3, k3, v3, cu_t, cu_t, mx, mx, causal=causal)
+
+        if which != "fwd":
+            o3 = flash_attn_varlen_func(q3, k3, v3, cu_t, cu_t, mx, mx, causal=causal)
+            g3 = torch.randn_like(o3)
+
+            def lib_bwd():
+                q3.grad = k3.grad = v3.grad = None
+                o3.backward(g3, retain_graph=True)
+    except Exception:  # flash-attn is not importable here: the row simply has no library column
+        lib_fwd = lib_bwd = None
     if which == "fwd":
         def fn():
             with torch.no_grad():
                 F_.attention_packed(qkv, meta, hq, hkv, D)
-        return fn, "attn_fwd_kernel", T * (2 * hq + 2 * hkv) * D * 2, fl, f"T={T} hq={hq} hkv={hkv} d={D}"
+        return (fn, "attn_fwd_kernel", T * (2 * hq + 2 * hkv) * D * 2, fl, f"T={T} hq={hq} hkv={hkv} d={D}", lib_fwd,
+                "flash_attn_varlen_func forward")
     o = F_.attention_packed(qkv, meta, hq, hkv, D)
     g = torch.randn_like(o)
 
@@ -130,7 +162,8 @@ def _attn(cu, hq, hkv, D, causal, bidir_n, which):
         o.backward(g, retain_graph=True)
 
     reg = "attn_dq_kernel" if which == "dq" else "attn_dkdv_kernel"
-    return fn, reg, T * (4 * hq + 4 * hkv) * D * 2, 2.5 * fl, f"backward (delta + dq + dk/dv kernels), T={T} hq={hq} hkv={hkv} d={D}"
+    return (fn, reg, T * (4 * hq + 4 * hkv) * D * 2, 2.5 * fl,
+            f"backward (delta + dq + dk/dv kernels), T={T} hq={hq} hkv={hkv} d={D}", lib_bwd, "flash_attn_varlen_func backward")
 
 
 def case_attn_llm(which):
@@ -259,6 +292,42 @@ def case_reduce_scatter():
     return fn, "rs_reduce_kernel", shard * (2 * world + 4), 0, f"{world} ranks x {shard} bf16 -> fp32 shard"
 
 
+def case_index(which):
+    """The index-generation kernels at the benchmark batch (32 samples x 3 views of 18 x 18 patches, 346 tokens per
+    sample): latency-bound single launches, reported in microseconds."""
+    def build():
+        from wallx_b200.config import wall_oss_config
+        from wallx_b200.data.synthetic import make_batch, make_processor
+        from wallx_b200.ops import _ext
+        from wallx_b200.ops import functional as F_
+        from wallx_b200.ops import index as IX
+
+        C = _ext.get()
+        B, views = 32, 3
+        grid = torch.tensor([[1, 18, 18]] * (B * views), dtype=torch.int64, device="cuda")
+        if which == "rope_index":
+            cfg = wall_oss_config(action_expert_intermediate=2048, num_hidden_layers=1)
+            proc = make_processor(cfg, 2048)
+            b = make_batch(cfg, proc, B, views=views, image_hw=(256, 256), prompt_len=64, horizon=32, mode="flow",
+                           generator=torch.Generator().manual_seed(0))
+            ids, am, g = b["input_ids"].cuda(), b["attention_mask"].cuda(), b["image_grid_thw"].cuda()
+            vc = cfg.vision_config
+            fn = lambda: IX.get_rope_index(ids, g, None, None, am, vc.spatial_merge_size, cfg.image_token_id, cfg.video_token_id,
+                                           cfg.vision_start_token_id, vc.tokens_per_second)
+            return fn, "rope_index_kernel", ids.numel() * (8 + 24), 0, f"ids [{ids.shape[0]}, {ids.shape[1]}], {B * views} images"
+        if which == "vit_rot_pos":
+            inv = 1.0 / (10000.0 ** (torch.arange(0, 40, 2, dtype=torch.float, device="cuda") / 40))
+            n = B * views * 324
+            return (lambda: IX.rot_pos_emb(inv, grid, 2)), "vit_rot_pos_kernel", n * 40 * 4, 0, f"{B * views} grids of 18 x 18 -> [{n}, 40]"
+        if which == "vit_window_index":
+            n = B * views * 81
+            return (lambda: IX.get_window_index(grid, 112, 2, 14)), "vit_window_index_kernel", n * 8, 0, f"{B * views} grids of 18 x 18, 112-pixel windows"
+        T = B * 346
+        tt = (torch.rand(T, device="cuda") < 0.09).to(torch.int32)
+        return (lambda: F_.make_route_plan(tt, 2)), "route_plan_kernel", T * 12, 0, f"{T} tokens, 2 experts"
+    return build
+
+
 CASES = {
     "gemm_qkv": case_gemm(16384, 2560, 2048),
     "gemm_gate_up_swiglu": case_gemm(16384, 22016, 2048, flags=8, extra="swiglu_raw"),
@@ -294,30 +363,40 @@ CASES = {
     "adamw_fp32_grad": case_adamw(True),
     "column_sum": case_column_sum,
     "reduce_scatter_local": case_reduce_scatter,
+    "rope_index": case_index("rope_index"),
+    "vit_rot_pos": case_index("vit_rot_pos"),
+    "vit_window_index": case_index("vit_window_index"),
+    "route_plan": case_index("route_plan"),
 }
 
 
-def run_case(name, iters, profile):
+def run_case(name, iters, profile, no_lib=False):
     from wallx_b200.ops import gemm as G
 
     torch.manual_seed(0)
-    fn, regex, nbytes, flops, note = CASES[name]()
+    built = CASES[name]()
+    fn, regex, nbytes, flops, note = built[:5]
+    lib_fn, lib_name = (built[5], built[6]) if len(built) > 5 else (None, None)
     warm = 1 if profile else 3
     n = 2 if profile else iters
-    for _ in range(warm):
-        fn()
-    torch.cuda.synchronize()
-    ts = []
-    for _ in range(n):
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        fn()
-        e1.record()
+
+    def median_ms(f):
+        for _ in range(warm):
+            f()
         torch.cuda.synchronize()
-        ts.append(e0.elapsed_time(e1))
+        ts = []
+        for _ in range(n):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            f()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    ms = median_ms(fn)
     G.check_status()
-    ts.sort()
-    ms = ts[len(ts) // 2]
     hbm, tf, tag = _peaks()
     rec = {"case": name, "kernel": regex, "ms": round(ms, 4), "note": note}
     if flops:
@@ -328,6 +407,11 @@ def run_case(name, iters, profile):
     rec["peaks"] = f"{hbm} GB/s copy, {tf} TFLOP/s cuBLAS bf16 burst, {tag}"
     if name.endswith("_dq") or name.endswith("_dkdv"):
         rec["timed"] = "whole attention backward (three kernels)"
+    if lib_fn is not None and not profile and not no_lib:
+        lib_ms = median_ms(lib_fn)
+        rec["library"] = lib_name
+        rec["library_ms"] = round(lib_ms, 4)
+        rec["speedup_vs_library"] = round(lib_ms / ms, 3)
     return rec
 
 
@@ -337,6 +421,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--profile", action="store_true")
     ap.add_argument("--list", action="store_true")
+    ap.add_argument("--no-lib", action="store_true", help="skip the library twin (cuBLAS / flash-attn 2) of each case")
     ap.add_argument("--out", default="")
     args = ap.parse_args(argv)
     if args.list:
@@ -349,7 +434,7 @@ def main(argv=None):
     names = list(CASES) if args.case == "all" else args.case.split(",")
     lines = []
     for nm in names:
-        rec = run_case(nm, args.iters, args.profile)
+        rec = run_case(nm, args.iters, args.profile, args.no_lib)
         lines.append(json.dumps(rec))
         print(lines[-1], flush=True)
         torch.cuda.empty_cache()

@@ -144,6 +144,23 @@ ag_push_kernel(PeerPtrs params, const ShardDesc* __restrict__ table, int rank, i
   }
 }
 
+// Same result through the NVSwitch multicast mapping of the parameter arena: one multimem.st per 16 bytes is
+// replicated by the switch into every GPU's copy (this rank's included), so each byte leaves this GPU once instead
+// of once per peer. `mc_base` is the multicast address of the arena, `local` this rank's own mapping (the source).
+__global__ void __launch_bounds__(256)
+ag_push_mc_kernel(void* mc_base, const void* local, const ShardDesc* __restrict__ table) {
+  const ShardDesc d = table[blockIdx.y];
+  const long n8 = WX_CHK(d.n >= 0 && ((d.n | d.arena_off) & 7) == 0 && mc_base != nullptr, 6004, d.arena_off, d.n) ? d.n >> 3 : 0;
+  const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const __nv_bfloat16*>(local) + d.arena_off);
+  float4* dst = reinterpret_cast<float4*>(reinterpret_cast<__nv_bfloat16*>(mc_base) + d.arena_off);
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const float4 x = src[i];
+    asm volatile("multimem.st.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + i), "f"(x.x), "f"(x.y), "f"(x.z), "f"(x.w)
+                 : "memory");
+  }
+}
+
 __global__ void small_allreduce_write_kernel(PeerPtrs scratch, const float* __restrict__ vals, int n, int rank,
                                              int world) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -239,6 +256,15 @@ int ag_push(const PeerPtrs& params, const ShardDesc* table_dev, int nbuf, int ra
   int gx = (sm_count() * 16 + nbuf - 1) / nbuf;
   gx = gx < 8 ? 8 : gx;
   ag_push_kernel<<<dim3(gx, nbuf), 256, 0, s>>>(params, table_dev, rank, world);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int ag_push_multicast(void* mc_base, const void* local_base, const ShardDesc* table_dev, int nbuf, cudaStream_t s) {
+  if (nbuf == 0) return 0;
+  if (mc_base == nullptr || local_base == nullptr) return -1;
+  int gx = (sm_count() * 16 + nbuf - 1) / nbuf;
+  gx = gx < 8 ? 8 : gx;
+  ag_push_mc_kernel<<<dim3(gx, nbuf), 256, 0, s>>>(mc_base, local_base, table_dev);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -38,6 +38,11 @@ int rs_reduce(const PeerPtrs& grads, const ShardDesc* table_dev, int nbuf, int w
 // Copies this rank's bf16 shards (table entries) from its own arena into every peer's arena.
 int ag_push(const PeerPtrs& params, const ShardDesc* table_dev, int nbuf, int rank, int world, cudaStream_t s);
 
+// The same copy through an NVSwitch multicast mapping of the arena (`mc_base`, from the symmetric-memory rendezvous):
+// multimem.st makes the switch replicate every 16 bytes into all GPUs' arenas, so the shard leaves this GPU once.
+// A barrier must follow before anyone reads the parameters, as for ag_push.
+int ag_push_multicast(void* mc_base, const void* local_base, const ShardDesc* table_dev, int nbuf, cudaStream_t s);
+
 // All-reduce (sum) of a small fp32 vector: each rank writes its values into slot `rank` of every
 // peer's scratch [world][n]; after the barrier every rank sums the `world` slots into out.
 int small_allreduce_write(const PeerPtrs& scratch, const float* vals, int n, int rank, int world, cudaStream_t s);

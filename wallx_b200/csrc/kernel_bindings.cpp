@@ -195,6 +195,14 @@ void ag_push(const std::vector<int64_t>& param_ptrs, const at::Tensor& table, in
               "ag_push");
 }
 
+void ag_push_multicast(int64_t mc_ptr, int64_t local_ptr, const at::Tensor& table) {
+  TORCH_CHECK(table.is_cuda() && table.scalar_type() == at::kLong && table.size(1) == 3 && table.is_contiguous());
+  TORCH_CHECK(mc_ptr != 0 && local_ptr != 0, "ag_push_multicast: no multicast mapping");
+  WX_CHECK_RC(wx::ag_push_multicast(reinterpret_cast<void*>(mc_ptr), reinterpret_cast<const void*>(local_ptr),
+                                    reinterpret_cast<const wx::ShardDesc*>(table.data_ptr<int64_t>()), table.size(0), cur_stream()),
+              "ag_push_multicast");
+}
+
 void small_allreduce_write(const std::vector<int64_t>& scratch_ptrs, const at::Tensor& vals, int64_t rank) {
   TORCH_CHECK(vals.is_cuda() && vals.scalar_type() == at::kFloat && vals.is_contiguous());
   WX_CHECK_RC(wx::small_allreduce_write(peer_ptrs(scratch_ptrs), vals.data_ptr<float>(), vals.numel(), rank,
@@ -287,6 +295,7 @@ void register_kernel_bindings(pybind11::module_& m) {
         pybind11::arg("status"), pybind11::arg("timeout_ms") = 2000);
   m.def("rs_reduce", &rs_reduce);
   m.def("ag_push", &ag_push);
+  m.def("ag_push_multicast", &ag_push_multicast);
   m.def("small_allreduce_write", &small_allreduce_write);
   m.def("small_allreduce_sum", &small_allreduce_sum);
 }

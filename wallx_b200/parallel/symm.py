@@ -33,6 +33,12 @@ class SymmComm:
         import torch.distributed as dist
 
         self.timeout_ms = max(1, int(barrier_timeout_s * 1000))
+        # multimem stores for the parameter push when the fabric offers a multicast mapping (WALLX_NVLS=0 turns it off:
+        # tests in which a rank may die keep every multicast object out of the picture)
+        import os
+
+        self.use_multicast = os.environ.get("WALLX_NVLS", "1") != "0"
+        self.param_mc = 0
         import torch.distributed._symmetric_memory as symm_mem
 
         self.symm_mem = symm_mem
@@ -70,7 +76,11 @@ class SymmComm:
         if self.param_arena is None or self.param_arena.numel() < total_elems or self.param_arena.dtype != dtype:
             self.param_arena = None
             self.param_arena = sm.empty(total_elems, dtype=dtype, device=self.device)
-            self.param_ptrs = [int(p) for p in sm.rendezvous(self.param_arena, self.group).buffer_ptrs]
+            hdl = sm.rendezvous(self.param_arena, self.group)
+            self.param_ptrs = [int(p) for p in hdl.buffer_ptrs]
+            # NVSwitch multicast mapping of the arena (0 when the fabric has none): lets the parameter push leave
+            # this GPU once instead of once per peer
+            self.param_mc = int(getattr(hdl, "multicast_ptr", 0) or 0) if self.use_multicast else 0
         if self.grad_arena is None or self.grad_arena.numel() < grad_elems or self.grad_arena.dtype != dtype:
             self.grad_arena = None
             self.grad_arena = sm.empty(grad_elems, dtype=dtype, device=self.device)
@@ -175,6 +185,9 @@ class SymmComm:
 
     def all_gather_params(self, buffers) -> None:
         if self.push_table.shape[0] > 0:
-            _ext.get().ag_push(self.param_ptrs, self.push_table, self.rank)
+            if self.param_mc:
+                _ext.get().ag_push_multicast(self.param_mc, self.param_ptrs[self.rank], self.push_table)
+            else:
+                _ext.get().ag_push(self.param_ptrs, self.push_table, self.rank)
         # all pushes have landed, and every owner has updated its rows, before anyone reads the parameters
         self.barrier()
