@@ -379,7 +379,13 @@ def main():
     host_only = arm.host_ms_per_step()
     ms_dev, ms_e2e_max, host_only = max_over_ranks([ms_dev, ms_e2e if ms_e2e is not None else 0.0, host_only], dev, world)
     global_batch = args.per_gpu_batch * world
-    peak_gb = max_over_ranks([torch.cuda.max_memory_allocated(dev) / 2 ** 30], dev, world)[0]
+    def peak_memory_gb(a):
+        # caching-allocator peak plus the symmetric arenas (bf16 parameters / shards and gradients at N > 1), which
+        # the allocator does not see
+        sym = a.engine.symm.arena_bytes() if a.engine.symm is not None else 0
+        return max_over_ranks([(torch.cuda.max_memory_allocated(dev) + sym) / 2 ** 30], dev, world)[0]
+
+    peak_gb = peak_memory_gb(arm)
     rec = {
         "metric": f"train samples/s, WALL-OSS-{args.mode.upper()}-size fine-tune (max over ranks, device-timed)",
         "value": round(global_batch * args.steps / (ms_dev / 1e3), 3), "unit": "samples/s", "n_gpus": world,
@@ -427,7 +433,7 @@ def main():
         k = max(2, min(args.steps, args.extra_steps))
         ms, host, l = a.timed(k, 2)
         ms = max_over_ranks([ms], dev, world)[0]
-        pk = max_over_ranks([torch.cuda.max_memory_allocated(dev) / 2 ** 30], dev, world)[0]
+        pk = peak_memory_gb(a)
         out = {"value": round(global_batch * k / (ms / 1e3), 3), "unit": "samples/s", "ms_per_step": round(ms / k, 3),
                "steps": k, "warmup": 2, "n_gpus": world, "peak_device_memory_gb": round(pk, 1),
                "host_enqueue_ms_per_step": round(host, 1), "parallelism": a.parallelism(), "loss": l}

@@ -26,7 +26,12 @@ from ..ops import _ext
 from ..ops import gemm as G
 from .zero3 import GatheredWeight, GatherWorkspace
 
-DEFAULT_PULLERS = 16  # copy CTAs per launch (of 148); fixed per weight because the ready flags count their arrivals
+import os as _os
+
+# Copy CTAs per launch (of 148 SMs); fixed per weight because the ready flags count their arrivals. Every copy CTA keeps
+# ten 16 KB bulk loads in flight (about 60 GB/s each over NVLink), and a layer's GEMMs need roughly 100 GB/s of remote
+# weight traffic to stay fed, so a handful suffices; each one is an SM the multiplication does not get.
+DEFAULT_PULLERS = int(_os.environ.get("WALLX_AG_PULLERS", "8"))
 
 
 class ShardedWeight(GatheredWeight):

@@ -106,6 +106,14 @@ class SymmComm:
     def alloc_grad(self, n: int, dtype) -> torch.Tensor:
         return self._take("grad", n, dtype)
 
+    def arena_bytes(self) -> int:
+        """Bytes of the two symmetric arenas that the current engine uses (they are not part of the caching
+        allocator's statistics)."""
+        if self.param_arena is None:
+            return 0
+        e = self.param_arena.element_size()
+        return (self._cursor["param"] + self._cursor["grad"]) * e
+
     def register_buffers(self, buffers) -> None:
         """Build the device tables: per unit the pieces of the gradient arena this rank reduces (one for a flat
         buffer, one per weight for a row-sharded unit) and the pieces of the parameter arena it pushes to its peers
