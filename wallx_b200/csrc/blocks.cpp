@@ -129,7 +129,7 @@ std::pair<Tensor, Tensor> norm_fwd(const Tensor& x, const Tensor& w, double eps,
   return {y, rstd};
 }
 
-// dx = rms_norm backward (+ `add`, the gradient arriving over the residual path), dw
+// dx = rms_norm backward + `add` (the gradient arriving over the residual path, added inside the kernel), dw
 std::pair<Tensor, Tensor> norm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const Tensor& rstd, const OptT& dest,
                                    const Tensor& add) {
   const int T = x.size(0), C = x.size(1);
@@ -138,10 +138,9 @@ std::pair<Tensor, Tensor> norm_bwd(const Tensor& dy, const Tensor& x, const Tens
   Tensor dw = at::empty_like(w);
   Tensor partial = at::empty({wx::rms_norm_bwd_blocks(T), C}, x.options().dtype(at::kFloat));
   WX_RC(wx::rms_norm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), mapped ? dest->data_ptr<int>() : nullptr,
-                         dx.data_ptr(), partial.data_ptr<float>(), dw.data_ptr(), T, C, cur()),
+                         dx.data_ptr(), partial.data_ptr<float>(), dw.data_ptr(), T, C, cur(), add.data_ptr()),
         "rms_norm_bwd");
   g_launches.fetch_add(1, std::memory_order_relaxed);  // the kernel plus its ordered partial reduction
-  dx.add_(add);
   return {dx, dw};
 }
 
@@ -153,12 +152,11 @@ Tensor col_sum(const Tensor& x) {
   return out;
 }
 
-Tensor rope(const Tensor& in, const Tensor& cos_t, const Tensor& sin_t, int64_t n_rot, int64_t d, bool inverse) {
-  Tensor out = at::empty_like(in);
-  WX_RC(wx::rope_qk(in.data_ptr(), out.data_ptr(), cos_t.data_ptr<float>(), sin_t.data_ptr<float>(), in.size(0), in.size(1),
-                    n_rot, d, inverse ? 1 : 0, cur()),
+// Rotates q and k in place (the block owns the buffer; the v columns stay where they are).
+void rope_inplace(Tensor& t, const Tensor& cos_t, const Tensor& sin_t, int64_t n_rot, int64_t d, bool inverse) {
+  WX_RC(wx::rope_qk(t.data_ptr(), t.data_ptr(), cos_t.data_ptr<float>(), sin_t.data_ptr<float>(), t.size(0), t.size(1), n_rot, d,
+                    inverse ? 1 : 0, cur()),
         "rope_qk");
-  return out;
 }
 
 wx::AttnShape attn_shape(const Tensor& qkv, int64_t hq, int64_t hkv, int64_t d, double scale, bool has_bidir, bool causal_self) {
@@ -220,17 +218,16 @@ std::vector<Tensor> block_fwd(const Tensor& x, const Tensor& ln1_w, const WTuple
 
   // ---- attention half
   auto [y1, rstd1] = norm_fwd(x, ln1_w, eps, OptT(), 0, false);
-  Tensor qkv_raw = empty_bf16(T, w_of(w_qkv).size(0), x);
+  Tensor qkv = empty_bf16(T, w_of(w_qkv).size(0), x);
   {
     std::vector<Spec> sp(1);
     sp[0].a = y1;
     sp[0].b = w_of(w_qkv);
-    sp[0].out = qkv_raw;
+    sp[0].out = qkv;
     sp[0].bias = b_qkv;
     launch(sp, {&w_qkv}, status);
   }
-  Tensor qkv = rope(qkv_raw, cos_t, sin_t, n_rot, d, false);
-  qkv_raw = Tensor();
+  rope_inplace(qkv, cos_t, sin_t, n_rot, d, false);
   Tensor o_attn = empty_bf16(T, hq * d, x);
   Tensor lse = at::empty({hq, T}, x.options().dtype(at::kFloat));
   {
@@ -482,8 +479,8 @@ std::vector<Tensor> block_bwd(const Tensor& dout_in, const Tensor& x, const Tens
     g_launches.fetch_add(rep > 1 ? 4 : 2, std::memory_order_relaxed);  // delta, dQ, dK/dV (+ the two partial reductions)
   }
   d_oattn = Tensor();
-  Tensor dqkv_raw = rope(dqkv, cos_t, sin_t, n_rot, d, true);
-  dqkv = Tensor();
+  rope_inplace(dqkv, cos_t, sin_t, n_rot, d, true);
+  Tensor& dqkv_raw = dqkv;
   Tensor dy1 = empty_bf16(T, H, x);
   {
     std::vector<Spec> sp(1);

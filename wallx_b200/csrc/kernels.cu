@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(NORM_THREADS)
 rms_norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                     const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
                     const int* __restrict__ dest, __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int T,
-                    int C) {
+                    int C, const __nv_bfloat16* __restrict__ add) {
   __shared__ float red[32];
   const int nchunk = C >> 3;
   float dwacc[NORM_MAX_CHUNKS][8];
@@ -162,6 +162,12 @@ rms_norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* _
         float o[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) o[e] = rstd * (g[c][e] - xh[c][e] * dot);
+        if (add != nullptr) {  // + the gradient of the residual path, with the rounding of a separate bf16 add
+          float af[8];
+          unpack8(reinterpret_cast<const BF8*>(add + static_cast<size_t>(row) * C)[i], af);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] = bf16_round(o[e]) + af[e];
+        }
         dxr[i] = pack8(o);
       }
     }
@@ -222,7 +228,7 @@ __global__ void __launch_bounds__(256)
 rms_norm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                          const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
                          const int* __restrict__ dest, __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial,
-                         int T) {
+                         int T, const __nv_bfloat16* __restrict__ add) {
   constexpr int C = CH * 256;
   __shared__ float dws[C];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -269,6 +275,12 @@ rms_norm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat
       unpack8(wr[lane + 32 * c], wf);
 #pragma unroll
       for (int e = 0; e < 8; ++e) o[e] = rstd * (df[e] * wf[e] - xf[e] * rstd * dot);
+      if (add != nullptr) {  // + the gradient of the residual path, with the rounding of a separate bf16 add
+        float af[8];
+        unpack8(reinterpret_cast<const BF8*>(add + static_cast<size_t>(row) * C)[lane + 32 * c], af);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = bf16_round(o[e]) + af[e];
+      }
       dxr[lane + 32 * c] = pack8(o);
     }
   }
@@ -332,9 +344,8 @@ swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dh, const __nv_bfloat16* __r
 // values are loaded once per token instead of once per head; the v columns (heads >= n_rot) are
 // copied by the same threads. `inverse` applies the transposed rotation (the backward pass).
 __global__ void __launch_bounds__(256)
-rope_qk_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
-               const float* __restrict__ cos_t, const float* __restrict__ sin_t, int T, int W, int n_rot, int D,
-               int inverse) {
+rope_qk_kernel(const __nv_bfloat16* in, __nv_bfloat16* out, const float* __restrict__ cos_t,
+               const float* __restrict__ sin_t, int T, int W, int n_rot, int D, int inverse, int copy_rest) {
   const int half = D >> 1;
   const int tpr = half >> 3;  // threads per token
   const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -371,7 +382,8 @@ rope_qk_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__
     *reinterpret_cast<BF8*>(orow + h * D + d0) = pack8(oa);
     *reinterpret_cast<BF8*>(orow + h * D + half + d0) = pack8(ob);
   }
-  // pass-through columns, 16 bytes at a time, spread over the token's threads
+  // pass-through columns, 16 bytes at a time, spread over the token's threads (nothing to do in place)
+  if (!copy_rest) return;
   const int base = n_rot * D;
   for (int off = base + d0; off < W; off += tpr * 8)
     *reinterpret_cast<BF8*>(orow + off) = *reinterpret_cast<const BF8*>(row + off);
@@ -379,13 +391,13 @@ rope_qk_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__
 
 // Variant for few tokens (decoding, the denoise loop): one thread per (token, head, 8-channel chunk), so that
 // a handful of tokens still spreads over many SMs; it reloads cos/sin per head.
-__global__ void rope_qk_chunk_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out,
-                               const float* __restrict__ cos_t, const float* __restrict__ sin_t, int T, int W,
-                               int n_rot, int D, int inverse) {
+__global__ void rope_qk_chunk_kernel(const __nv_bfloat16* in, __nv_bfloat16* out, const float* __restrict__ cos_t,
+                                     const float* __restrict__ sin_t, int T, int W, int n_rot, int D, int inverse,
+                                     int copy_rest) {
   const int half = D >> 1;
   const int chunks_per_head = half >> 3;
   const int rot_chunks = n_rot * chunks_per_head;
-  const int copy_chunks = (W - n_rot * D) >> 3;
+  const int copy_chunks = copy_rest ? (W - n_rot * D) >> 3 : 0;
   const int per_row = rot_chunks + copy_chunks;
   const long idx = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<long>(T) * per_row) return;
@@ -824,7 +836,8 @@ int rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, const int* 
 int rms_norm_bwd_blocks(int T) { return T < sm_count() * 2 ? (T > 0 ? T : 1) : sm_count() * 2; }
 
 int rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const int* dest, void* dx,
-                 float* dw_partial, void* dw, int T, int C, cudaStream_t s) {
+                 float* dw_partial, void* dw, int T, int C, cudaStream_t s, const void* add) {
+  const __nv_bfloat16* addb = reinterpret_cast<const __nv_bfloat16*>(add);
   if (C % 8 != 0 || C > NORM_THREADS * 8 * NORM_MAX_CHUNKS) return -1;
   const int grid = rms_norm_bwd_blocks(T);
   if (C % 256 == 0 && C <= 2048) {  // one warp per row; the number of partial rows is the same
@@ -833,7 +846,7 @@ int rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd
     const __nv_bfloat16* wb = reinterpret_cast<const __nv_bfloat16*>(w);
     __nv_bfloat16* dxb = reinterpret_cast<__nv_bfloat16*>(dx);
     switch (C / 256) {
-#define WX_CASE(n) case n: rms_norm_bwd_warp_kernel<n><<<grid, 256, 0, s>>>(dyb, xb, wb, rstd, dest, dxb, dw_partial, T); break;
+#define WX_CASE(n) case n: rms_norm_bwd_warp_kernel<n><<<grid, 256, 0, s>>>(dyb, xb, wb, rstd, dest, dxb, dw_partial, T, addb); break;
       WX_CASE(1) WX_CASE(2) WX_CASE(3) WX_CASE(4) WX_CASE(5) WX_CASE(6) WX_CASE(7) WX_CASE(8)
 #undef WX_CASE
     }
@@ -842,7 +855,7 @@ int rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd
   }
   rms_norm_bwd_kernel<<<grid, NORM_THREADS, 0, s>>>(
       reinterpret_cast<const __nv_bfloat16*>(dy), reinterpret_cast<const __nv_bfloat16*>(x),
-      reinterpret_cast<const __nv_bfloat16*>(w), rstd, dest, reinterpret_cast<__nv_bfloat16*>(dx), dw_partial, T, C);
+      reinterpret_cast<const __nv_bfloat16*>(w), rstd, dest, reinterpret_cast<__nv_bfloat16*>(dx), dw_partial, T, C, addb);
   reduce_partials_kernel<<<(C + 255) / 256, 256, 0, s>>>(dw_partial, reinterpret_cast<__nv_bfloat16*>(dw), grid, C);
   return static_cast<int>(cudaGetLastError());
 }
@@ -866,16 +879,19 @@ int rope_qk(const void* in, void* out, const float* cos_t, const float* sin_t, i
   if (total == 0) return 0;
   // few tokens: too little parallelism with one thread per 8-channel column; head dims that are not a
   // multiple of 128 (ViT: 80): a token's threads would read 80-byte pieces
+  // in place (in == out): every thread reads its rotation pairs before it writes them, and the columns that are not
+  // rotated (v) need no copy, which saves a third of the traffic of a q|k|v buffer with as many v as q heads
+  const int copy_rest = (in != out) ? 1 : 0;
   if (total < static_cast<long>(sm_count()) * 256 || D % 128 != 0) {
-    const long per_row = static_cast<long>(n_rot) * (D / 16) + (W - n_rot * D) / 8;
+    const long per_row = static_cast<long>(n_rot) * (D / 16) + (copy_rest ? (W - n_rot * D) / 8 : 0);
     rope_qk_chunk_kernel<<<static_cast<unsigned>((per_row * T + 255) / 256), 256, 0, s>>>(
         reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(out), cos_t, sin_t, T, W, n_rot, D,
-        inverse);
+        inverse, copy_rest);
     return static_cast<int>(cudaGetLastError());
   }
   rope_qk_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, s>>>(
       reinterpret_cast<const __nv_bfloat16*>(in), reinterpret_cast<__nv_bfloat16*>(out), cos_t, sin_t, T, W, n_rot, D,
-      inverse);
+      inverse, copy_rest);
   return static_cast<int>(cudaGetLastError());
 }
 

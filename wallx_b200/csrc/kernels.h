@@ -12,10 +12,13 @@ namespace wx {
 int rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, const int* dest, int T, int C, float eps,
                  cudaStream_t s);
 int rms_norm_bwd_blocks(int T);
+// `add` (optional, bf16 [T, C]): added to dx with the rounding of a separate bf16 add (the gradient that arrives
+// over the residual connection around the normalised branch).
 int rms_norm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const int* dest, void* dx,
-                 float* dw_partial, void* dw, int T, int C, cudaStream_t s);
+                 float* dw_partial, void* dw, int T, int C, cudaStream_t s, const void* add = nullptr);
 int swiglu_bwd(const void* dh, const void* gu, void* dgu, int R, int width_gu, long ld_dh, long ld_gu,
                cudaStream_t s);
+// `out` may be `in` (in place: the columns that are not rotated are then left alone instead of copied).
 int rope_qk(const void* in, void* out, const float* cos_t, const float* sin_t, int T, int W, int n_rot, int D,
             int inverse, cudaStream_t s);
 int route_plan(const int* types, int T, int E, int rows, int* dest, int* seg, int* segk, int* inv, cudaStream_t s);
