@@ -451,10 +451,6 @@ std::vector<Tensor> block_bwd(const Tensor& dout_in, const Tensor& x, const Tens
     sp[0].out = d_oattn;
     launch(sp, {&w_o}, status);
   }
-  {
-    std::vector<Spec> sp{wgrad_spec(dx2, o_attn, w_o, dW_o, false)};
-    launch(sp, {nullptr}, status);
-  }
   if (has_b_o) db_o = col_sum(dx2);
   Tensor dqkv = at::empty_like(qkv);
   {
@@ -491,8 +487,10 @@ std::vector<Tensor> block_bwd(const Tensor& dout_in, const Tensor& x, const Tens
     launch(sp, {&w_qkv}, status);
   }
   {
-    std::vector<Spec> sp{wgrad_spec(dqkv_raw, y1, w_qkv, dW_qkv, false)};
-    launch(sp, {nullptr}, status);
+    // the two attention weight gradients share one launch: each alone leaves most of its last wave of tiles idle
+    // (weights of a few thousand rows and columns give barely more tiles than SMs), together they fill it
+    std::vector<Spec> sp{wgrad_spec(dqkv_raw, y1, w_qkv, dW_qkv, false), wgrad_spec(dx2, o_attn, w_o, dW_o, false)};
+    launch(sp, {nullptr, nullptr}, status);
   }
   if (has_b_qkv) db_qkv = col_sum(dqkv_raw);
   auto [dx, dln1] = norm_bwd(dy1, x, ln1_w, rstd1, OptT(), dx2);  // + gradient of the attention's residual path
