@@ -245,11 +245,15 @@ rms_norm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat
     const BF8* xr = reinterpret_cast<const BF8*>(x + static_cast<size_t>(row) * C);
     const BF8* gr = reinterpret_cast<const BF8*>(dy + static_cast<size_t>(grow) * C);
     const float rstd = rstd_in[row];
-    BF8 xraw[CH], graw[CH];
+    BF8 xraw[CH], graw[CH], araw[CH];
+    // all loads of the row are issued together (the residual-path gradient too: loading it after the reduction
+    // would put a second memory round trip on every row's critical path)
+    const BF8* ar = add != nullptr ? reinterpret_cast<const BF8*>(add + static_cast<size_t>(row) * C) : nullptr;
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
       xraw[c] = xr[lane + 32 * c];
       graw[c] = gr[lane + 32 * c];
+      if (ar != nullptr) araw[c] = ar[lane + 32 * c];
     }
     float dot = 0.f;
 #pragma unroll
@@ -275,9 +279,9 @@ rms_norm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat
       unpack8(wr[lane + 32 * c], wf);
 #pragma unroll
       for (int e = 0; e < 8; ++e) o[e] = rstd * (df[e] * wf[e] - xf[e] * rstd * dot);
-      if (add != nullptr) {  // + the gradient of the residual path, with the rounding of a separate bf16 add
+      if (ar != nullptr) {  // + the gradient of the residual path, with the rounding of a separate bf16 add
         float af[8];
-        unpack8(reinterpret_cast<const BF8*>(add + static_cast<size_t>(row) * C)[lane + 32 * c], af);
+        unpack8(araw[c], af);
 #pragma unroll
         for (int e = 0; e < 8; ++e) o[e] = bf16_round(o[e]) + af[e];
       }
