@@ -244,6 +244,8 @@ def _ag_call(x, shards, transpose_w, flags=0, rank=0, n_pullers=0, epoch_flags=N
     (4, 1280, 1024, 4000, 2, 5),     # 320 rows per rank: shards straddle 256-row tiles
     (8, 2048, 11008, 700, 7, 3),     # down-projection shape: 22 KB rows, 16-byte-multiple chunks
     (2, 768, 136, 129, 0, 40),       # more pullers than chunks per tile
+    (2, 2560, 2048, 8192, 1, 0),     # enough 256 x 256 tiles for the CTA-pair kernel (copy clusters + GEMM pairs)
+    (8, 22016, 2048, 4096, 3, 8),    # gate/up shape on CTA pairs, 2752 rows per rank
 ])
 def test_gemm_gathered_weight_forward(world, rows, cols, M, rank, n_pullers):
     from wallx_b200.ops import gemm as G
@@ -269,7 +271,8 @@ def test_gemm_gathered_weight_forward(world, rows, cols, M, rank, n_pullers):
     torch.testing.assert_close(y2.float(), ref * 0.5, atol=2e-2 * ref.abs().max().item(), rtol=2e-2)
 
 
-@pytest.mark.parametrize("world,rows,cols,M", [(2, 2560, 2048, 1000), (4, 1280, 1024, 515), (1, 256, 512, 128)])
+@pytest.mark.parametrize("world,rows,cols,M", [(2, 2560, 2048, 1000), (4, 1280, 1024, 515), (1, 256, 512, 128),
+                                               (2, 2560, 2048, 8192), (8, 22016, 2048, 4096)])  # the last two: CTA pairs
 def test_gemm_gathered_weight_dgrad(world, rows, cols, M):
     from wallx_b200.ops import gemm as G
 

@@ -893,8 +893,9 @@ int gemm_ag_launch(const GemmCall* calls, const AgInfo* ags, int ncalls, cudaStr
   const int rc = fill_args(args, calls, ncalls, 256);
   if (rc != 0) return rc;
   const int sms = num_sms();
-  int np = ags[0].n_pullers > 0 ? ags[0].n_pullers : 16;
-  if (np > sms / 2) np = sms / 2;
+  int np = ags[0].n_pullers > 0 ? ags[0].n_pullers : 8;
+  np = (np + 1) & ~1;  // even: on CTA pairs whole clusters copy, and both kernels must count the same arrivals per tile
+  if (np > sms / 2) np = (sms / 2) & ~1;
   long tiles = 0;
   for (int i = 0; i < ncalls; ++i) {
     const GemmCall& call = calls[i];
@@ -935,6 +936,35 @@ int gemm_ag_launch(const GemmCall* calls, const AgInfo* ags, int ncalls, cudaStr
     tiles += static_cast<long>((call.M + BM - 1) / BM) * ((call.N + 255) / 256);
   }
   if (tiles <= 0) return 0;
+  // CTA pairs (256 x 256 tiles) when the problem has enough of them to fill the pairs that remain beside the copy
+  // CTAs; the tensor maps then use 128-row B boxes (each CTA of a pair loads its half of the 256 weight rows)
+  {
+    static const bool pair_ok = [] {
+      const char* e = getenv("WX_AG_PAIR");
+      return e == nullptr || atoi(e) != 0;
+    }();
+    long ptiles = 0;
+    int max_n = 0;
+    for (int i = 0; i < ncalls; ++i) {
+      ptiles += static_cast<long>((calls[i].M + 255) / 256) * ((calls[i].N + 255) / 256);
+      max_n = calls[i].N > max_n ? calls[i].N : max_n;
+    }
+    const int np2 = np;  // even (see above): whole clusters copy
+    if (pair_ok && max_n > 128 && ptiles >= (sms - np2) / 2) {
+      GemmArgs pargs;
+      if (fill_args(pargs, calls, ncalls, 128) == 0) {
+        pargs.ag[0] = args.ag[0];
+        pargs.ag[1] = args.ag[1];
+        for (int i = 0; i < ncalls; ++i) {
+          pargs.ag[i].n_pullers = np2;
+          pargs.ag[i].target = np2 * ags[i].epoch;
+        }
+        const int prc = b_mn ? launch_pair_ag_t<true>(pargs, ptiles, np2, stream, status)
+                             : launch_pair_ag_t<false>(pargs, ptiles, np2, stream, status);
+        if (prc != -10) return prc;
+      }
+    }
+  }
   const int workers = tiles < sms - np ? static_cast<int>(tiles) : sms - np;
   const int grid = workers + np;
   if (!b_mn) return launch_t<256, false, false, true>(args, grid, stream, status);

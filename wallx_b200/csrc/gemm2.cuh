@@ -30,9 +30,20 @@ constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + 256;
 constexpr int kPairTileM = 2 * BM;
 constexpr int kPairTileN = 256;
 
-template <bool A_MN, bool B_MN>
+// AG: the weight operand is gathered from the ranks' shards while the kernel runs (see AgInfo in gemm.h). The first
+// `n_pullers` CTAs of the grid (whole clusters, so an even number) copy instead of multiplying: one thread of each
+// runs the same bulk-copy ring as in the single-CTA kernel; the GEMM pairs take the 256-row weight tiles in arrival
+// order and their producers wait (bounded) on a tile's flag before its first B load.
+template <bool A_MN, bool B_MN, bool AG = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
+  static_assert(!AG || !A_MN, "gathered-weight mode: K-major A");
+  static_assert(!AG || kPairStages * kPairStageBytes >= kAgRing * kAgChunkMax, "ring must fit in the stage area");
+  static_assert(!AG || 2 * kPairStages + 4 >= kAgRing, "not enough barriers for the ring");
+  const int n_pull = AG ? args.ag[0].n_pullers : 0;
+  const bool puller = AG && static_cast<int>(blockIdx.x) < n_pull;
+  const int rot0 = (AG && !B_MN) ? args.ag[0].rot : 0;
+  const int rot1 = (AG && !B_MN) ? args.ag[1].rot : 0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes);
@@ -48,13 +59,17 @@ gemm_pair_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status
   const bool leader = rank == 0;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kPairStages; ++s) {
-      mbar_init(&full_bar[s], 1);   // used in the leader only: its producer's arrive + both CTAs' bytes
-      mbar_init(&empty_bar[s], 1);  // one commit per use, in each CTA
-    }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(&tfull_bar[a], 1);   // one commit per tile, in each CTA
-      mbar_init(&tempty_bar[a], 2 * kEpiWarps);  // used in the leader only: the epilogue warps of both CTAs
+    if (puller) {
+      for (int s = 0; s < kAgRing; ++s) mbar_init(&full_bar[s], 1);  // the copy ring uses the first barriers
+    } else {
+      for (int s = 0; s < kPairStages; ++s) {
+        mbar_init(&full_bar[s], 1);   // used in the leader only: its producer's arrive + both CTAs' bytes
+        mbar_init(&empty_bar[s], 1);  // one commit per use, in each CTA
+      }
+      for (int a = 0; a < 2; ++a) {
+        mbar_init(&tfull_bar[a], 1);   // one commit per tile, in each CTA
+        mbar_init(&tempty_bar[a], 2 * kEpiWarps);  // used in the leader only: the epilogue warps of both CTAs
+      }
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -73,10 +88,16 @@ gemm_pair_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status
   Dims d;
   load_dims<kPairTileN, kPairTileM>(args, d);
   const int total_tiles = d.tiles[0] + d.tiles[1];
-  const int pair = static_cast<int>(blockIdx.x) >> 1;
-  const int npair = static_cast<int>(gridDim.x) >> 1;
+  const int pair = (static_cast<int>(blockIdx.x) - n_pull) >> 1;
+  const int npair = (static_cast<int>(gridDim.x) - n_pull) >> 1;
 
-  if (warp == 0) {
+  if (puller) {
+    if (threadIdx.x == 0) {
+      int seq = 0;  // chunk sequence number carries over: the ring's barrier phases continue
+      for (int i = 0; i < args.nprob; ++i)
+        if (!ag_pull(args.ag[i], static_cast<int>(blockIdx.x), smem, full_bar, abort_flag, seq)) break;
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
       for (int i = 0; i < args.nprob; ++i) {
@@ -86,14 +107,32 @@ gemm_pair_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
+      int ag_ready[2] = {0, 0};  // MN-major B: 256-row blocks of the weight known to be in place
       for (int t = pair; t < total_tiles && ok; t += npair) {
-        const TileInfo ti = decode_tile(d, t);
+        const TileInfo ti = decode_tile(d, t, AG, rot0, rot1);
         const Problem& p = args.p[ti.prob];
         const int m_base = d.m0[ti.prob] + ti.mt * kPairTileM + static_cast<int>(rank) * BM;
         const int n_base = ti.nt * kPairTileN + static_cast<int>(rank) * 128;
         const int k_base = d.k0[ti.prob];
         const int nkb = (d.K[ti.prob] + BK - 1) / BK;
         for (int kb = 0; kb < nkb; ++kb) {
+          if (AG) {
+            if (!B_MN) {  // the pair's 256 weight rows are one flag tile
+              if (kb == 0 && !ag_wait(&args.ag[ti.prob].flags[ti.nt], args.ag[ti.prob].target, abort_flag)) {
+                ok = false;
+                break;
+              }
+            } else {
+              const int blk = (k_base + kb * BK + BK - 1) >> 8;
+              if (blk >= ag_ready[ti.prob]) {
+                if (!ag_wait(&args.ag[ti.prob].flags[blk], args.ag[ti.prob].target, abort_flag)) {
+                  ok = false;
+                  break;
+                }
+                ag_ready[ti.prob] = blk + 1;  // pullers finish tiles in order
+              }
+            }
+          }
           if (!mbar_wait(&empty_bar[s], phase ^ 1u, abort_flag)) {
             ok = false;
             break;
@@ -131,7 +170,7 @@ gemm_pair_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status
       int it = 0;
       bool ok = true;
       for (int t = pair; t < total_tiles && ok; t += npair, ++it) {
-        const TileInfo ti = decode_tile(d, t);
+        const TileInfo ti = decode_tile(d, t, AG, rot0, rot1);
         const int nkb = (d.K[ti.prob] + BK - 1) / BK;
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
@@ -177,7 +216,7 @@ gemm_pair_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status
     const int chunk0 = half * (kPairTileN / 64), chunk1 = chunk0 + kPairTileN / 64;
     int it = 0;
     for (int t = pair; t < total_tiles; t += npair, ++it) {
-      const TileInfo ti = decode_tile(d, t);
+      const TileInfo ti = decode_tile(d, t, AG, rot0, rot1);
       const Problem& p = args.p[ti.prob];
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
@@ -242,6 +281,27 @@ int launch_pair_t(const GemmArgs& args, long tiles, cudaStream_t stream, int* st
   if (cap <= 0) return -10;
   const int pairs = tiles < cap ? static_cast<int>(tiles) : cap;
   gemm_pair_kernel<A_MN, B_MN><<<2 * pairs, kThreads, kPairSmemBytes, stream>>>(args, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Gathered-weight launch on CTA pairs: `n_pull` copy CTAs (even) + GEMM pairs; -10 when clusters cannot be scheduled
+// or too few pairs would be left.
+template <bool B_MN>
+int launch_pair_ag_t(const GemmArgs& args, long tiles, int n_pull, cudaStream_t stream, int* status) {
+  const int cap = pair_capacity<false, B_MN>();  // same resources per CTA as the gathered instantiation
+  if (cap <= n_pull / 2 + 1) return -10;
+  auto kern = gemm_pair_kernel<false, B_MN, true>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes) != cudaSuccess) {
+      cudaGetLastError();
+      return -10;
+    }
+    attr_set = true;
+  }
+  const int avail = cap - n_pull / 2;
+  const int pairs = tiles < avail ? static_cast<int>(tiles) : avail;
+  kern<<<n_pull + 2 * pairs, kThreads, kPairSmemBytes, stream>>>(args, status);
   return static_cast<int>(cudaGetLastError());
 }
 
