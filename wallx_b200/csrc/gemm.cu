@@ -939,9 +939,10 @@ int gemm_ag_launch(const GemmCall* calls, const AgInfo* ags, int ncalls, cudaStr
   // CTA pairs (256 x 256 tiles) when the problem has enough of them to fill the pairs that remain beside the copy
   // CTAs; the tensor maps then use 128-row B boxes (each CTA of a pair loads its half of the 256 weight rows)
   {
+    // opt-in (WX_AG_PAIR=1) until it has been timed against the single-CTA gathered kernel on more than one GPU
     static const bool pair_ok = [] {
       const char* e = getenv("WX_AG_PAIR");
-      return e == nullptr || atoi(e) != 0;
+      return e != nullptr && atoi(e) != 0;
     }();
     long ptiles = 0;
     int max_n = 0;
