@@ -635,3 +635,21 @@ def test_timers_gather_through_a_transport_object():
     table = t._get_elapsed_time_all_ranks(["a", "missing"], reset=False)
     assert table.shape == (4, 2) and _Comm.calls == 1
     assert table[1, 0] > 0 and table[0, 0] == 0.5 and float(table[:, 1].sum()) == 0.5  # row 0 is what the fake peer sent
+
+
+def test_gather_flags_are_reset_when_the_number_of_copy_ctas_changes():
+    """The ready flags of a gathered weight count the copy CTAs' arrivals per launch (target = copy CTAs x epoch), so a
+    different number on the same weight must restart the count instead of meeting a target that is already, or never,
+    reached."""
+    from wallx_b200.parallel.zero3 import GatheredWeight
+
+    flags = torch.full((3,), 40, dtype=torch.int32)
+    g = GatheredWeight(512, 64, 2, 0, [0, 0], flags, torch.zeros(512, 64))
+    g.epoch = 5
+    g.pin_pullers(8)          # first launch fixes the number; earlier counts are this weight's own
+    assert g.n_pullers == 8 and g.epoch == 5 and int(flags[0]) == 40
+    g.pin_pullers(8)
+    assert g.epoch == 5 and int(flags[0]) == 40
+    g.pin_pullers(4)          # changed: flags and epoch start over
+    assert g.n_pullers == 4 and g.epoch == 0 and int(flags.abs().sum()) == 0
+    assert g.next_epoch() == 1

@@ -259,6 +259,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     }
     return out;
   }, pybind11::arg("clear") = true, "range-check records of the debug build (all zeros in a release build)");
+  m.def("gemm_tile_rates", [](const std::vector<double>& set) {
+    if (set.size() == 4) wx::gemm_set_tile_rates(set.data());
+    std::vector<double> cur(4);
+    wx::gemm_get_tile_rates(cur.data());
+    return cur;
+  }, pybind11::arg("set") = std::vector<double>(), "get (and with four values: set) the per-tile-shape rates of the tile cost model");
   m.def("read_status", &wxb::read_status, "read and clear the device-side wait-timeout status");
   m.def("status_tensor", [](int64_t device_index) {
     return wxb::status_tensor(at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(device_index)));

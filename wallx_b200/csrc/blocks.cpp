@@ -17,6 +17,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <cstdlib>
 #include <tuple>
 #include <vector>
 
@@ -114,6 +115,42 @@ void launch(std::vector<Spec>& specs, std::vector<const WTuple*> ws, int* status
     if (ws[i] != nullptr && gathered(*ws[i])) launch_gathered(&specs[i], &ws[i], 1, status);
     else launch_plain(&specs[i], 1, status);
   }
+}
+
+// One or two problems with operands in place, while the launch's copy CTAs gather the weights `pf` (one or two
+// row-sharded weights, into their staging views) for the launches that follow.
+void launch_prefetching(std::vector<Spec>& specs, const std::vector<const WTuple*>& pf, int* status) {
+  const int n = static_cast<int>(specs.size()), m = static_cast<int>(pf.size());
+  TORCH_CHECK(n >= 1 && n <= 2 && m >= 1 && m <= 2);
+  wx::GemmCall cs[2];
+  for (int i = 0; i < n; ++i) wxb::fill_call(cs[i], to_tuple(specs[i]));
+  wx::AgInfo ags[2] = {};
+  long cols[2] = {0, 0};
+  for (int i = 0; i < m; ++i) {
+    const WTuple& w = *pf[i];
+    const auto& peers = std::get<2>(w);
+    TORCH_CHECK(peers.size() >= 1 && peers.size() <= 8 && w_of(w).is_contiguous(), "block: bad gather record");
+    for (size_t r = 0; r < peers.size(); ++r) ags[i].peer[r] = reinterpret_cast<const void*>(static_cast<uintptr_t>(peers[r]));
+    ags[i].staging = w_of(w).data_ptr();
+    ags[i].flags = std::get<3>(w)->data_ptr<int>();
+    ags[i].world = static_cast<int>(peers.size());
+    ags[i].rank = static_cast<int>(std::get<5>(w));
+    ags[i].rows_per_rank = static_cast<int>(std::get<4>(w));
+    ags[i].n_pullers = static_cast<int>(std::get<6>(w));
+    ags[i].epoch = static_cast<int>(std::get<7>(w));
+    cols[i] = w_of(w).size(1);
+  }
+  WX_RC(wx::gemm_launch_prefetch(cs, n, ags, cols, m, cur(), status), "gemm_launch_prefetch");
+}
+
+// Backward of a block with row-sharded weights: only the first dgrad GEMM gathers its weight on the critical path; each
+// weight-gradient GEMM (which needs no weight) carries the gather of the weights the following dgrad GEMMs multiply by.
+bool prefetch_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("WX_AG_PREFETCH");
+    return e == nullptr || atoi(e) != 0;
+  }();
+  return on;
 }
 
 Tensor empty_bf16(int64_t r, int64_t c, const Tensor& like) { return at::empty({r, c}, like.options().dtype(at::kBFloat16)); }
@@ -334,6 +371,12 @@ std::vector<Tensor> block_bwd(const Tensor& dout_in, const Tensor& x, const Tens
   const bool moe = dest.has_value() && dest->defined();
   const int n_exp = static_cast<int>(ffn.size() / 2);
   Tensor dout = dout_in.contiguous();
+  // every weight row-sharded, and the two staging slots suffice (at most two experts): gathers ride on the wgrad GEMMs
+  bool pf = prefetch_enabled() && n_exp <= 2 && gathered(w_qkv) && gathered(w_o) &&
+            w_of(w_qkv).data_ptr() != w_of(w_o).data_ptr();
+  for (const WTuple& w : ffn) pf = pf && gathered(w);
+  if (pf && n_exp == 2)
+    pf = w_of(ffn[0]).data_ptr() != w_of(ffn[2]).data_ptr() && w_of(ffn[1]).data_ptr() != w_of(ffn[3]).data_ptr();
   std::vector<Tensor> dW_ffn_dn, dW_ffn_gu, dW_o, dW_qkv;
   Tensor db_gu, db_dn, db_o, db_qkv;
   Tensor dxn;  // gradient w.r.t. the FFN's (normalised, possibly permuted) input
@@ -373,7 +416,13 @@ std::vector<Tensor> block_bwd(const Tensor& dout_in, const Tensor& x, const Tens
         s.dyn = segk->select(0, e);
         sp.push_back(s);
       }
-      launch(sp, std::vector<const WTuple*>(sp.size(), nullptr), status);
+      if (pf) {
+        std::vector<const WTuple*> nxt;
+        for (int e = 0; e < n_exp; ++e) nxt.push_back(&ffn[2 * e]);  // the gate/up weights, for the dgrad below
+        launch_prefetching(sp, nxt, status);
+      } else {
+        launch(sp, std::vector<const WTuple*>(sp.size(), nullptr), status);
+      }
     }
     dxn = empty_bf16(rows, H, x);
     for (int e0 = 0; e0 < n_exp; e0 += 2) {
@@ -389,7 +438,7 @@ std::vector<Tensor> block_bwd(const Tensor& dout_in, const Tensor& x, const Tens
         s.M = rows;
         s.dyn = seg->select(0, e);
         sp.push_back(s);
-        ws.push_back(&ffn[2 * e]);
+        ws.push_back(pf ? nullptr : &ffn[2 * e]);  // prefetched: already whole in its staging view
       }
       launch(sp, ws, status);
     }
@@ -404,7 +453,8 @@ std::vector<Tensor> block_bwd(const Tensor& dout_in, const Tensor& x, const Tens
         s.dyn = segk->select(0, e);
         sp.push_back(s);
       }
-      launch(sp, std::vector<const WTuple*>(sp.size(), nullptr), status);
+      if (pf) launch_prefetching(sp, {&w_o, &w_qkv}, status);  // for the two attention dgrads below
+      else launch(sp, std::vector<const WTuple*>(sp.size(), nullptr), status);
     }
   } else {
     Tensor dgu = at::empty_like(gu);
@@ -420,7 +470,8 @@ std::vector<Tensor> block_bwd(const Tensor& dout_in, const Tensor& x, const Tens
     }
     {
       std::vector<Spec> sp{wgrad_spec(dout, h, ffn[1], dW_ffn_dn, false)};
-      launch(sp, {nullptr}, status);
+      if (pf) launch_prefetching(sp, {&ffn[0]}, status);
+      else launch(sp, {nullptr}, status);
     }
     if (has_b_dn) db_dn = col_sum(dout);
     dxn = empty_bf16(T, H, x);
@@ -430,11 +481,12 @@ std::vector<Tensor> block_bwd(const Tensor& dout_in, const Tensor& x, const Tens
       sp[0].b = w_of(ffn[0]);
       sp[0].b_mn = true;
       sp[0].out = dxn;
-      launch(sp, {&ffn[0]}, status);
+      launch(sp, {pf ? nullptr : &ffn[0]}, status);
     }
     {
       std::vector<Spec> sp{wgrad_spec(dgu, xn, ffn[0], dW_ffn_gu, false)};
-      launch(sp, {nullptr}, status);
+      if (pf) launch_prefetching(sp, {&w_o, &w_qkv}, status);
+      else launch(sp, {nullptr}, status);
     }
     if (has_b_gu) db_gu = col_sum(dgu);
   }
@@ -449,7 +501,7 @@ std::vector<Tensor> block_bwd(const Tensor& dout_in, const Tensor& x, const Tens
     sp[0].b = w_of(w_o);
     sp[0].b_mn = true;
     sp[0].out = d_oattn;
-    launch(sp, {&w_o}, status);
+    launch(sp, {pf ? nullptr : &w_o}, status);
   }
   if (has_b_o) db_o = col_sum(dx2);
   Tensor dqkv = at::empty_like(qkv);
@@ -484,7 +536,7 @@ std::vector<Tensor> block_bwd(const Tensor& dout_in, const Tensor& x, const Tens
     sp[0].b = w_of(w_qkv);
     sp[0].b_mn = true;
     sp[0].out = dy1;
-    launch(sp, {&w_qkv}, status);
+    launch(sp, {pf ? nullptr : &w_qkv}, status);
   }
   {
     // the two attention weight gradients share one launch: each alone leaves most of its last wave of tiles idle

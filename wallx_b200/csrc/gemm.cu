@@ -60,7 +60,12 @@ struct GemmArgs {
   Problem p[2];
   int nprob;
   int raster_group;  // 0: default
-  AgDev ag[2];  // one per problem; used by the AG instantiations only
+  AgDev ag[2];  // used by the AG instantiations only
+  // AG instantiations: 1 = ag[i] is the B operand of problem i and the producers wait for its tiles (fused gather);
+  // 0 = the copy CTAs fetch `n_ag` weights for LATER launches while this launch multiplies operands that are already
+  // in place (prefetch: nothing in this launch waits for them)
+  int ag_wait;
+  int n_ag;
 };
 
 constexpr int kAgRing = 12;          // 16 KB buffers in the (otherwise unused) stage area of a puller CTA
@@ -479,14 +484,15 @@ template <int BN, bool A_MN, bool B_MN, bool AG>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
   using C = Cfg<BN>;
-  static_assert(!AG || (BN == 256 && !A_MN), "gathered-weight mode: 256-wide tiles, K-major A");
+  static_assert(!AG || BN == 256, "copy CTAs: 256-wide tiles only");
   static_assert(!AG || C::STAGES * C::STAGE_BYTES >= kAgRing * kAgChunkMax, "ring must fit in the stage area");
   const int n_pull = AG ? args.ag[0].n_pullers : 0;
   const bool puller = AG && static_cast<int>(blockIdx.x) < n_pull;
   const int cta = static_cast<int>(blockIdx.x) - n_pull;
   const int ncta = static_cast<int>(gridDim.x) - n_pull;
-  const int rot0 = (AG && !B_MN) ? args.ag[0].rot : 0;
-  const int rot1 = (AG && !B_MN) ? args.ag[1].rot : 0;
+  const bool gathered = AG && args.ag_wait != 0;  // B operands arrive while the kernel runs
+  const int rot0 = (gathered && !B_MN) ? args.ag[0].rot : 0;
+  const int rot1 = (gathered && !B_MN) ? args.ag[1].rot : 0;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -534,7 +540,8 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
   if (puller) {
     if (threadIdx.x == 0) {
       int seq = 0;  // chunk sequence number carries over: the ring's barrier phases continue
-      for (int i = 0; i < args.nprob; ++i)
+      const int n = gathered ? args.nprob : args.n_ag;
+      for (int i = 0; i < n; ++i)
         if (!ag_pull(args.ag[i], static_cast<int>(blockIdx.x), smem, full_bar, abort_flag, seq)) break;
     }
   } else if (warp == 0) {
@@ -549,7 +556,7 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
       bool ok = true;
       int ag_ready[2] = {0, 0};  // MN-major B: 256-row blocks of the weight known to be in place
       for (int t = cta; t < total_tiles && ok; t += ncta) {
-        const TileInfo ti = decode_tile(d, t, AG, rot0, rot1);
+        const TileInfo ti = decode_tile(d, t, gathered, rot0, rot1);
         const Problem& p = args.p[ti.prob];
         const int m_base = d.m0[ti.prob] + ti.mt * BM;
         const int n_base = ti.nt * BN;
@@ -561,7 +568,7 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
           break;
         }
         for (int kb = 0; kb < nkb; ++kb) {
-          if (AG) {
+          if (gathered) {
             if (!B_MN) {
               if (kb == 0 && !ag_wait(&args.ag[ti.prob].flags[ti.nt], args.ag[ti.prob].target, abort_flag)) {
                 ok = false;
@@ -614,7 +621,7 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
       int it = 0;
       bool ok = true;
       for (int t = cta; t < total_tiles && ok; t += ncta, ++it) {
-        const TileInfo ti = decode_tile(d, t, AG, rot0, rot1);
+        const TileInfo ti = decode_tile(d, t, gathered, rot0, rot1);
         const int nkb = (d.K[ti.prob] + BK - 1) / BK;
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
@@ -655,7 +662,7 @@ gemm_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
     const int chunk1 = (kChunks >= 2) ? chunk0 + kChunks / 2 : (half == 0 ? 1 : 0);
     int it = 0;
     for (int t = cta; t < total_tiles; t += ncta, ++it) {
-      const TileInfo ti = decode_tile(d, t, AG, rot0, rot1);
+      const TileInfo ti = decode_tile(d, t, gathered, rot0, rot1);
       const Problem& p = args.p[ti.prob];
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
@@ -760,6 +767,8 @@ int fill_args(GemmArgs& args, const GemmCall* calls, int ncalls, int bn) {
   }
   args.ag[0] = AgDev{};
   args.ag[1] = AgDev{};
+  args.ag_wait = 1;
+  args.n_ag = 0;
   for (int i = 0; i < ncalls; ++i) {
     const GemmCall& c = calls[i];
     Problem& p = args.p[i];
@@ -794,6 +803,33 @@ int fill_args(GemmArgs& args, const GemmCall* calls, int ncalls, int bn) {
   return 0;
 }
 
+// Device view of one gather: chunking of the weight's byte run, flag target of this epoch, starting tile.
+int fill_ag_dev(AgDev& a, const AgInfo& ag, long w_rows, long w_cols, int np, bool b_mn) {
+  for (int r = 0; r < ag.world; ++r) a.peer[r] = static_cast<const uint8_t*>(ag.peer[r]);
+  a.staging = static_cast<uint8_t*>(ag.staging);
+  a.flags = ag.flags;
+  a.shard_bytes = static_cast<long>(ag.rows_per_rank) * w_cols * 2;
+  a.tile_bytes = 256 * w_cols * 2;
+  a.total_bytes = w_rows * w_cols * 2;
+  a.ntiles = static_cast<int>((w_rows + 255) / 256);
+  // chunk: the largest multiple of 16 bytes, at most 16 KB, dividing both the shard and the tile
+  int chunk = 0;
+  for (int c = kAgChunkMax; c >= 16; c -= 16)
+    if (a.shard_bytes % c == 0 && a.tile_bytes % c == 0) {
+      chunk = c;
+      break;
+    }
+  if (chunk == 0) return -9;
+  a.chunk_bytes = chunk;
+  a.cpt = static_cast<int>(a.tile_bytes / chunk);
+  a.last_chunks = static_cast<int>((a.total_bytes - static_cast<long>(a.ntiles - 1) * a.tile_bytes) / chunk);
+  a.cps = static_cast<int>(a.shard_bytes / chunk);
+  a.n_pullers = np;
+  a.target = np * ag.epoch;
+  a.rot = b_mn ? 0 : static_cast<int>((static_cast<long>(ag.rank) * ag.rows_per_rank) / 256) % a.ntiles;
+  return 0;
+}
+
 }  // namespace
 
 WX_CHK_DEFINE_READER(gemm_check_read)
@@ -804,6 +840,19 @@ int gemm_checked_build() { return WX_CHECKED_BUILD; }
 #include "gemm2.cuh"
 
 namespace wx {
+
+namespace {
+// TFLOP/s of the 128 x {256, 128, 64} single-CTA tiles and of the 256 x 256 CTA-pair tile on a large problem.
+double g_tile_rates[4] = {1260.0, 970.0, 525.0, 1360.0};
+}  // namespace
+
+void gemm_set_tile_rates(const double* rates4) {
+  for (int i = 0; i < 4; ++i)
+    if (rates4[i] > 0.0) g_tile_rates[i] = rates4[i];
+}
+void gemm_get_tile_rates(double* rates4) {
+  for (int i = 0; i < 4; ++i) rates4[i] = g_tile_rates[i];
+}
 
 int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* status, int force_bn) {
   if (ncalls < 1 || ncalls > 2) return -1;
@@ -818,8 +867,9 @@ int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* sta
       t += static_cast<long>((calls[i].M + BM - 1) / BM) * ((calls[i].N + bn - 1) / bn);
     return t;
   };
-  // Tile width: minimise (number of waves) x (time of one tile); per-width MMA efficiency measured
-  // on B200 (BN 256 / 128 / 64 reach about 1260 / 970 / 525 TFLOP/s with every SM busy).
+  // Tile width: minimise (number of waves) x (time of one tile). The per-width rates (TFLOP/s with every SM busy) come
+  // from g_tile_rates: measured once per process on the device in use (gemm_set_tile_rates, called by
+  // ops.gemm.calibrate_tile_rates), with the figures of one B200 as the start-up values.
   int bn = 64;
   bool use_pair = force_bn == 512;
   if (force_bn == 64 || force_bn == 128 || force_bn == 256 || (force_bn == 32 && !a_mn && !b_mn)) {
@@ -828,7 +878,7 @@ int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* sta
     int max_n = 0;
     for (int i = 0; i < ncalls; ++i) max_n = calls[i].N > max_n ? calls[i].N : max_n;
     const int widths[3] = {256, 128, 64};
-    const double eff[3] = {1260.0, 970.0, 525.0};
+    const double eff[3] = {g_tile_rates[0], g_tile_rates[1], g_tile_rates[2]};
     const double bias[3] = {1.0, 1.12, 1.25};  // wave counting is crude: prefer the wider tile on near ties
     double best = 1e300;
     for (int w = 0; w < 3; ++w) {
@@ -849,7 +899,7 @@ int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* sta
         pt += static_cast<long>((calls[i].M + 255) / 256) * ((calls[i].N + 255) / 256);
       const long pairs = sms / 2;
       const long pwaves = (pt + pairs - 1) / pairs;
-      const double pcost = static_cast<double>(pwaves) * 256 / 1360.0;
+      const double pcost = static_cast<double>(pwaves) * 256 / g_tile_rates[3];
       if (pcost < best) use_pair = true;
     }
   }
@@ -910,29 +960,8 @@ int gemm_ag_launch(const GemmCall* calls, const AgInfo* ags, int ncalls, cudaStr
     for (int r = 0; r < ag.world; ++r)
       if (ag.peer[r] == nullptr || (reinterpret_cast<uintptr_t>(ag.peer[r]) & 15) != 0) return -9;
     if ((reinterpret_cast<uintptr_t>(ag.staging) & 15) != 0) return -9;
-    AgDev& a = args.ag[i];
-    for (int r = 0; r < ag.world; ++r) a.peer[r] = static_cast<const uint8_t*>(ag.peer[r]);
-    a.staging = static_cast<uint8_t*>(ag.staging);
-    a.flags = ag.flags;
-    a.shard_bytes = static_cast<long>(ag.rows_per_rank) * w_cols * 2;
-    a.tile_bytes = 256 * w_cols * 2;
-    a.total_bytes = w_rows * w_cols * 2;
-    a.ntiles = static_cast<int>((w_rows + 255) / 256);
-    // chunk: the largest multiple of 16 bytes, at most 16 KB, dividing both the shard and the tile
-    int chunk = 0;
-    for (int c = kAgChunkMax; c >= 16; c -= 16)
-      if (a.shard_bytes % c == 0 && a.tile_bytes % c == 0) {
-        chunk = c;
-        break;
-      }
-    if (chunk == 0) return -9;
-    a.chunk_bytes = chunk;
-    a.cpt = static_cast<int>(a.tile_bytes / chunk);
-    a.last_chunks = static_cast<int>((a.total_bytes - static_cast<long>(a.ntiles - 1) * a.tile_bytes) / chunk);
-    a.cps = static_cast<int>(a.shard_bytes / chunk);
-    a.n_pullers = np;
-    a.target = np * ag.epoch;
-    a.rot = b_mn ? 0 : static_cast<int>((static_cast<long>(ag.rank) * ag.rows_per_rank) / 256) % a.ntiles;
+    const int frc = fill_ag_dev(args.ag[i], ag, w_rows, w_cols, np, b_mn);
+    if (frc != 0) return frc;
     tiles += static_cast<long>((call.M + BM - 1) / BM) * ((call.N + 255) / 256);
   }
   if (tiles <= 0) return 0;
@@ -960,8 +989,8 @@ int gemm_ag_launch(const GemmCall* calls, const AgInfo* ags, int ncalls, cudaStr
           pargs.ag[i].n_pullers = np2;
           pargs.ag[i].target = np2 * ags[i].epoch;
         }
-        const int prc = b_mn ? launch_pair_ag_t<true>(pargs, ptiles, np2, stream, status)
-                             : launch_pair_ag_t<false>(pargs, ptiles, np2, stream, status);
+        const int prc = b_mn ? launch_pair_ag_t<false, true>(pargs, ptiles, np2, stream, status)
+                             : launch_pair_ag_t<false, false>(pargs, ptiles, np2, stream, status);
         if (prc != -10) return prc;
       }
     }
@@ -970,6 +999,70 @@ int gemm_ag_launch(const GemmCall* calls, const AgInfo* ags, int ncalls, cudaStr
   const int grid = workers + np;
   if (!b_mn) return launch_t<256, false, false, true>(args, grid, stream, status);
   return launch_t<256, false, true, true>(args, grid, stream, status);
+}
+
+// One or two GEMM problems whose operands are all in place, plus up to two weight gathers that the launch's copy CTAs
+// run for LATER launches (ags[i].staging is filled from ags[i].peer; `cols[i]` is weight i's row length in elements).
+// Nothing in this launch waits for the gathers: a kernel launched afterwards on the same stream may read the staging
+// buffers as plain operands. Used in backward: the weight-gradient GEMM of one projection (which needs no weight)
+// carries the gather of the weight that the next dgrad GEMM multiplies by, so that gather costs no time of its own.
+int gemm_launch_prefetch(const GemmCall* calls, int ncalls, const AgInfo* ags, const long* cols, int n_ags, cudaStream_t stream,
+                         int* status) {
+  if (ncalls < 1 || ncalls > 2 || n_ags < 1 || n_ags > 2) return -1;
+  const bool a_mn = calls[0].a_mn, b_mn = calls[0].b_mn;
+  for (int i = 1; i < ncalls; ++i)
+    if (calls[i].a_mn != a_mn || calls[i].b_mn != b_mn) return -2;
+  for (int i = 0; i < ncalls; ++i)
+    if ((calls[i].flags & (GEMM_ACT_SWIGLU | GEMM_SWIGLU_BWD)) && (calls[i].N % 32 != 0)) return -3;
+  const int sms = num_sms();
+  int np = ags[0].n_pullers > 0 ? ags[0].n_pullers : 8;
+  np = (np + 1) & ~1;
+  if (np > sms / 2) np = (sms / 2) & ~1;
+  AgDev devs[2] = {AgDev{}, AgDev{}};
+  for (int i = 0; i < n_ags; ++i) {
+    const AgInfo& ag = ags[i];
+    if (ag.world < 1 || ag.world > 8 || ag.rows_per_rank < 1 || ag.epoch < 1 || cols[i] < 8 || (cols[i] * 2) % 16 != 0) return -6;
+    for (int r = 0; r < ag.world; ++r)
+      if (ag.peer[r] == nullptr || (reinterpret_cast<uintptr_t>(ag.peer[r]) & 15) != 0) return -9;
+    if (ag.staging == nullptr || (reinterpret_cast<uintptr_t>(ag.staging) & 15) != 0) return -9;
+    const int frc = fill_ag_dev(devs[i], ag, static_cast<long>(ag.world) * ag.rows_per_rank, cols[i], np, true);
+    if (frc != 0) return frc;
+  }
+  long ptiles = 0, tiles = 0;
+  int max_n = 0;
+  for (int i = 0; i < ncalls; ++i) {
+    ptiles += static_cast<long>((calls[i].M + 255) / 256) * ((calls[i].N + 255) / 256);
+    tiles += static_cast<long>((calls[i].M + BM - 1) / BM) * ((calls[i].N + 255) / 256);
+    max_n = calls[i].N > max_n ? calls[i].N : max_n;
+  }
+  if (tiles <= 0) return -1;
+  auto finish = [&](GemmArgs& a) {
+    a.ag[0] = devs[0];
+    a.ag[1] = devs[1];
+    a.ag_wait = 0;
+    a.n_ag = n_ags;
+  };
+  if (max_n > 128 && ptiles >= (sms - np) / 4) {  // CTA pairs unless the problem is tiny
+    GemmArgs pargs;
+    if (fill_args(pargs, calls, ncalls, 128) == 0) {
+      finish(pargs);
+      int prc = -10;
+      if (!a_mn && !b_mn) prc = launch_pair_ag_t<false, false>(pargs, ptiles, np, stream, status);
+      else if (!a_mn && b_mn) prc = launch_pair_ag_t<false, true>(pargs, ptiles, np, stream, status);
+      else if (a_mn && b_mn) prc = launch_pair_ag_t<true, true>(pargs, ptiles, np, stream, status);
+      if (prc != -10) return prc;
+    }
+  }
+  GemmArgs args;
+  const int rc = fill_args(args, calls, ncalls, 256);
+  if (rc != 0) return rc;
+  finish(args);
+  const int workers = tiles < sms - np ? static_cast<int>(tiles) : sms - np;
+  const int grid = workers + np;
+  if (!a_mn && !b_mn) return launch_t<256, false, false, true>(args, grid, stream, status);
+  if (!a_mn && b_mn) return launch_t<256, false, true, true>(args, grid, stream, status);
+  if (a_mn && b_mn) return launch_t<256, true, true, true>(args, grid, stream, status);
+  return -2;
 }
 
 }  // namespace wx

@@ -82,6 +82,17 @@ int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* sta
 // first gather is the caller's job).
 int gemm_ag_launch(const GemmCall* calls, const AgInfo* ags, int ncalls, cudaStream_t stream, int* status);
 
+// One or two problems whose operands are all in place, plus up to two weight gathers (ags[i] with row length cols[i])
+// that the launch's copy CTAs run for later launches; nothing in this launch waits for them. See gemm.cu.
+int gemm_launch_prefetch(const GemmCall* calls, int ncalls, const AgInfo* ags, const long* cols, int n_ags, cudaStream_t stream,
+                         int* status);
+
+// Rates (TFLOP/s) that steer the tile choice of gemm_launch: 128 x 256 / 128 x 128 / 128 x 64 single-CTA tiles and the
+// 256 x 256 CTA-pair tile. Start-up values are one B200's; a caller may replace them with what it measured on the
+// device in use (non-positive entries are ignored).
+void gemm_set_tile_rates(const double* rates4);
+void gemm_get_tile_rates(double* rates4);
+
 // Debug build (-DWX_CHECK): copies out {first violating site, violation count, two values} of this translation
 // unit's range checks and clears the record when `clear`; all zeros in a release build. Returns a CUDA error code.
 int gemm_check_read(long long* out4, int clear);

@@ -37,13 +37,13 @@ constexpr int kPairTileN = 256;
 template <bool A_MN, bool B_MN, bool AG = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_pair_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status) {
-  static_assert(!AG || !A_MN, "gathered-weight mode: K-major A");
   static_assert(!AG || kPairStages * kPairStageBytes >= kAgRing * kAgChunkMax, "ring must fit in the stage area");
   static_assert(!AG || 2 * kPairStages + 4 >= kAgRing, "not enough barriers for the ring");
   const int n_pull = AG ? args.ag[0].n_pullers : 0;
   const bool puller = AG && static_cast<int>(blockIdx.x) < n_pull;
-  const int rot0 = (AG && !B_MN) ? args.ag[0].rot : 0;
-  const int rot1 = (AG && !B_MN) ? args.ag[1].rot : 0;
+  const bool gathered = AG && args.ag_wait != 0;  // B operands arrive while the kernel runs (else: prefetch only)
+  const int rot0 = (gathered && !B_MN) ? args.ag[0].rot : 0;
+  const int rot1 = (gathered && !B_MN) ? args.ag[1].rot : 0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kPairStages * kPairStageBytes);
@@ -94,7 +94,8 @@ gemm_pair_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status
   if (puller) {
     if (threadIdx.x == 0) {
       int seq = 0;  // chunk sequence number carries over: the ring's barrier phases continue
-      for (int i = 0; i < args.nprob; ++i)
+      const int n = gathered ? args.nprob : args.n_ag;
+      for (int i = 0; i < n; ++i)
         if (!ag_pull(args.ag[i], static_cast<int>(blockIdx.x), smem, full_bar, abort_flag, seq)) break;
     }
   } else if (warp == 0) {
@@ -109,14 +110,14 @@ gemm_pair_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status
       bool ok = true;
       int ag_ready[2] = {0, 0};  // MN-major B: 256-row blocks of the weight known to be in place
       for (int t = pair; t < total_tiles && ok; t += npair) {
-        const TileInfo ti = decode_tile(d, t, AG, rot0, rot1);
+        const TileInfo ti = decode_tile(d, t, gathered, rot0, rot1);
         const Problem& p = args.p[ti.prob];
         const int m_base = d.m0[ti.prob] + ti.mt * kPairTileM + static_cast<int>(rank) * BM;
         const int n_base = ti.nt * kPairTileN + static_cast<int>(rank) * 128;
         const int k_base = d.k0[ti.prob];
         const int nkb = (d.K[ti.prob] + BK - 1) / BK;
         for (int kb = 0; kb < nkb; ++kb) {
-          if (AG) {
+          if (gathered) {
             if (!B_MN) {  // the pair's 256 weight rows are one flag tile
               if (kb == 0 && !ag_wait(&args.ag[ti.prob].flags[ti.nt], args.ag[ti.prob].target, abort_flag)) {
                 ok = false;
@@ -170,7 +171,7 @@ gemm_pair_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status
       int it = 0;
       bool ok = true;
       for (int t = pair; t < total_tiles && ok; t += npair, ++it) {
-        const TileInfo ti = decode_tile(d, t, AG, rot0, rot1);
+        const TileInfo ti = decode_tile(d, t, gathered, rot0, rot1);
         const int nkb = (d.K[ti.prob] + BK - 1) / BK;
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
@@ -216,7 +217,7 @@ gemm_pair_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status
     const int chunk0 = half * (kPairTileN / 64), chunk1 = chunk0 + kPairTileN / 64;
     int it = 0;
     for (int t = pair; t < total_tiles; t += npair, ++it) {
-      const TileInfo ti = decode_tile(d, t, AG, rot0, rot1);
+      const TileInfo ti = decode_tile(d, t, gathered, rot0, rot1);
       const Problem& p = args.p[ti.prob];
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
@@ -286,11 +287,11 @@ int launch_pair_t(const GemmArgs& args, long tiles, cudaStream_t stream, int* st
 
 // Gathered-weight launch on CTA pairs: `n_pull` copy CTAs (even) + GEMM pairs; -10 when clusters cannot be scheduled
 // or too few pairs would be left.
-template <bool B_MN>
+template <bool A_MN, bool B_MN>
 int launch_pair_ag_t(const GemmArgs& args, long tiles, int n_pull, cudaStream_t stream, int* status) {
-  const int cap = pair_capacity<false, B_MN>();  // same resources per CTA as the gathered instantiation
+  const int cap = pair_capacity<A_MN, B_MN>();  // same resources per CTA as the instantiation with copy CTAs
   if (cap <= n_pull / 2 + 1) return -10;
-  auto kern = gemm_pair_kernel<false, B_MN, true>;
+  auto kern = gemm_pair_kernel<A_MN, B_MN, true>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes) != cudaSuccess) {

@@ -71,3 +71,39 @@ def check_status(device: Optional[torch.device] = None) -> None:
     st = _ext.get().read_status(idx)
     if st != 0:
         raise RuntimeError(f"wallx_b200: a device-side wait timed out (status {st}); results are invalid")
+
+
+_CALIBRATED = set()
+
+
+def calibrate_tile_rates(device: Optional[torch.device] = None, force: bool = False):
+    """Measure, once per process and device, the rate of each tile shape of the GEMM core (128 x 256 / 128 x 128 /
+    128 x 64 single-CTA tiles, 256 x 256 CTA pairs) on a problem that fills the device, and hand the four numbers to the
+    tile cost model (which otherwise uses the figures of one B200). Takes a few milliseconds; call it outside any
+    stream capture. Returns the rates in TFLOP/s."""
+    C = _ext.get()
+    idx = torch.cuda.current_device() if device is None else (torch.device(device).index or 0)
+    if idx in _CALIBRATED and not force:
+        return C.gemm_tile_rates([])
+    dev = torch.device("cuda", idx)
+    M, N, K = 8192, 4096, 4096
+    a = torch.randn(M, K, device=dev).to(torch.bfloat16)
+    b = torch.randn(N, K, device=dev).to(torch.bfloat16)
+    out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    spec = GemmSpec(a, b, out)
+    rates = []
+    for bn in (256, 128, 64, 512):
+        try:
+            for _ in range(2):
+                launch([spec], bn)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(3):
+                launch([spec], bn)
+            e1.record()
+            torch.cuda.synchronize(dev)
+            rates.append(3 * 2.0 * M * N * K / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+        except RuntimeError:  # CTA pairs cannot be scheduled on this device: keep the start-up value out of the race
+            rates.append(1e-3 if bn == 512 else 0.0)
+    _CALIBRATED.add(idx)
+    return C.gemm_tile_rates([float(r) for r in rates])

@@ -117,6 +117,15 @@ class TrainEngine:
                 used += b.attach_gather([p + off for p in symm.param_ptrs], self.workspace, self._ag_flags[used:])
         self.optimizer = FlatAdamW(self.buffers, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
                                    max_grad_norm=max_grad_norm, grad_accum=grad_accum * world)
+        if self.buffers and self.buffers[0].device.type == "cuda":
+            # per-tile-shape GEMM rates of this device for the tile cost model (measured once per process, a few ms)
+            from ..ops import _ext
+            from ..ops import gemm as G
+
+            import os
+
+            if hasattr(_ext.get(), "gemm_tile_rates") and os.environ.get("WALLX_CALIBRATE", "1") != "0":
+                G.calibrate_tile_rates(self.buffers[0].device)
         self.last_norm_sq: Optional[torch.Tensor] = None
         self.last_bad: Optional[torch.Tensor] = None  # device float: some rank's device-side wait ran out in the last step
         # ranks agree on which parameters were used unless batches differ in modality; the merge

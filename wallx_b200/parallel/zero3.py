@@ -84,8 +84,10 @@ class GatheredWeight:
 
 
 def slot_of(name: str) -> int:
-    """Staging slot of a weight. The two experts' weights of one launch must sit in different slots."""
-    return 1 if ".experts.1." in name else 0
+    """Staging slot of a weight. Weights that are gathered by one launch must sit in different slots: the two experts'
+    gate/up (and down) projections, and the QKV and output projections of a block's attention (their gathers ride
+    together on the FFN's weight-gradient GEMM in backward)."""
+    return 1 if (".experts.1." in name or "qkv" in name) else 0
 
 
 class RowShardedBuffer:
