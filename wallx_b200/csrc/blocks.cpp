@@ -363,7 +363,11 @@ std::vector<Tensor> block_bwd(const Tensor& dout_in, const Tensor& x, const Tens
                               bool has_b_qkv, const Tensor& cos_t, const Tensor& sin_t, int64_t n_rot, const Tensor& qtab,
                               const Tensor& ktab, int64_t hq, int64_t hkv, int64_t d, double scale, bool has_bidir, bool causal_self,
                               const WTuple& w_o, bool has_b_o, const std::vector<WTuple>& ffn, bool has_b_gu, bool has_b_dn,
-                              const OptT& dest, const OptT& seg, const OptT& segk, int64_t rows) {
+                              const OptT& dest, const OptT& seg, const OptT& segk, int64_t rows, bool dn_in_place,
+                              const std::vector<WTuple>& next_dn) {
+  // dn_in_place: the down-projection weights are already whole in their staging views (the block whose backward ran
+  // just before prefetched them); next_dn: up to two row-sharded weights to gather for the block whose backward runs
+  // next (its down projections), carried by this block's last weight-gradient launch.
   check_common(x, cos_t, sin_t, qtab, ktab, d);
   c10::cuda::CUDAGuard guard(x.device());
   int* status = wxb::status_tensor(x.device()).data_ptr<int>();
@@ -401,7 +405,7 @@ std::vector<Tensor> block_bwd(const Tensor& dout_in, const Tensor& x, const Tens
         s.dyn = seg->select(0, e);
         s.flags = wx::GEMM_SWIGLU_BWD | wx::GEMM_ZERO_PAD_ROWS;
         sp.push_back(s);
-        ws.push_back(&ffn[2 * e + 1]);
+        ws.push_back(dn_in_place ? nullptr : &ffn[2 * e + 1]);
       }
       launch(sp, ws, status);
     }
@@ -466,7 +470,7 @@ std::vector<Tensor> block_bwd(const Tensor& dout_in, const Tensor& x, const Tens
       sp[0].out = dgu;
       sp[0].out2 = gu;
       sp[0].flags = wx::GEMM_SWIGLU_BWD;
-      launch(sp, {&ffn[1]}, status);
+      launch(sp, {dn_in_place ? nullptr : &ffn[1]}, status);
     }
     {
       std::vector<Spec> sp{wgrad_spec(dout, h, ffn[1], dW_ffn_dn, false)};
@@ -542,7 +546,13 @@ std::vector<Tensor> block_bwd(const Tensor& dout_in, const Tensor& x, const Tens
     // the two attention weight gradients share one launch: each alone leaves most of its last wave of tiles idle
     // (weights of a few thousand rows and columns give barely more tiles than SMs), together they fill it
     std::vector<Spec> sp{wgrad_spec(dqkv_raw, y1, w_qkv, dW_qkv, false), wgrad_spec(dx2, o_attn, w_o, dW_o, false)};
-    launch(sp, {nullptr, nullptr}, status);
+    if (!next_dn.empty()) {
+      std::vector<const WTuple*> nxt;
+      for (const WTuple& w : next_dn) nxt.push_back(&w);
+      launch_prefetching(sp, nxt, status);
+    } else {
+      launch(sp, {nullptr, nullptr}, status);
+    }
   }
   if (has_b_qkv) db_qkv = col_sum(dqkv_raw);
   auto [dx, dln1] = norm_bwd(dy1, x, ln1_w, rstd1, OptT(), dx2);  // + gradient of the attention's residual path

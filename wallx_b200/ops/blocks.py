@@ -22,6 +22,7 @@ from . import _ext
 from . import functional as F_
 
 ENABLED = os.environ.get("WALLX_FUSED_BLOCKS", "1") != "0"
+PREFETCH_NEXT = os.environ.get("WX_AG_PREFETCH_NEXT", "1") != "0"
 
 
 _PULLERS = None
@@ -36,14 +37,21 @@ def _default_pullers() -> int:
     return _PULLERS
 
 
-def _wtuple(w: torch.Tensor, sink, forward: bool):
-    """(weight or staging view, sink view or None, peers, flags, rows per rank, rank, copy CTAs, epoch)."""
+def _wtuple(w: torch.Tensor, sink, forward: bool, gather: bool = True):
+    """(weight or staging view, sink view or None, peers, flags, rows per rank, rank, copy CTAs, epoch).
+    ``gather=False``: the weight is already whole in its staging view, no gather is enqueued for it by this call."""
     gw = F_._shard_of(w)
     sview = sink[0] if sink is not None else None
     if gw is None:
         return (w, sview, [], None, 0, 0, 0, 0)
     gw.pin_pullers(gw.n_pullers or _default_pullers())
-    return (w, sview, gw.peer_ptrs, gw.flags, gw.rows_per_rank, gw.rank, gw.n_pullers, gw.next_epoch())
+    return (w, sview, gw.peer_ptrs, gw.flags, gw.rows_per_rank, gw.rank, gw.n_pullers,
+            gw.next_epoch() if gather else max(gw.epoch, 1))
+
+
+# The down-projection weights of the block whose forward ran last: its backward runs right after the backward of
+# the block that is running forward now, so that block's backward gathers them ahead of time (row-sharded weights).
+_PREV_DOWN = []
 
 
 class _BlockFn(torch.autograd.Function):
@@ -63,7 +71,10 @@ class _BlockFn(torch.autograd.Function):
                           plan.dest if moe else None, plan.seg if moe else None, plan.inv if moe else None,
                           int(plan.rows) if moe else 0, bool(need_bwd))
         out = res[0]
+        global _PREV_DOWN
+        prev_down, _PREV_DOWN = _PREV_DOWN, [ffn_w[2 * e + 1] for e in range(len(ffn_w) // 2)]
         if need_bwd:
+            ctx.prev_down = [w for w in prev_down if F_._shard_of(w) is not None][:2]
             y1, rstd1, qkv, o_attn, lse, x2, rstd2, xn, gu, h = res[1:]
             ctx.save_for_backward(x, ln1_w, y1, rstd1, qkv, o_attn, lse, x2, ln2_w, rstd2, xn, gu, h, cos, sin, qtab, ktab,
                                   w_qkv, w_o, *ffn_w)
@@ -80,18 +91,33 @@ class _BlockFn(torch.autograd.Function):
         n_rot, hq, hkv, d, scale, has_bidir, causal_self, plan = ctx.cfg
         weights = [w_qkv, w_o, *ffn_w]
         sinks = ctx.sinks
-        wt = [_wtuple(w, s, False) for w, s in zip(weights, sinks)]
+        n_exp = len(ffn_w) // 2
+        downs = [ffn_w[2 * e + 1] for e in range(n_exp)]
+        dn_shards = [F_._shard_of(w) for w in downs]
+        # the block whose backward ran just before this one may have gathered this block's down projections already
+        dn_in_place = bool(dn_shards) and all(g is not None and g.in_place() for g in dn_shards)
+        wt = [_wtuple(w, s, False, gather=not (dn_in_place and any(w is d_ for d_ in downs)))
+              for w, s in zip(weights, sinks)]
+        for g in dn_shards:
+            if g is not None:
+                g.prefetched = False  # consumed by this backward
+        # gathers of the next block's down projections ride on this block's last weight-gradient launch; after it the
+        # two staging slots belong to them
+        nxt = ctx.prev_down if PREFETCH_NEXT and all(F_._shard_of(w) is not None for w in weights) else []
+        if len({F_._shard_of(w).slot for w in nxt}) != len(nxt):
+            nxt = []
         moe = plan is not None
         hb = ctx.has_bias
         res = C.block_bwd(dout, x, ln1_w, y1, rstd1, qkv, o_attn, lse, x2, ln2_w, rstd2, xn, gu, h, wt[0], hb[0], cos, sin,
                           n_rot, qtab, ktab, hq, hkv, d, scale, has_bidir, causal_self, wt[1], hb[1], wt[2:], hb[2], hb[3],
                           plan.dest if moe else None, plan.seg if moe else None, plan.segk if moe else None,
-                          int(plan.rows) if moe else 0)
+                          int(plan.rows) if moe else 0, dn_in_place, [_wtuple(w, None, False) for w in nxt])
+        for w in nxt:
+            F_._shard_of(w).prefetched = True
         dx, dln1, dln2, db_qkv, db_o, db_gu, db_dn, dw_qkv, dw_o = res[:9]
         dw_ffn = list(res[9:])
         # sink callbacks in the order the gradients were produced (all of them are enqueued by now)
         order = []
-        n_exp = len(ffn_w) // 2
         order += [2 + 2 * e + 1 for e in range(n_exp)] + [2 + 2 * e for e in range(n_exp)] + [1, 0]
         for i in order:
             if sinks[i] is not None:

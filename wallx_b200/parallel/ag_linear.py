@@ -57,9 +57,9 @@ class ShardedWeight(GatheredWeight):
         self.shard = symm_mem.empty(rows // world, cols, dtype=torch.bfloat16, device=device)
         self.shard.zero_()
         hdl = symm_mem.rendezvous(self.shard, group)
-        self.workspace = workspace if workspace is not None else GatherWorkspace(rows * cols, device, slots=1)
         flags = torch.zeros((rows + 255) // 256, dtype=torch.int32, device=device)
         super().__init__(rows, cols, world, rank, [int(p) for p in hdl.buffer_ptrs], flags, None)
+        self.workspace = workspace if workspace is not None else GatherWorkspace(rows * cols, device, slots=1)
 
     def load_full(self, full: torch.Tensor) -> None:
         """Keep this rank's rows of a replicated full weight."""

@@ -39,6 +39,9 @@ class GatherWorkspace:
         self.buf = torch.empty(slots, max_elems, dtype=dtype, device=device)
         self.max_elems = int(max_elems)
         self.slots = slots
+        # which weight was gathered into each slot last (set whenever a gather into the slot is enqueued): a launch
+        # may read a slot as a plain operand only while the weight it wants is still the owner
+        self.owner = [None] * slots
 
     def view(self, rows: int, cols: int, slot: int = 0) -> torch.Tensor:
         n = rows * cols
@@ -60,17 +63,33 @@ class GatheredWeight:
         self.epoch = 0
         self.slot = int(slot)
         self._staging = staging
+        self.workspace: Optional[GatherWorkspace] = None  # set by the engine: slot ownership for prefetched gathers
+        self.prefetched = False  # whole and current in its staging view, gathered ahead of its use
         self.n_pullers: Optional[int] = None  # fixed by the first launch: the flags count arrivals of that many copy CTAs
 
     def staging(self, slot: Optional[int] = None) -> torch.Tensor:
         return self._staging
 
     def next_epoch(self) -> int:
+        """Called once per enqueued gather of this weight (fused into a GEMM or carried by another launch)."""
         self.epoch += 1
         if self.epoch >= (1 << 24):  # flags are int32 counts of n_pullers * epoch
             self.flags.zero_()
             self.epoch = 1
+        self.prefetched = False
+        ws = self.workspace
+        if ws is not None:
+            prev = ws.owner[self.slot]
+            if prev is not None and prev is not self:
+                prev.prefetched = False  # its copy in the slot is about to be overwritten
+            ws.owner[self.slot] = self
         return self.epoch
+
+    def in_place(self) -> bool:
+        """True when the whole, current weight sits in its staging view because an earlier launch gathered it ahead
+        of time and nothing has been gathered into that slot since."""
+        ws = self.workspace
+        return bool(self.prefetched and ws is not None and ws.owner[self.slot] is self)
 
     def pin_pullers(self, n_pullers: int) -> None:
         """The ready flags count ``n_pullers`` arrivals per launch, so the number must not change while counts from
@@ -270,6 +289,7 @@ class RowShardedBuffer:
             gw = GatheredWeight(R, C, self.world, self.rank, [b + o * esize for b in peer_param_ptrs],
                                 flags[used:used + nf], workspace.view(R, C, slot), slot)
             used += nf
+            gw.workspace = workspace
             self.gathered[i] = gw
             p.data = gw.staging()
             p._wx_shard = gw
