@@ -14,6 +14,7 @@
 #include "attention.h"
 #include "bind_common.h"
 #include "comm.h"
+#include "decode.h"
 #include "gemm.h"
 #include "kernels.h"
 
@@ -251,7 +252,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     long long r[4];
     struct Unit { const char* name; int (*read)(long long*, int); };
     const Unit units[] = {{"gemm", &wx::gemm_check_read}, {"attention", &wx::attn_check_read}, {"kernels", &wx::kernels_check_read},
-                          {"index", &wx::index_check_read}, {"comm", &wx::comm_check_read}};
+                          {"index", &wx::index_check_read}, {"comm", &wx::comm_check_read},
+                          {"decode", &wx::decode_check_read}};
     for (const Unit& u : units) {
       const int rc = u.read(r, clear ? 1 : 0);
       if (rc != 0) wxb::fail_code("check_report", rc);

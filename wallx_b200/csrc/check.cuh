@@ -8,7 +8,7 @@
 // host function that copies it out and clears it.
 //
 // Site ids: 1xxx ptx helpers (TMA / bulk copies / mbarrier / TMEM), 2xxx gemm, 3xxx attention, 4xxx kernels,
-// 5xxx index, 6xxx comm.
+// 5xxx index, 6xxx comm, 7xxx decode.
 #pragma once
 #include <cuda_runtime.h>
 

@@ -16,6 +16,7 @@
 // cuBLAS calls behind every nn.Linear in wall_x/model.
 #include "gemm.h"
 #include "devinfo.h"
+#include "launch.h"
 #include "ptx.cuh"
 
 #include <cstdlib>
@@ -162,6 +163,145 @@ __device__ __forceinline__ TileInfo decode_tile(const Dims& d, int t, bool gathe
 __device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
+// Bias / activation / residual / accumulate and the store of 32 consecutive columns [n0, n0 + 32) of destination row
+// `drow`: `v` holds the fp32 accumulators (ignored for `zero_row`, which stores zeros: padding rows of a segment).
+__device__ __forceinline__ void epilogue_chunk(const Problem& p, float (&v)[32], long drow, int n0, bool zero_row) {
+  const int flags = p.flags;
+  const bool swiglu = (flags & GEMM_ACT_SWIGLU) != 0;
+  const bool out_fp32 = (flags & GEMM_OUT_FP32) != 0;
+  const bool accum = (flags & GEMM_ACCUMULATE) != 0 && !zero_row;
+  const int nvalid = min(32, p.N - n0);
+  if (p.bias != nullptr && !zero_row) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < nvalid) v[j] += __bfloat162float(p.bias[n0 + j]);
+  }
+  if (flags & GEMM_SWIGLU_BWD) {
+    // v = dL/dh for channels [n0, n0 + 32): two 32-column blocks [16 gate | 16 up] of the saved raw values
+    const uint4* gsrc =
+        reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.D2) + drow * p.ldd2 + 2 * n0);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + drow * p.ldd + 2 * n0);
+#pragma unroll
+    for (int blk = 0; blk < 2; ++blk) {
+      uint4 raw[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) raw[q] = zero_row ? make_uint4(0u, 0u, 0u, 0u) : gsrc[4 * blk + q];
+      const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&raw[0]);  // 16 gate values
+      const __nv_bfloat162* ub = reinterpret_cast<const __nv_bfloat162*>(&raw[2]);  // 16 up values
+      uint32_t og[8], ou[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float2 g2 = __bfloat1622float2(gb[e]);
+        const float2 u2 = __bfloat1622float2(ub[e]);
+        const float d0 = v[16 * blk + 2 * e], d1 = v[16 * blk + 2 * e + 1];
+        const float s0 = 1.0f / (1.0f + __expf(-g2.x)), s1 = 1.0f / (1.0f + __expf(-g2.y));
+        og[e] = pack_bf16x2(d0 * u2.x * s0 * (1.0f + g2.x * (1.0f - s0)), d1 * u2.y * s1 * (1.0f + g2.y * (1.0f - s1)));
+        ou[e] = pack_bf16x2(d0 * g2.x * s0, d1 * g2.y * s1);
+      }
+      dst[4 * blk + 0] = make_uint4(og[0], og[1], og[2], og[3]);
+      dst[4 * blk + 1] = make_uint4(og[4], og[5], og[6], og[7]);
+      dst[4 * blk + 2] = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+      dst[4 * blk + 3] = make_uint4(ou[4], ou[5], ou[6], ou[7]);
+    }
+    return;
+  }
+  if (swiglu) {
+    // columns [n0, n0+16) are gate, [n0+16, n0+32) are up; N is a multiple of 32 here.
+    if (p.D2 != nullptr) {
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D2) + drow * p.ldd2 + n0);
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        dst[q] = make_uint4(pack_bf16x2(v[8 * q + 0], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                            pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+    }
+    float h[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      // round gate and up to bf16 first so that the result equals the unfused path
+      const float g = __bfloat162float(__float2bfloat16(v[j]));
+      const float u = __bfloat162float(__float2bfloat16(v[16 + j]));
+      h[j] = silu_f(g) * u;
+    }
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + drow * p.ldd + (n0 >> 1));
+#pragma unroll
+    for (int q = 0; q < 2; ++q)
+      dst[q] = make_uint4(pack_bf16x2(h[8 * q + 0], h[8 * q + 1]), pack_bf16x2(h[8 * q + 2], h[8 * q + 3]),
+                          pack_bf16x2(h[8 * q + 4], h[8 * q + 5]), pack_bf16x2(h[8 * q + 6], h[8 * q + 7]));
+    return;
+  }
+  if (flags & GEMM_ACT_GELU) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+  }
+  if (p.residual != nullptr && !zero_row) {
+    const __nv_bfloat16* rs = p.residual + drow * p.ldr + n0;
+    if (nvalid == 32 && (p.ldr & 7) == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0) {
+      const uint4* rs4 = reinterpret_cast<const uint4*>(rs);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint4 x = rs4[q];
+        const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(xb[e]);
+          v[8 * q + 2 * e] += f.x;
+          v[8 * q + 2 * e + 1] += f.y;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < nvalid) v[j] += __bfloat162float(rs[j]);
+    }
+  }
+  if (out_fp32) {
+    float* dst = reinterpret_cast<float*>(p.D) + drow * p.ldd + n0;
+    if (nvalid == 32 && (p.ldd & 3) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15) == 0) {
+      float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        if (accum) {
+          const float4 old = d4[q];
+          o.x += old.x;
+          o.y += old.y;
+          o.z += old.z;
+          o.w += old.w;
+        }
+        d4[q] = o;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < nvalid) dst[j] = accum ? dst[j] + v[j] : v[j];
+    }
+  } else {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.D) + drow * p.ldd + n0;
+    if (nvalid == 32 && (p.ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15) == 0) {
+      uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (accum) {
+          const uint4 x = d4[q];
+          const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(xb[e]);
+            v[8 * q + 2 * e] += f.x;
+            v[8 * q + 2 * e + 1] += f.y;
+          }
+        }
+        d4[q] = make_uint4(pack_bf16x2(v[8 * q + 0], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                           pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < nvalid) dst[j] = __float2bfloat16(accum ? __bfloat162float(dst[j]) + v[j] : v[j]);
+    }
+  }
+}
+
 // Epilogue of one warp for one output tile: the warp's 32 accumulator rows (TMEM lanes of its
 // quarter, BN fp32 columns starting at taddr0) go through bias / activation / residual / row map /
 // accumulate and are stored. `row_in_prob` is this thread's row within the problem; the warp
@@ -184,10 +324,6 @@ __device__ __forceinline__ void epilogue_rows(const Problem& p, int M, int m0, i
   }
   // debug build: the destination row lies inside D (after the row map, with zero-filled pad rows included)
   if (store_ok && !WX_CHK(drow >= 0 && (p.d_rows == 0 || drow < p.d_rows), 2005, drow, p.d_rows)) store_ok = false;
-  const int flags = p.flags;
-  const bool swiglu = (flags & GEMM_ACT_SWIGLU) != 0;
-  const bool out_fp32 = (flags & GEMM_OUT_FP32) != 0;
-  const bool accum = (flags & GEMM_ACCUMULATE) != 0 && !zero_row;
 
 #pragma unroll 1
   for (int c = chunk0; c < chunk1; ++c) {
@@ -199,136 +335,7 @@ __device__ __forceinline__ void epilogue_rows(const Problem& p, int M, int m0, i
     float v[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = zero_row ? 0.f : __uint_as_float(r[j]);
-    const int nvalid = min(32, p.N - n0);
-    if (p.bias != nullptr && !zero_row) {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < nvalid) v[j] += __bfloat162float(p.bias[n0 + j]);
-    }
-    if (flags & GEMM_SWIGLU_BWD) {
-      // v = dL/dh for channels [n0, n0 + 32): two 32-column blocks [16 gate | 16 up] of the saved raw values
-      const uint4* gsrc =
-          reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.D2) + drow * p.ldd2 + 2 * n0);
-      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + drow * p.ldd + 2 * n0);
-#pragma unroll
-      for (int blk = 0; blk < 2; ++blk) {
-        uint4 raw[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) raw[q] = zero_row ? make_uint4(0u, 0u, 0u, 0u) : gsrc[4 * blk + q];
-        const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&raw[0]);  // 16 gate values
-        const __nv_bfloat162* ub = reinterpret_cast<const __nv_bfloat162*>(&raw[2]);  // 16 up values
-        uint32_t og[8], ou[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float2 g2 = __bfloat1622float2(gb[e]);
-          const float2 u2 = __bfloat1622float2(ub[e]);
-          const float d0 = v[16 * blk + 2 * e], d1 = v[16 * blk + 2 * e + 1];
-          const float s0 = 1.0f / (1.0f + __expf(-g2.x)), s1 = 1.0f / (1.0f + __expf(-g2.y));
-          og[e] = pack_bf16x2(d0 * u2.x * s0 * (1.0f + g2.x * (1.0f - s0)), d1 * u2.y * s1 * (1.0f + g2.y * (1.0f - s1)));
-          ou[e] = pack_bf16x2(d0 * g2.x * s0, d1 * g2.y * s1);
-        }
-        dst[4 * blk + 0] = make_uint4(og[0], og[1], og[2], og[3]);
-        dst[4 * blk + 1] = make_uint4(og[4], og[5], og[6], og[7]);
-        dst[4 * blk + 2] = make_uint4(ou[0], ou[1], ou[2], ou[3]);
-        dst[4 * blk + 3] = make_uint4(ou[4], ou[5], ou[6], ou[7]);
-      }
-      continue;
-    }
-    if (swiglu) {
-      // columns [n0, n0+16) are gate, [n0+16, n0+32) are up; N is a multiple of 32 here.
-      if (p.D2 != nullptr) {
-        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D2) + drow * p.ldd2 + n0);
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-          dst[q] = make_uint4(pack_bf16x2(v[8 * q + 0], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
-                              pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
-      }
-      float h[16];
-#pragma unroll
-      for (int j = 0; j < 16; ++j) {
-        // round gate and up to bf16 first so that the result equals the unfused path
-        const float g = __bfloat162float(__float2bfloat16(v[j]));
-        const float u = __bfloat162float(__float2bfloat16(v[16 + j]));
-        h[j] = silu_f(g) * u;
-      }
-      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + drow * p.ldd + (n0 >> 1));
-#pragma unroll
-      for (int q = 0; q < 2; ++q)
-        dst[q] = make_uint4(pack_bf16x2(h[8 * q + 0], h[8 * q + 1]), pack_bf16x2(h[8 * q + 2], h[8 * q + 3]),
-                            pack_bf16x2(h[8 * q + 4], h[8 * q + 5]), pack_bf16x2(h[8 * q + 6], h[8 * q + 7]));
-      continue;
-    }
-    if (flags & GEMM_ACT_GELU) {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
-    }
-    if (p.residual != nullptr && !zero_row) {
-      const __nv_bfloat16* rs = p.residual + drow * p.ldr + n0;
-      if (nvalid == 32 && (p.ldr & 7) == 0 && (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0) {
-        const uint4* rs4 = reinterpret_cast<const uint4*>(rs);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint4 x = rs4[q];
-          const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&x);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(xb[e]);
-            v[8 * q + 2 * e] += f.x;
-            v[8 * q + 2 * e + 1] += f.y;
-          }
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (j < nvalid) v[j] += __bfloat162float(rs[j]);
-      }
-    }
-    if (out_fp32) {
-      float* dst = reinterpret_cast<float*>(p.D) + drow * p.ldd + n0;
-      if (nvalid == 32 && (p.ldd & 3) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15) == 0) {
-        float4* d4 = reinterpret_cast<float4*>(dst);
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-          if (accum) {
-            const float4 old = d4[q];
-            o.x += old.x;
-            o.y += old.y;
-            o.z += old.z;
-            o.w += old.w;
-          }
-          d4[q] = o;
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (j < nvalid) dst[j] = accum ? dst[j] + v[j] : v[j];
-      }
-    } else {
-      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.D) + drow * p.ldd + n0;
-      if (nvalid == 32 && (p.ldd & 7) == 0 && (reinterpret_cast<uintptr_t>(p.D) & 15) == 0) {
-        uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          if (accum) {
-            const uint4 x = d4[q];
-            const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&x);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 f = __bfloat1622float2(xb[e]);
-              v[8 * q + 2 * e] += f.x;
-              v[8 * q + 2 * e + 1] += f.y;
-            }
-          }
-          d4[q] = make_uint4(pack_bf16x2(v[8 * q + 0], v[8 * q + 1]), pack_bf16x2(v[8 * q + 2], v[8 * q + 3]),
-                             pack_bf16x2(v[8 * q + 4], v[8 * q + 5]), pack_bf16x2(v[8 * q + 6], v[8 * q + 7]));
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (j < nvalid) dst[j] = __float2bfloat16(accum ? __bfloat162float(dst[j]) + v[j] : v[j]);
-      }
-    }
+    epilogue_chunk(p, v, drow, n0, zero_row);
   }
 }
 
@@ -756,7 +763,7 @@ int launch_bn(const GemmArgs& args, bool a_mn, bool b_mn, int grid, cudaStream_t
   return launch_t<BN, true, true>(args, grid, stream, status);
 }
 
-int fill_args(GemmArgs& args, const GemmCall* calls, int ncalls, int bn) {
+int fill_args(GemmArgs& args, const GemmCall* calls, int ncalls, int bn, int a_rows = BM) {
   args.nprob = ncalls;
   {
     static const int env_group = [] {
@@ -774,7 +781,7 @@ int fill_args(GemmArgs& args, const GemmCall* calls, int ncalls, int bn) {
     Problem& p = args.p[i];
     bool ok;
     if (!c.a_mn)
-      ok = make_tmap(&p.tmA, c.A, c.a_extent_k, c.a_extent_mn, c.lda, BK, BM);
+      ok = make_tmap(&p.tmA, c.A, c.a_extent_k, c.a_extent_mn, c.lda, BK, a_rows);
     else
       ok = make_tmap(&p.tmA, c.A, c.a_extent_mn, c.a_extent_k, c.lda, 64, BK);
     if (!ok) return -4;
@@ -838,6 +845,7 @@ int gemm_checked_build() { return WX_CHECKED_BUILD; }
 }  // namespace wx
 
 #include "gemm2.cuh"
+#include "gemm_skinny.cuh"
 
 namespace wx {
 
@@ -859,6 +867,31 @@ int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* sta
   const bool a_mn = calls[0].a_mn, b_mn = calls[0].b_mn;
   for (int i = 1; i < ncalls; ++i)
     if (calls[i].a_mn != a_mn || calls[i].b_mn != b_mn) return -2;
+
+  // Few rows (decode, denoise steps): clusters of CTAs that split K (gemm_skinny.cuh). force_bn = 16 selects that
+  // kernel where it is legal, 17 the same with one CTA per column tile (no split); other forced widths bypass it.
+  if (!a_mn && !b_mn && (force_bn == 0 || force_bn == 16 || force_bn == 17)) {
+    int max_m = 0, min_nkb = 1 << 30;
+    long st = 0;
+    bool plain = true;
+    for (int i = 0; i < ncalls; ++i) {
+      max_m = calls[i].M > max_m ? calls[i].M : max_m;
+      st += (calls[i].N + kSkinnyBN - 1) / kSkinnyBN;
+      const int nkb = (calls[i].K + BK - 1) / BK;
+      min_nkb = nkb < min_nkb ? nkb : min_nkb;
+      if ((calls[i].flags & (GEMM_ACT_SWIGLU | GEMM_SWIGLU_BWD)) && (calls[i].N % 32 != 0)) plain = false;
+      if (calls[i].flags & GEMM_ZERO_PAD_ROWS) plain = false;  // rows past M are never visited by that kernel
+    }
+    if (plain && max_m >= 1 && max_m <= BM && st >= 1 && st <= 1024) {
+      GemmArgs sargs;
+      const int a_rows = skinny_rows(max_m);
+      const int src = fill_args(sargs, calls, ncalls, kSkinnyBN, a_rows);
+      if (src != 0) return src;
+      const int splits = force_bn == 17 ? 1 : skinny_splits(st, min_nkb, num_sms());
+      return launch_skinny(sargs, a_rows, static_cast<int>(st), splits, stream, status);
+    }
+    if (force_bn == 16 || force_bn == 17) return -11;
+  }
 
   const int sms = num_sms();
   auto count_tiles = [&](int bn) {

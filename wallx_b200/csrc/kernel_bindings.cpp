@@ -4,6 +4,8 @@
 #include <torch/extension.h>
 
 #include "comm.h"
+#include "decode.h"
+#include "launch.h"
 #include "kernels.h"
 
 namespace {
@@ -79,6 +81,48 @@ at::Tensor rope_qk(const at::Tensor& qkv, const at::Tensor& cos_t, const at::Ten
   WX_CHECK_RC(wx::rope_qk(qkv.data_ptr(), out.data_ptr(), cos_t.data_ptr<float>(), sin_t.data_ptr<float>(), qkv.size(0),
                           qkv.size(1), n_rot, D, inverse ? 1 : 0, cur_stream()),
               "rope_qk");
+  return out;
+}
+
+// Rotary on q and k of a packed q|k|v buffer (q in place); rotated k and v go to the rows' slots of the cache.
+void rope_cache(at::Tensor& qkv, const at::Tensor& cos_t, const at::Tensor& sin_t, const at::Tensor& cache_rows,
+                at::Tensor& cache, int64_t hq, int64_t hkv, int64_t D) {
+  check_bf16(qkv, "qkv");
+  TORCH_CHECK(qkv.is_contiguous() && cache.is_cuda() && cache.scalar_type() == at::kBFloat16 && cache.dim() == 2 &&
+              cache.stride(1) == 1, "rope_cache: contiguous bf16 qkv and a bf16 [rows, >= 2 hkv D] cache");
+  TORCH_CHECK(cos_t.scalar_type() == at::kFloat && sin_t.scalar_type() == at::kFloat && cos_t.is_contiguous() &&
+              sin_t.is_contiguous() && cos_t.size(0) == qkv.size(0) && cos_t.size(1) == D && sin_t.size(0) == qkv.size(0),
+              "rope_cache: cos/sin must be fp32 [T, D]");
+  TORCH_CHECK(cache_rows.is_cuda() && cache_rows.scalar_type() == at::kLong && cache_rows.is_contiguous() &&
+              cache_rows.numel() == qkv.size(0), "rope_cache: int64 cache row per token");
+  c10::cuda::CUDAGuard g(qkv.device());
+  WX_CHECK_RC(wx::rope_cache(qkv.data_ptr(), cos_t.data_ptr<float>(), sin_t.data_ptr<float>(), cache_rows.data_ptr<int64_t>(),
+                             cache.data_ptr(), qkv.size(0), qkv.size(1), hq, hkv, D, cache.stride(0), cache.size(0),
+                             cur_stream()),
+              "rope_cache");
+}
+
+bool attn_decode_supported(int64_t Tq, int64_t hq, int64_t hkv, int64_t D) {
+  return wx::attn_decode_supported(static_cast<int>(Tq), static_cast<int>(hq), static_cast<int>(hkv), static_cast<int>(D));
+}
+
+// Few query rows over cached keys / values (row-strided views are fine); tables as for the tensor-core kernel.
+at::Tensor attn_decode(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& qtab,
+                       const at::Tensor& ktab, int64_t hq, int64_t hkv, int64_t D, double scale) {
+  TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 &&
+              v.scalar_type() == at::kBFloat16 && q.dim() == 2 && k.dim() == 2 && v.dim() == 2 && q.stride(1) == 1 &&
+              k.stride(1) == 1 && v.stride(1) == 1, "attn_decode: bf16 row-strided q, k, v");
+  TORCH_CHECK(q.size(1) == hq * D && k.size(1) == hkv * D && v.size(1) == hkv * D && k.size(0) == v.size(0));
+  TORCH_CHECK(qtab.scalar_type() == at::kInt && qtab.is_contiguous() && qtab.size(0) == q.size(0) && qtab.size(1) == 4);
+  TORCH_CHECK(ktab.scalar_type() == at::kInt && ktab.is_contiguous() && ktab.size(0) == k.size(0) && ktab.size(1) == 4);
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(q.data_ptr()) % 16) == 0 && (reinterpret_cast<uintptr_t>(k.data_ptr()) % 16) == 0 &&
+              (reinterpret_cast<uintptr_t>(v.data_ptr()) % 16) == 0, "attn_decode: 16-byte aligned operands");
+  c10::cuda::CUDAGuard g(q.device());
+  at::Tensor out = at::empty({q.size(0), hq * D}, q.options());
+  WX_CHECK_RC(wx::attn_decode(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), qtab.data_ptr(),
+                              ktab.data_ptr(), out.data_ptr(), out.stride(0), q.size(0), k.size(0), hq, hkv, D,
+                              static_cast<float>(scale), cur_stream()),
+              "attn_decode");
   return out;
 }
 
@@ -279,6 +323,11 @@ void register_kernel_bindings(pybind11::module_& m) {
   m.def("rms_norm_bwd", &rms_norm_bwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("rope_qk", &rope_qk);
+  m.def("set_pdl", [](bool on) { wx::pdl_set(on); });
+  m.def("pdl_enabled", []() { return wx::pdl_enabled(); });
+  m.def("rope_cache", &rope_cache);
+  m.def("attn_decode", &attn_decode);
+  m.def("attn_decode_supported", &attn_decode_supported);
   m.def("route_plan", &route_plan);
   m.def("permute_rows", &permute_rows);
   m.def("gather_rows", &gather_rows);

@@ -9,6 +9,7 @@
 #include "kernels.h"
 #include "check.cuh"
 #include "devinfo.h"
+#include "launch.h"
 
 #include <cuda_bf16.h>
 #include <math.h>
@@ -194,6 +195,8 @@ rms_norm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
   constexpr int C = CH * 256;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const BF8* wr = reinterpret_cast<const BF8*>(w);
+  pdl_wait();
+  pdl_launch_dependents();
   for (int row = blockIdx.x * 8 + warp; row < T; row += gridDim.x * 8) {
     const BF8* xr = reinterpret_cast<const BF8*>(x + static_cast<size_t>(row) * C);
     BF8 raw[CH];
@@ -823,12 +826,13 @@ int rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, const int* 
     const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
     const __nv_bfloat16* wb = reinterpret_cast<const __nv_bfloat16*>(w);
     __nv_bfloat16* yb = reinterpret_cast<__nv_bfloat16*>(y);
+    cudaError_t e = cudaSuccess;
     switch (C / 256) {
-#define WX_CASE(n) case n: rms_norm_fwd_warp_kernel<n><<<g, 256, 0, s>>>(xb, wb, yb, rstd, dest, T, eps); break;
+#define WX_CASE(n) case n: e = launch_kernel(rms_norm_fwd_warp_kernel<n>, dim3(g), dim3(256), 0, s, xb, wb, yb, rstd, dest, T, eps); break;
       WX_CASE(1) WX_CASE(2) WX_CASE(3) WX_CASE(4) WX_CASE(5) WX_CASE(6) WX_CASE(7) WX_CASE(8)
 #undef WX_CASE
     }
-    return static_cast<int>(cudaGetLastError());
+    return static_cast<int>(e);
   }
   const int grid = T < sm_count() * 8 ? T : sm_count() * 8;
   rms_norm_fwd_kernel<<<grid, NORM_THREADS, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x),

@@ -15,6 +15,7 @@ evaluations. The Euler loop can be captured in a CUDA graph (``use_cuda_graph=Tr
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -102,6 +103,7 @@ class FlowSampler:
                                k_rows=self.cache.offsets[-1])
         cos, sin = model.model.rotary(pos3.index_select(1, pre_idx))
         plan = F_.make_route_plan(pre_types, cfg.num_experts) if cfg.mlp_moe else None
+        F_.RoutePlan.note_single_expert(plan, pre_types)
         meta_pre.device_tables(dev)
         self.ctx_pre = StepContext(meta_pre, cos, sin, plan, cache=self.cache, cache_mode="prefill")
 
@@ -122,6 +124,7 @@ class FlowSampler:
         meta_suf.device_tables(dev)
         cos_s, sin_s = model.model.rotary(pos3.index_select(1, suf_idx))
         plan_s = F_.make_route_plan(suf_types, cfg.num_experts) if cfg.mlp_moe else None
+        F_.RoutePlan.note_single_expert(plan_s, suf_types)
         self.ctx = StepContext(meta_suf, cos_s, sin_s, plan_s, cache=self.cache, cache_mode="step")
         self.dof_mask = dof_mask.to(dev, emb.dtype) if dof_mask is not None else None
         self.action_rows = torch.nonzero(self.suf_is_action, as_tuple=False).squeeze(1)
@@ -220,6 +223,18 @@ def predict_flow(model, pred_horizon=None, action_dim=None, input_ids=None, acti
     return out
 
 
+def _pdl_switch(on: bool):
+    """Turn programmatic dependent launch of the small inference kernels on (when the extension is there) and return
+    the setter, so that the caller can turn it off again."""
+    from ..ops import _ext
+
+    C = _ext.get(required=False)
+    if C is None or not hasattr(C, "set_pdl"):
+        return lambda _on: None
+    C.set_pdl(bool(on))
+    return C.set_pdl
+
+
 class FlowEngine:
     """Serving engine for a fixed observation layout: one CUDA graph per action chunk.
 
@@ -275,16 +290,22 @@ class FlowEngine:
         with torch.no_grad():
             self._run()  # eager warm-up: builds every cached table before capture
             if use_cuda_graph and dev.type == "cuda":
-                torch.cuda.synchronize(dev)
-                side = torch.cuda.Stream(device=dev)
-                side.wait_stream(torch.cuda.current_stream(dev))
-                with torch.cuda.stream(side):
-                    self._run()
-                torch.cuda.current_stream(dev).wait_stream(side)
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
-                    self._run()
-                self.graph = g
+                # Inside the graph the small kernels of the denoise loop are launched as programmatic dependents:
+                # each one's prologue overlaps the tail of the kernel before it (csrc/launch.h).
+                pdl = _pdl_switch(os.environ.get("WALLX_PDL", "1") == "1")
+                try:
+                    torch.cuda.synchronize(dev)
+                    side = torch.cuda.Stream(device=dev)
+                    side.wait_stream(torch.cuda.current_stream(dev))
+                    with torch.cuda.stream(side):
+                        self._run()
+                    torch.cuda.current_stream(dev).wait_stream(side)
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g):
+                        self._run()
+                    self.graph = g
+                finally:
+                    pdl(False)
 
     def _layout_signature(self, ids_host: torch.Tensor) -> torch.Tensor:
         sig = torch.zeros_like(ids_host, dtype=torch.int8)
@@ -363,6 +384,8 @@ class _Decoder:
                            k_rows=self.cache.offsets[-1])
         cos, sin = model.model.rotary(pos3)
         plan = F_.make_route_plan(types, cfg.num_experts) if cfg.mlp_moe else None
+        if plan is not None:
+            plan.single_expert = 0  # text generation: every token goes through the VLM expert
         ctx = StepContext(meta, cos, sin, plan, cache=self.cache, cache_mode="prefill")
         h = model.model(emb, ctx)
         last = torch.tensor([c - 1 for c in pack.cu[1:]], device=dev)
@@ -384,6 +407,8 @@ class _Decoder:
         self.next_pos = self.next_pos + 1
         cos, sin = m.model.rotary(pos3)
         plan = F_.make_route_plan(torch.zeros(B, dtype=torch.int32, device=dev), cfg.num_experts) if cfg.mlp_moe else None
+        if plan is not None:
+            plan.single_expert = 0
         ctx = StepContext(meta, cos, sin, plan, cache=self.cache, cache_mode="step")
         self.last_hidden = m.model(emb, ctx)
 

@@ -79,8 +79,15 @@ class Attention(nn.Module):
     def forward(self, x: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> torch.Tensor:
         hq, hkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         qkv = self.qkv_proj(x)
+        cached = not (ctx.cache is None or ctx.cache_mode == "none")
+        if cached and F_.cached_step_kernels_usable(qkv, d):
+            # rotary and cache write in one launch, then the small-query kernel when only a few rows are new
+            buf = ctx.cache.buffers[self.layer_idx]
+            F_.rope_cache_(qkv, ctx.cos, ctx.sin, ctx.meta.cache_rows, buf, hq, hkv, d)
+            o = F_.attention_decode(qkv[:, : hq * d], buf[:, : hkv * d], buf[:, hkv * d:], ctx.meta, hq, hkv, d)
+            return self.o_proj(o, residual=residual)
         qkv = F_.rope_qk(qkv, ctx.cos, ctx.sin, hq + hkv, d)
-        if ctx.cache is None or ctx.cache_mode == "none":
+        if not cached:
             o = F_.attention_packed(qkv, ctx.meta, hq, hkv, d)
         else:
             buf = ctx.cache.buffers[self.layer_idx]
@@ -144,6 +151,9 @@ class DecoderLayer(nn.Module):
                 n_rot=a.num_heads + a.num_kv_heads, hq=a.num_heads, hkv=a.num_kv_heads, d=a.head_dim,
                 eps=self.input_layernorm.variance_epsilon, plan=plan)
         x = self.self_attn(self.input_layernorm(x), ctx, residual=x)
+        if self.moe is not None and ctx.plan.single_expert is not None and not torch.is_grad_enabled():
+            # every token of this call belongs to one expert (known on the host): a plain FFN, no grouping of rows
+            return self.moe.experts[ctx.plan.single_expert](self.post_attention_layernorm(x), residual=x)
         if self.moe is not None:
             xp = self.post_attention_layernorm(x, dest=ctx.plan.dest, out_rows=ctx.plan.rows)
             return self.moe(xp, x, ctx.plan)

@@ -26,6 +26,7 @@ SOURCES = [
     "attention.cu",
     "comm.cu",
     "index.cu",
+    "decode.cu",
 ]
 
 NVCC_FLAGS = [

@@ -351,8 +351,22 @@ class RoutePlan:
     upper bound of the grouped buffer height.
     """
 
+    @staticmethod
+    def note_single_expert(plan: "Optional[RoutePlan]", token_types: torch.Tensor) -> None:
+        """Record on ``plan`` that all of ``token_types`` are equal (one host read; call outside hot loops)."""
+        if plan is None or token_types.numel() == 0:
+            return
+        t = token_types.reshape(-1)
+        first = int(t[0])
+        if bool((t == first).all()):
+            plan.single_expert = first
+
     def __init__(self, dest, seg, segk, inv, rows: int):
         self.dest, self.seg, self.segk, self.inv, self.rows = dest, seg, segk, inv, rows
+        # set by a caller that knows on the host that every token goes to one expert (the action rows of a denoise
+        # step, the text tokens of a decoding step): inference paths then run that expert as a plain FFN, without
+        # grouping rows
+        self.single_expert: Optional[int] = None
 
 
 def route_rows(T: int, num_experts: int) -> int:
@@ -743,6 +757,38 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, meta: AttnMeta,
     if _is_cuda(q):
         return _AttnFn.apply(q, k, v, meta, hq, hkv, d, scale)
     return _attention_torch(q, k, v, meta, hq, hkv, d, scale)
+
+
+DECODE_MAX_ROWS = 128  # query rows up to which the cached step uses the small-query attention kernel
+
+
+def cached_step_kernels_usable(qkv: torch.Tensor, d: int) -> bool:
+    """True when the fused rotary + cache write and the small-query attention kernel can serve this call: CUDA,
+    inference (they have no backward), contiguous bf16 q|k|v."""
+    return (_is_cuda(qkv) and not torch.is_grad_enabled() and qkv.dtype == torch.bfloat16 and qkv.is_contiguous()
+            and d % 16 == 0)
+
+
+def rope_cache_(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, cache_rows: torch.Tensor, cache: torch.Tensor,
+                hq: int, hkv: int, d: int) -> torch.Tensor:
+    """Rotary on the q and k heads of ``qkv`` (q rotated in place) with the rotated k and the v columns of row ``t``
+    written to row ``cache_rows[t]`` of ``cache [rows, 2 * hkv * d]``: the rotary kernel and the index copy of the
+    cached step in one launch. Returns ``qkv`` (only its q columns are meaningful afterwards)."""
+    _C().rope_cache(qkv, cos, sin, cache_rows, cache, int(hq), int(hkv), int(d))
+    return qkv
+
+
+def attention_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, meta: AttnMeta, hq: int, hkv: int, d: int,
+                     scale: Optional[float] = None) -> torch.Tensor:
+    """:func:`attention` for a handful of query rows over a long cached key range (decode and denoise steps): one CTA
+    per query row and key-value head with the keys staged in shared memory (csrc/decode.cu). Inference only; falls
+    back to :func:`attention` for shapes the kernel does not serve."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    if not (_is_cuda(q) and not torch.is_grad_enabled() and q.shape[0] <= DECODE_MAX_ROWS
+            and _C().attn_decode_supported(q.shape[0], hq, hkv, d)):
+        return attention(q, k, v, meta, hq, hkv, d, scale)
+    qtab, ktab = meta.device_tables(q.device)
+    return _C().attn_decode(q, k, v, qtab, ktab, int(hq), int(hkv), int(d), float(scale))
 
 
 def attention_packed(qkv: torch.Tensor, meta: AttnMeta, hq: int, hkv: int, d: int,

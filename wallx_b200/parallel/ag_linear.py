@@ -32,6 +32,19 @@ import os as _os
 # ten 16 KB bulk loads in flight (about 60 GB/s each over NVLink), and a layer's GEMMs need roughly 100 GB/s of remote
 # weight traffic to stay fed, so a handful suffices; each one is an SM the multiplication does not get.
 DEFAULT_PULLERS = int(_os.environ.get("WALLX_AG_PULLERS", "8"))
+_PULLERS_FROM_ENV = "WALLX_AG_PULLERS" in _os.environ
+
+
+def auto_pullers(specs: Sequence[G.GemmSpec], weights: Sequence[GatheredWeight]) -> int:
+    """Copy CTAs for a launch: enough that the remote rows arrive within the multiplication's own time. A copy CTA
+    moves about 60 GB/s and should run at half of that to stay ahead of the tiles; never fewer than the default
+    (start-up of the gather is latency-bound), never more than 32 (every copy CTA is an SM the GEMM does not get)."""
+    flops = sum(2.0 * s.M * s.N * s.K for s in specs)
+    remote = sum(2.0 * w.rows * w.cols * (w.world - 1) / max(w.world, 1) for w in weights)
+    t = max(flops / 1.2e15, 1e-6)
+    n = int(-(-remote // (t * 30e9)))
+    n = max(DEFAULT_PULLERS, min(32, n))
+    return (n + 1) & ~1
 
 
 class ShardedWeight(GatheredWeight):
@@ -82,7 +95,12 @@ class ShardedWeight(GatheredWeight):
 
 def ag_launch(specs: Sequence[G.GemmSpec], weights: Sequence[GatheredWeight], n_pullers: int = 0) -> None:
     """One launch of one or two problems; ``specs[i].b`` must be weight i's staging view (distinct slots)."""
-    np_ = int(n_pullers) if n_pullers else (weights[0].n_pullers or DEFAULT_PULLERS)
+    if n_pullers:
+        np_ = int(n_pullers)
+    elif weights[0].n_pullers:
+        np_ = weights[0].n_pullers  # fixed by the weight's first launch
+    else:
+        np_ = DEFAULT_PULLERS if _PULLERS_FROM_ENV else auto_pullers(specs, weights)
     for w in weights:
         w.pin_pullers(np_)
     _ext.get().gemm_ag([s.as_tuple() for s in specs], [w.peer_ptrs for w in weights], [w.flags for w in weights],
