@@ -17,6 +17,7 @@
 #include "check.cuh"
 #include "devinfo.h"
 #include "launch.h"
+#include "ptx.cuh"
 
 #include <atomic>
 
@@ -95,12 +96,17 @@ constexpr int kDecKPitch = 272;      // bytes per staged key row: 256 + 16, so t
                                      // bytes at a time fall into different banks
 constexpr int kDecVPitch = 256;
 constexpr int kDecMaxWarps = 4;
+constexpr int kDecMaxSplits = 8;     // CTAs of a cluster that share the key blocks of one query row
+constexpr int kDecComb = kDecD + 4;  // floats a warp hands to the combine step: its 128 channels, then m and l
 
+// About 70 KB, so that three CTAs fit on an SM: a CTA loads a block and then works on it, and the other CTAs of the
+// SM fill the time of its loads.
 struct DecSmem {
-  uint8_t k[2][kDecBlock * kDecKPitch];  // two blocks: the copy of the next one runs under the arithmetic of this one
-  uint8_t v[2][kDecBlock * kDecVPitch];
+  uint8_t k[kDecBlock * kDecKPitch];
+  uint8_t v[kDecBlock * kDecVPitch];
   float p[kDecMaxWarps][kDecBlock];
-  int vis[2][kDecBlock];
+  float comb[kDecMaxWarps][kDecComb];
+  int vis[kDecBlock];
 };
 
 // 16-byte asynchronous copy global -> shared; `bytes` = 0 writes zeros (rows past the key range)
@@ -108,26 +114,28 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, int
   const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
+// Grid: x = query row * splits + split (a cluster of `splits` CTAs per row), y = key-value head, z = group of `warps`
+// query heads. CTA `split` of a cluster takes the key blocks split, split + splits, ... of the row's key range; its
+// warps (one query head each) keep a running maximum, sum and weighted value sum, and leave them in shared memory.
+// After a cluster barrier the first CTA of the cluster merges the partial results in split order through distributed
+// shared memory and stores the row.
 __global__ void __launch_bounds__(kDecMaxWarps * 32)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long ldq, const __nv_bfloat16* __restrict__ k, long ldk,
                    const __nv_bfloat16* __restrict__ v, long ldv, const int4* __restrict__ qtab,
                    const int4* __restrict__ ktab, __nv_bfloat16* __restrict__ out, long ldo, int Tq, int Tk, int hq,
-                   int hkv, float scale_log2e, int warps) {
+                   int hkv, float scale_log2e, int warps, int splits) {
   extern __shared__ uint8_t dec_smem_raw[];
   DecSmem& sm = *reinterpret_cast<DecSmem*>((reinterpret_cast<uintptr_t>(dec_smem_raw) + 15) & ~uintptr_t(15));
-  const int row = static_cast<int>(blockIdx.x);
+  const int row = static_cast<int>(blockIdx.x) / splits;
+  const int split = static_cast<int>(blockIdx.x) - row * splits;  // = %cluster_ctarank
   const int kvh = static_cast<int>(blockIdx.y);
   const int rep = hq / hkv;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int head_in_group = static_cast<int>(blockIdx.z) * warps + warp;
-  const bool active = head_in_group < rep;  // warps past the last query head only help with the staging
+  const bool active = head_in_group < rep && warp < warps;  // other warps only help with the staging
   const int head = kvh * rep + head_in_group;
   pdl_wait();
   pdl_launch_dependents();
@@ -147,106 +155,143 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, long ldq, const __nv_bfl
   }
   float m = -INFINITY, l = 0.f;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
-
-  // stage one block of keys, values and visibility flags (all threads; nothing is waited for here)
   const int nthreads = static_cast<int>(blockDim.x);
-  auto stage = [&](int base, int buf) {
+
+  for (int base = k_lo + split * kDecBlock; base < k_hi; base += splits * kDecBlock) {
+    __syncthreads();  // everybody is done with the block before this one
     for (int i = threadIdx.x; i < kDecBlock * 16; i += nthreads) {
       const int r = i >> 4, piece = i & 15;
       const int j = base + r;
       const bool in = j < k_hi;
       const size_t jj = in ? static_cast<size_t>(j) : 0;  // a valid address even when nothing is read from it
-      cp_async16(sm.k[buf] + r * kDecKPitch + piece * 16, k + jj * ldk + kvh * kDecD + piece * 8, in ? 16 : 0);
-      cp_async16(sm.v[buf] + r * kDecVPitch + piece * 16, v + jj * ldv + kvh * kDecD + piece * 8, in ? 16 : 0);
+      cp_async16(sm.k + r * kDecKPitch + piece * 16, k + jj * ldk + kvh * kDecD + piece * 8, in ? 16 : 0);
+      cp_async16(sm.v + r * kDecVPitch + piece * 16, v + jj * ldv + kvh * kDecD + piece * 8, in ? 16 : 0);
     }
     for (int r = threadIdx.x; r < kDecBlock; r += nthreads) {
       const int j = base + r;
       int vis = 0;
       if (j < k_hi) vis = (j <= k_lim) || (qflag != 0 && (ktab[j].w & 1) != 0);
-      sm.vis[buf][r] = vis;
+      sm.vis[r] = vis;
     }
-    cp_async_commit();
-  };
-  if (k_lo < k_hi) stage(k_lo, 0);
-  int buf = 0;
-  for (int base = k_lo; base < k_hi; base += kDecBlock, buf ^= 1) {
-    // the other buffer was consumed before the barrier that ended the previous iteration
-    if (base + kDecBlock < k_hi) {
-      stage(base + kDecBlock, buf ^ 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();  // this block's copies (every thread's) have landed
-    const uint8_t* sk = sm.k[buf];
-    const uint8_t* sv = sm.v[buf];
-    const int* svis = sm.vis[buf];
-    if (active) {
-      // ---- scores: lane owns keys lane, lane + 32, lane + 64, lane + 96 of the block
-      float s[4];
+    cp_async_wait_all();
+    __syncthreads();  // the block (every thread's copies) has landed
+    if (!active) continue;
+    // ---- scores: lane owns keys lane, lane + 32, lane + 64, lane + 96 of the block (four independent sums)
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+    const uint8_t* kr = sm.k + lane * kDecKPitch;
+#pragma unroll
+    for (int cidx = 0; cidx < 16; ++cidx) {
+      float qf[8];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(qv[4 * cidx + e]);
+        qf[2 * e] = f.x;
+        qf[2 * e + 1] = f.y;
+      }
 #pragma unroll
       for (int r4 = 0; r4 < 4; ++r4) {
-        const int r = lane + 32 * r4;
-        const uint4* kr = reinterpret_cast<const uint4*>(sk + r * kDecKPitch);
-        float dot = 0.f;
+        const uint4 x = *reinterpret_cast<const uint4*>(kr + r4 * 32 * kDecKPitch + cidx * 16);
+        const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&x);
 #pragma unroll
-        for (int cidx = 0; cidx < 16; ++cidx) {
-          const uint4 x = kr[cidx];
-          const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&x);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 kf = __bfloat1622float2(xb[e]);
-            const float2 qf = __bfloat1622float2(qv[4 * cidx + e]);
-            dot = fmaf(kf.x, qf.x, dot);
-            dot = fmaf(kf.y, qf.y, dot);
-          }
+        for (int e = 0; e < 4; ++e) {
+          const float2 kf = __bfloat1622float2(xb[e]);
+          s[r4] = fmaf(kf.x, qf[2 * e], s[r4]);
+          s[r4] = fmaf(kf.y, qf[2 * e + 1], s[r4]);
         }
-        s[r4] = svis[r] ? dot * scale_log2e : -INFINITY;
-      }
-      float bm = fmaxf(fmaxf(s[0], s[1]), fmaxf(s[2], s[3]));
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
-      if (bm != -INFINITY) {  // something of this block is visible (uniform over the warp)
-        const float m_new = fmaxf(m, bm);
-        const float corr = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
-        float ps = 0.f;
-#pragma unroll
-        for (int r4 = 0; r4 < 4; ++r4) {
-          const float pj = (s[r4] == -INFINITY) ? 0.f : exp2f(s[r4] - m_new);
-          sm.p[warp][lane + 32 * r4] = pj;
-          ps += pj;
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
-        l = l * corr + ps;
-        m = m_new;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc[e] *= corr;
-        __syncwarp();
-        // ---- weighted values: lane owns channels 4 * lane .. 4 * lane + 3
-        const int nvalid = min(kDecBlock, k_hi - base);
-#pragma unroll 4
-        for (int j = 0; j < nvalid; ++j) {
-          const float pj = sm.p[warp][j];
-          const uint2 x = *reinterpret_cast<const uint2*>(sv + j * kDecVPitch + lane * 8);
-          const float2 v01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x.x));
-          const float2 v23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x.y));
-          acc[0] = fmaf(pj, v01.x, acc[0]);
-          acc[1] = fmaf(pj, v01.y, acc[1]);
-          acc[2] = fmaf(pj, v23.x, acc[2]);
-          acc[3] = fmaf(pj, v23.y, acc[3]);
-        }
-        __syncwarp();
       }
     }
-    __syncthreads();  // everybody is done with this buffer: the next iteration's copy may overwrite it
+#pragma unroll
+    for (int r4 = 0; r4 < 4; ++r4) s[r4] = sm.vis[lane + 32 * r4] ? s[r4] * scale_log2e : -INFINITY;
+    float bm = fmaxf(fmaxf(s[0], s[1]), fmaxf(s[2], s[3]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+    if (bm == -INFINITY) continue;  // nothing of this block is visible (uniform over the warp)
+    const float m_new = fmaxf(m, bm);
+    const float corr = (m == -INFINITY) ? 0.f : exp2f(m - m_new);
+    float ps = 0.f;
+#pragma unroll
+    for (int r4 = 0; r4 < 4; ++r4) {
+      const float pj = (s[r4] == -INFINITY) ? 0.f : exp2f(s[r4] - m_new);
+      sm.p[warp][lane + 32 * r4] = pj;
+      ps += pj;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+    l = l * corr + ps;
+    m = m_new;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[e] *= corr;
+    __syncwarp();
+    // ---- weighted values: lane owns channels 4 * lane .. 4 * lane + 3
+    const int nvalid = min(kDecBlock, k_hi - base);
+    const uint8_t* vr = sm.v + lane * 8;
+#pragma unroll 4
+    for (int j = 0; j < nvalid; ++j) {
+      const float pj = sm.p[warp][j];
+      const uint2 x = *reinterpret_cast<const uint2*>(vr + j * kDecVPitch);
+      const float2 v01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x.x));
+      const float2 v23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&x.y));
+      acc[0] = fmaf(pj, v01.x, acc[0]);
+      acc[1] = fmaf(pj, v01.y, acc[1]);
+      acc[2] = fmaf(pj, v23.x, acc[2]);
+      acc[3] = fmaf(pj, v23.y, acc[3]);
+    }
+    __syncwarp();
   }
-  if (!active) return;
-  const float inv = l > 0.f ? 1.f / l : 0.f;
-  uint2 o;
-  *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv);
-  *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
-  *reinterpret_cast<uint2*>(out + static_cast<size_t>(row) * ldo + head * kDecD + lane * 4) = o;
+
+  // ---- hand the partial result to the cluster's first CTA and merge there, in split order
+  if (active) {
+    *reinterpret_cast<float4*>(&sm.comb[warp][lane * 4]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    if (lane == 0) {
+      sm.comb[warp][kDecD] = m;
+      sm.comb[warp][kDecD + 1] = l;
+    }
+  }
+  __syncthreads();
+  if (splits > 1) {
+    cluster_arrive();
+    cluster_wait();
+  }
+  if (active && split == 0) {
+    const uint32_t mine = smem_u32(&sm.comb[warp][0]);
+    float ms[kDecMaxSplits];
+    float m_all = -INFINITY;
+#pragma unroll
+    for (int sp = 0; sp < kDecMaxSplits; ++sp) {
+      ms[sp] = -INFINITY;
+      if (sp < splits) {
+        const float4 ml = ld_cluster_f32x4(mapa_u32(mine + kDecD * 4, static_cast<uint32_t>(sp)));
+        ms[sp] = ml.x;
+        m_all = fmaxf(m_all, ml.x);
+      }
+    }
+    float o4[4] = {0.f, 0.f, 0.f, 0.f};
+    float l_all = 0.f;
+#pragma unroll
+    for (int sp = 0; sp < kDecMaxSplits; ++sp) {
+      if (sp < splits && ms[sp] != -INFINITY) {
+        const uint32_t peer = mapa_u32(mine, static_cast<uint32_t>(sp));
+        const float w = exp2f(ms[sp] - m_all);
+        const float4 a = ld_cluster_f32x4(peer + lane * 16);
+        const float4 ml = ld_cluster_f32x4(peer + kDecD * 4);
+        o4[0] = fmaf(w, a.x, o4[0]);
+        o4[1] = fmaf(w, a.y, o4[1]);
+        o4[2] = fmaf(w, a.z, o4[2]);
+        o4[3] = fmaf(w, a.w, o4[3]);
+        l_all = fmaf(w, ml.y, l_all);
+      }
+    }
+    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+    uint2 o;
+    *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(o4[0] * inv, o4[1] * inv);
+    *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(o4[2] * inv, o4[3] * inv);
+    *reinterpret_cast<uint2*>(out + static_cast<size_t>(row) * ldo + head * kDecD + lane * 4) = o;
+  }
+  if (splits > 1) {  // nobody leaves while the first CTA may still read its partial result
+    __syncthreads();
+    cluster_arrive();
+    cluster_wait();
+  }
 }
 
 }  // namespace
@@ -266,7 +311,7 @@ bool attn_decode_supported(int Tq, int hq, int hkv, int D) {
 }
 
 int attn_decode(const void* q, long ldq, const void* k, long ldk, const void* v, long ldv, const void* qtab,
-                const void* ktab, void* out, long ldo, int Tq, int Tk, int hq, int hkv, int D, float scale,
+                const void* ktab, void* out, long ldo, int Tq, int Tk, int hq, int hkv, int D, float scale, int max_keys,
                 cudaStream_t s) {
   if (!attn_decode_supported(Tq, hq, hkv, D)) return -1;
   if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 4)) return -2;
@@ -275,6 +320,10 @@ int attn_decode(const void* q, long ldq, const void* k, long ldk, const void* v,
   // fewer than two warps would leave the staging of a block to 32 threads: run at least two
   const int launch_warps = warps < 2 ? 2 : warps;
   const int z = (rep + warps - 1) / warps;
+  // one CTA per key block of the longest row, up to the cluster limit (rows with fewer blocks leave CTAs idle)
+  const int keys = max_keys > 0 && max_keys < Tk ? max_keys : Tk;
+  int splits = (keys + kDecBlock - 1) / kDecBlock;
+  splits = splits < 1 ? 1 : (splits > kDecMaxSplits ? kDecMaxSplits : splits);
   static bool attr_set = false;
   const int smem = static_cast<int>(sizeof(DecSmem)) + 16;
   if (!attr_set) {
@@ -282,12 +331,12 @@ int attn_decode(const void* q, long ldq, const void* k, long ldk, const void* v,
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set = true;
   }
-  return static_cast<int>(launch_kernel(
-      attn_decode_kernel, dim3(static_cast<unsigned>(Tq), static_cast<unsigned>(hkv), static_cast<unsigned>(z)),
-      dim3(launch_warps * 32), smem, s, reinterpret_cast<const __nv_bfloat16*>(q), ldq,
+  return static_cast<int>(launch_kernel_cluster(
+      attn_decode_kernel, dim3(static_cast<unsigned>(Tq * splits), static_cast<unsigned>(hkv), static_cast<unsigned>(z)),
+      dim3(launch_warps * 32), smem, s, static_cast<unsigned>(splits), reinterpret_cast<const __nv_bfloat16*>(q), ldq,
       reinterpret_cast<const __nv_bfloat16*>(k), ldk, reinterpret_cast<const __nv_bfloat16*>(v), ldv,
       reinterpret_cast<const int4*>(qtab), reinterpret_cast<const int4*>(ktab), reinterpret_cast<__nv_bfloat16*>(out), ldo,
-      Tq, Tk, hq, hkv, scale * 1.4426950408889634f, warps));
+      Tq, Tk, hq, hkv, scale * 1.4426950408889634f, warps, splits));
 }
 
 WX_CHK_DEFINE_READER(decode_check_read)

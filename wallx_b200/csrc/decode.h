@@ -13,10 +13,10 @@ int rope_cache(void* qkv, const float* cos_t, const float* sin_t, const long* ca
 
 // Attention of Tq <= 256 query rows over cached keys / values; `qtab` / `ktab` are the per-row tables of the
 // tensor-core attention kernel (int4 per query row: first key, end key, causal limit, flag; int4 per key row: bit 0 of
-// .w = flagged key).
+// .w = flagged key). `max_keys`: the longest key range of a query row (0: unknown), which sets how many CTAs share a row.
 bool attn_decode_supported(int Tq, int hq, int hkv, int D);
 int attn_decode(const void* q, long ldq, const void* k, long ldk, const void* v, long ldv, const void* qtab,
-                const void* ktab, void* out, long ldo, int Tq, int Tk, int hq, int hkv, int D, float scale,
+                const void* ktab, void* out, long ldo, int Tq, int Tk, int hq, int hkv, int D, float scale, int max_keys,
                 cudaStream_t s);
 
 int decode_check_read(long long* out4, int clear);

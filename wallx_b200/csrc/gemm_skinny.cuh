@@ -32,7 +32,9 @@ struct SkinnyCfg {
   static constexpr int A_BYTES = A_ROWS * BK * 2;
   static constexpr int B_BYTES = kSkinnyBN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (A_ROWS == 32) ? 16 : (A_ROWS == 64) ? 12 : 8;
+  // about 100 KB of stages, so that two CTAs fit on an SM: under programmatic dependent launch the CTAs of the next
+  // few-row GEMM then sit beside this one's and stream their weights while this one finishes
+  static constexpr int STAGES = (A_ROWS == 32) ? 8 : (A_ROWS == 64) ? 6 : 4;
   static constexpr int SLACK = BM * BK * 2 - A_BYTES;  // what the 128-row A descriptor reads beyond the last stage's rows
   static constexpr int PARTIAL_BYTES = A_ROWS * kSkinnyPitch * 4;  // aliases the start of the ring once the MMAs are done
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SLACK + 1024 + 512;
@@ -68,6 +70,10 @@ gemm_skinny_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ stat
   // runs while the kernel ahead in the stream is still finishing
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // With static sizes (no device-side row count or K) the weight loads depend on nothing an earlier kernel writes:
+  // they are issued here, ahead of the wait on that kernel; the activation loads follow the wait.
+  const int tile_n = nt * kSkinnyBN;
+  int early = 0;
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -78,6 +84,16 @@ gemm_skinny_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ stat
     fence_mbar_init();
     tma_prefetch_desc(&p.tmA);
     tma_prefetch_desc(&p.tmB);
+    if (p.dyn == nullptr && p.M > 0 && p.M <= A_ROWS && p.K > 0 && (p.k0 & 7) == 0 && tile_n < p.N) {
+      const int nkb_s = (p.K + BK - 1) / BK;
+      const int b0 = static_cast<int>(static_cast<long>(nkb_s) * rank / splits);
+      const int b1 = static_cast<int>(static_cast<long>(nkb_s) * (rank + 1) / splits);
+      early = min(b1 - b0, C::STAGES);
+      for (int j = 0; j < early; ++j) {
+        mbar_arrive_expect_tx(&full_bar[j], C::STAGE_BYTES);
+        tma_load_2d(smem + j * C::STAGE_BYTES + C::A_BYTES, &p.tmB, &full_bar[j], p.k0 + (b0 + j) * BK, tile_n);
+      }
+    }
   }
   if (warp == 2) {
     tmem_alloc(tmem_slot, kSkinnyBN);
@@ -117,9 +133,11 @@ gemm_skinny_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ stat
           const int use = j / C::STAGES;
           if (use > 0 && !mbar_wait(&empty_bar[s], static_cast<uint32_t>(use - 1) & 1u, abort_flag)) break;
           uint8_t* sA = smem + s * C::STAGE_BYTES;
-          mbar_arrive_expect_tx(&full_bar[s], C::STAGE_BYTES);
           const int kc = k0 + (kb0 + j) * BK;
-          tma_load_2d(sA + C::A_BYTES, &p.tmB, &full_bar[s], kc, n_base);  // the weight slice first: it comes from DRAM
+          if (j >= early) {  // (the first `early` weight slices are already on their way)
+            mbar_arrive_expect_tx(&full_bar[s], C::STAGE_BYTES);
+            tma_load_2d(sA + C::A_BYTES, &p.tmB, &full_bar[s], kc, n_base);  // the weight slice first: it comes from DRAM
+          }
           tma_load_2d(sA, &p.tmA, &full_bar[s], kc, m0);
         }
       }

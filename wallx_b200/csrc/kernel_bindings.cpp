@@ -108,7 +108,7 @@ bool attn_decode_supported(int64_t Tq, int64_t hq, int64_t hkv, int64_t D) {
 
 // Few query rows over cached keys / values (row-strided views are fine); tables as for the tensor-core kernel.
 at::Tensor attn_decode(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& qtab,
-                       const at::Tensor& ktab, int64_t hq, int64_t hkv, int64_t D, double scale) {
+                       const at::Tensor& ktab, int64_t hq, int64_t hkv, int64_t D, double scale, int64_t max_keys) {
   TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 &&
               v.scalar_type() == at::kBFloat16 && q.dim() == 2 && k.dim() == 2 && v.dim() == 2 && q.stride(1) == 1 &&
               k.stride(1) == 1 && v.stride(1) == 1, "attn_decode: bf16 row-strided q, k, v");
@@ -121,7 +121,7 @@ at::Tensor attn_decode(const at::Tensor& q, const at::Tensor& k, const at::Tenso
   at::Tensor out = at::empty({q.size(0), hq * D}, q.options());
   WX_CHECK_RC(wx::attn_decode(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), qtab.data_ptr(),
                               ktab.data_ptr(), out.data_ptr(), out.stride(0), q.size(0), k.size(0), hq, hkv, D,
-                              static_cast<float>(scale), cur_stream()),
+                              static_cast<float>(scale), static_cast<int>(max_keys), cur_stream()),
               "attn_decode");
   return out;
 }

@@ -788,7 +788,8 @@ def attention_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, meta: At
             and _C().attn_decode_supported(q.shape[0], hq, hkv, d)):
         return attention(q, k, v, meta, hq, hkv, d, scale)
     qtab, ktab = meta.device_tables(q.device)
-    return _C().attn_decode(q, k, v, qtab, ktab, int(hq), int(hkv), int(d), float(scale))
+    max_keys = max((k1 - k0 for k0, k1 in meta.k_ranges), default=0)
+    return _C().attn_decode(q, k, v, qtab, ktab, int(hq), int(hkv), int(d), float(scale), int(max_keys))
 
 
 def attention_packed(qkv: torch.Tensor, meta: AttnMeta, hq: int, hkv: int, d: int,
