@@ -91,7 +91,7 @@ def test_release_build_contains_no_range_check_code():
     nvcc = shutil.which("nvcc")
     csrc = ROOT / "wallx_b200" / "csrc"
     if nvcc is not None:
-        for unit in ("kernels.cu", "index.cu", "comm.cu"):
+        for unit in ("kernels.cu", "index.cu", "comm.cu", "decode.cu"):
             base = [nvcc, "-E", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-I", str(csrc), str(csrc / unit)]
             plain = subprocess.run(base, capture_output=True, text=True, check=True).stdout
             checked = subprocess.run(base + ["-DWX_CHECK"], capture_output=True, text=True, check=True).stdout
