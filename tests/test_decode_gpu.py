@@ -44,6 +44,34 @@ def test_few_row_gemm_matches_fp32_and_the_general_kernel(M, N, K):
     assert torch.equal(split, auto)
 
 
+@pytest.mark.parametrize("M,N,K", [(314, 2048, 11008), (200, 2560, 2048), (972, 1280, 3456), (1024, 2048, 2048),
+                                   (314, 4096, 2048)])
+def test_prefix_sized_gemm_on_k_splitting_clusters(M, N, K):
+    """Launches made inside an ``inference_kernels`` region with autograd off may run a few hundred rows on 128 x 256
+    tiles whose K range is split over a cluster; all other launches keep the general kernel. Both against fp32, and the
+    split sum must not depend on timing."""
+    from wallx_b200.ops import gemm as G
+
+    g = torch.Generator().manual_seed(M + N + K)
+    a = _bf(torch.randn(M, K, generator=g))
+    w = _bf(torch.randn(N, K, generator=g) * 0.03)
+    bias = _bf(torch.randn(N, generator=g))
+    res = _bf(torch.randn(M, N, generator=g))
+    ref = a.float() @ w.float().t() + bias.float() + res.float()
+    train = G.gemm(a, w, bias=bias, residual=res)
+    with torch.no_grad():
+        plain = G.gemm(a, w, bias=bias, residual=res)
+        with G.inference_kernels():
+            infer = G.gemm(a, w, bias=bias, residual=res)
+            again = G.gemm(a, w, bias=bias, residual=res)
+    torch.cuda.synchronize()
+    G.check_status()
+    assert torch.equal(train, plain), "grad mode alone must not change the kernel"
+    _close(train, ref, 1e-2, what="general kernel")
+    _close(infer, ref, 1e-2, what="inference launch")
+    assert torch.equal(infer, again)
+
+
 def test_few_row_gemm_swiglu_fp32_out_and_device_side_sizes():
     from wallx_b200.ops import gemm as G, ref
 

@@ -870,13 +870,20 @@ int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* sta
 
   // Few rows (decode, denoise steps): clusters of CTAs that split K (gemm_skinny.cuh). force_bn = 16 selects that
   // kernel where it is legal, 17 the same with one CTA per column tile (no split); other forced widths bypass it.
+  // force_bn = 18 is "automatic, inference": it also lets problems of up to 1024 rows whose 128 x 256 tiles fill less
+  // than half of the SMs run on K-splitting clusters (prefix passes: few tiles, long K, one serial chain per tile).
+  // Training launches (0) never take that second path, so its different summation order cannot enter a comparison
+  // of training runs.
+  const bool infer = force_bn == 18;
+  if (infer) force_bn = 0;
   if (!a_mn && !b_mn && (force_bn == 0 || force_bn == 16 || force_bn == 17)) {
     int max_m = 0, min_nkb = 1 << 30;
-    long st = 0;
+    long st = 0, mid = 0;
     bool plain = true;
     for (int i = 0; i < ncalls; ++i) {
       max_m = calls[i].M > max_m ? calls[i].M : max_m;
       st += (calls[i].N + kSkinnyBN - 1) / kSkinnyBN;
+      mid += static_cast<long>((calls[i].N + kMidBN - 1) / kMidBN) * ((calls[i].M + BM - 1) / BM);
       const int nkb = (calls[i].K + BK - 1) / BK;
       min_nkb = nkb < min_nkb ? nkb : min_nkb;
       if ((calls[i].flags & (GEMM_ACT_SWIGLU | GEMM_SWIGLU_BWD)) && (calls[i].N % 32 != 0)) plain = false;
@@ -888,9 +895,18 @@ int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* sta
       const int src = fill_args(sargs, calls, ncalls, kSkinnyBN, a_rows);
       if (src != 0) return src;
       const int splits = force_bn == 17 ? 1 : skinny_splits(st, min_nkb, num_sms());
-      return launch_skinny(sargs, a_rows, static_cast<int>(st), splits, stream, status);
+      return launch_skinny(sargs, a_rows, kSkinnyBN, static_cast<int>(st), splits, stream, status);
     }
     if (force_bn == 16 || force_bn == 17) return -11;
+    if (infer && plain && max_m > BM && max_m <= 1024 && mid >= 1) {
+      const int splits = skinny_splits(mid, min_nkb, num_sms());
+      if (splits >= 2) {
+        GemmArgs sargs;
+        const int src = fill_args(sargs, calls, ncalls, kMidBN, BM);
+        if (src != 0) return src;
+        return launch_skinny(sargs, BM, kMidBN, static_cast<int>(mid), splits, stream, status);
+      }
+    }
   }
 
   const int sms = num_sms();

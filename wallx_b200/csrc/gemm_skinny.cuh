@@ -24,36 +24,45 @@ namespace {
 
 constexpr int kSkinnyBN = 64;
 constexpr int kSkinnyThreads = 192;  // TMA warp, MMA warp, 4 epilogue warps (one per TMEM lane quarter)
-constexpr int kSkinnyPitch = kSkinnyBN + 4;  // floats per row of the partial tile (16-byte row stores without conflicts)
+constexpr int kMidBN = 256;    // tile width of the same kernel for 129..1024 rows (128-row tiles, see gemm_launch)
 constexpr int kSkinnyMaxSplits = 8;          // portable cluster size
 
-template <int A_ROWS>
+__device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
+
+template <int A_ROWS, int BN>
 struct SkinnyCfg {
   static constexpr int A_BYTES = A_ROWS * BK * 2;
-  static constexpr int B_BYTES = kSkinnyBN * BK * 2;
+  static constexpr int PITCH = BN + 4;  // floats per row of the partial tile (16-byte row stores without conflicts)
+  static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   // about 100 KB of stages, so that two CTAs fit on an SM: under programmatic dependent launch the CTAs of the next
   // few-row GEMM then sit beside this one's and stream their weights while this one finishes
-  static constexpr int STAGES = (A_ROWS == 32) ? 8 : (A_ROWS == 64) ? 6 : 4;
+  static constexpr int STAGES = (BN == 256) ? 4 : (A_ROWS == 32) ? 8 : (A_ROWS == 64) ? 6 : 4;
   static constexpr int SLACK = BM * BK * 2 - A_BYTES;  // what the 128-row A descriptor reads beyond the last stage's rows
-  static constexpr int PARTIAL_BYTES = A_ROWS * kSkinnyPitch * 4;  // aliases the start of the ring once the MMAs are done
+  static constexpr int PARTIAL_BYTES = A_ROWS * PITCH * 4;  // aliases the start of the ring once the MMAs are done
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SLACK + 1024 + 512;
   static_assert(SMEM_BYTES <= 227 * 1024, "stage ring does not fit");
   static_assert(STAGE_BYTES % 1024 == 0, "stages must keep the 1024-byte alignment of the swizzle pattern");
   static_assert(PARTIAL_BYTES <= STAGES * STAGE_BYTES, "partial tile must fit in the ring");
 };
 
-template <int A_ROWS>
+template <int A_ROWS, int BN>
 __global__ void __launch_bounds__(kSkinnyThreads, 1)
 gemm_skinny_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ status, int splits) {
-  using C = SkinnyCfg<A_ROWS>;
+  using C = SkinnyCfg<A_ROWS, BN>;
   // Clusters are laid out from the static sizes (problem 0's column tiles, then problem 1's); the row count and K
   // may be smaller on the device (dyn). Everything that decides whether a CTA works is uniform over its cluster.
   const int tile = static_cast<int>(blockIdx.x) / splits;
   const int rank = static_cast<int>(blockIdx.x) - tile * splits;  // = %cluster_ctarank
-  const int tn0 = (args.p[0].N + kSkinnyBN - 1) / kSkinnyBN;
-  const int prob = tile < tn0 ? 0 : 1;
-  const int nt = tile - (prob ? tn0 : 0);
+  // tiles of a problem: column tiles x 128-row tiles (static row count), row tiles fastest so that the clusters
+  // which share a weight slice run at the same time
+  const int mt0 = (args.p[0].M + BM - 1) / BM;
+  const int t0 = ((args.p[0].N + BN - 1) / BN) * mt0;
+  const int prob = tile < t0 ? 0 : 1;
+  const int mtiles = prob ? (args.p[1].M + BM - 1) / BM : mt0;
+  const int tp = tile - (prob ? t0 : 0);
+  const int nt = tp / mtiles;
+  const int mt = tp - nt * mtiles;
   if (prob >= args.nprob) return;  // cannot happen with the host's grid
   const Problem& p = args.p[prob];
 
@@ -72,7 +81,7 @@ gemm_skinny_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ stat
   const int lane = threadIdx.x & 31;
   // With static sizes (no device-side row count or K) the weight loads depend on nothing an earlier kernel writes:
   // they are issued here, ahead of the wait on that kernel; the activation loads follow the wait.
-  const int tile_n = nt * kSkinnyBN;
+  const int tile_n = nt * BN;
   int early = 0;
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -84,7 +93,7 @@ gemm_skinny_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ stat
     fence_mbar_init();
     tma_prefetch_desc(&p.tmA);
     tma_prefetch_desc(&p.tmB);
-    if (p.dyn == nullptr && p.M > 0 && p.M <= A_ROWS && p.K > 0 && (p.k0 & 7) == 0 && tile_n < p.N) {
+    if (p.dyn == nullptr && p.M > mt * BM && p.K > 0 && (p.k0 & 7) == 0 && tile_n < p.N) {
       const int nkb_s = (p.K + BK - 1) / BK;
       const int b0 = static_cast<int>(static_cast<long>(nkb_s) * rank / splits);
       const int b1 = static_cast<int>(static_cast<long>(nkb_s) * (rank + 1) / splits);
@@ -96,7 +105,7 @@ gemm_skinny_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ stat
     }
   }
   if (warp == 2) {
-    tmem_alloc(tmem_slot, kSkinnyBN);
+    tmem_alloc(tmem_slot, BN);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -115,13 +124,16 @@ gemm_skinny_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ stat
     if (d3 >= 0) K = d3;
   }
   // a problem without rows on the device, or a column tile past N: nothing to do (uniform over the cluster)
-  const bool live = M > 0 && K > 0 && nt * kSkinnyBN < p.N && WX_CHK(M <= A_ROWS && (k0 & 7) == 0, 2006, M, k0);
+  M -= mt * BM;  // rows of this tile (the last row tile of a problem may be short, or empty on the device)
+  m0 += mt * BM;
+  if (M > BM) M = BM;
+  const bool live = M > 0 && K > 0 && nt * BN < p.N && WX_CHK(M <= A_ROWS && (k0 & 7) == 0, 2006, M, k0);
 
   const int nkb = (K + BK - 1) / BK;
   const int kb0 = static_cast<int>(static_cast<long>(nkb) * rank / splits);
   const int kb1 = static_cast<int>(static_cast<long>(nkb) * (rank + 1) / splits);
   const int nblk = kb1 - kb0;  // this CTA's k blocks (0 when there are more CTAs than blocks: it contributes zeros)
-  const int n_base = nt * kSkinnyBN;
+  const int n_base = nt * BN;
 
   if (!live) {
     // straight to the teardown: no cluster barrier is used by a cluster that does not work
@@ -143,7 +155,7 @@ gemm_skinny_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ stat
       }
     } else if (warp == 1) {
       if (lane == 0) {
-        constexpr uint32_t idesc = make_idesc_bf16(BM, kSkinnyBN, false, false);
+        constexpr uint32_t idesc = make_idesc_bf16(BM, BN, false, false);
         bool ok = true;
         for (int j = 0; j < nblk; ++j) {
           const int s = j % C::STAGES;
@@ -172,9 +184,9 @@ gemm_skinny_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ stat
           have = mbar_wait(tfull_bar, 0u, abort_flag);
           tc_fence_after();
         }
-        float* prow = partial + (quarter * 32 + lane) * kSkinnyPitch;
+        float* prow = partial + (quarter * 32 + lane) * C::PITCH;
 #pragma unroll
-        for (int c = 0; c < kSkinnyBN / 32; ++c) {
+        for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
           if (have) {
             tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c * 32, r);
@@ -190,6 +202,22 @@ gemm_skinny_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ stat
         tc_fence_before();
       }
     }
+    // What the epilogue of this thread's first piece will read from global memory (row map, residual, bias) is
+    // requested now, so that it arrives while the cluster barrier is being waited for.
+    const int pieces = M * (BN / 32);
+    {
+      const int i = static_cast<int>(threadIdx.x) * splits + rank;
+      if (i < pieces) {
+        const int r = i / (BN / 32);
+        const int n0 = n_base + (i - r * (BN / 32)) * 32;
+        long drow = static_cast<long>(m0) + r;
+        if (p.row_map != nullptr) drow = p.row_map[drow];
+        if (drow >= 0 && n0 < p.N) {
+          if (p.residual != nullptr) prefetch_l1(p.residual + drow * p.ldr + n0);
+          if (p.bias != nullptr) prefetch_l1(p.bias + n0);
+        }
+      }
+    }
     // (the tile overwrites the first stages: every MMA that read them has completed, tfull_bar says so)
     __syncthreads();
     if (splits > 1) {
@@ -197,19 +225,18 @@ gemm_skinny_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ stat
       cluster_wait();
     }
     // ---- sum over the cluster and epilogue: piece i = (row i / 2, 32-column half i % 2) goes to CTA i % splits
-    const int pieces = M * (kSkinnyBN / 32);
     const uint32_t partial_addr = smem_u32(partial);
     for (int slot = threadIdx.x;; slot += kSkinnyThreads) {
       const int i = slot * splits + rank;
       if (i >= pieces) break;
-      const int r = i / (kSkinnyBN / 32);
-      const int c = i - r * (kSkinnyBN / 32);
+      const int r = i / (BN / 32);
+      const int c = i - r * (BN / 32);
       const int n0 = n_base + c * 32;
       if (n0 >= p.N) continue;
       float v[32];
 #pragma unroll
       for (int e = 0; e < 32; ++e) v[e] = 0.f;
-      const uint32_t off = static_cast<uint32_t>((r * kSkinnyPitch + c * 32) * 4);
+      const uint32_t off = static_cast<uint32_t>((r * C::PITCH + c * 32) * 4);
       for (int s = 0; s < splits; ++s) {
         const uint32_t base = mapa_u32(partial_addr + off, static_cast<uint32_t>(s));
 #pragma unroll
@@ -242,14 +269,14 @@ gemm_skinny_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ stat
   if (threadIdx.x == 0 && *abort_flag) atomicExch(status, 1);
   if (warp == 2) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kSkinnyBN);
+    tmem_dealloc(tmem_base, BN);
   }
 }
 
-template <int A_ROWS>
+template <int A_ROWS, int BN>
 int launch_skinny_t(const GemmArgs& args, int tiles, int splits, cudaStream_t stream, int* status) {
-  using C = SkinnyCfg<A_ROWS>;
-  auto kern = gemm_skinny_kernel<A_ROWS>;
+  using C = SkinnyCfg<A_ROWS, BN>;
+  auto kern = gemm_skinny_kernel<A_ROWS, BN>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
@@ -270,10 +297,11 @@ inline int skinny_splits(long tiles, int min_nkb, int sms) {
   return s;
 }
 
-int launch_skinny(const GemmArgs& args, int a_rows, int tiles, int splits, cudaStream_t stream, int* status) {
-  if (a_rows == 32) return launch_skinny_t<32>(args, tiles, splits, stream, status);
-  if (a_rows == 64) return launch_skinny_t<64>(args, tiles, splits, stream, status);
-  return launch_skinny_t<128>(args, tiles, splits, stream, status);
+int launch_skinny(const GemmArgs& args, int a_rows, int bn, int tiles, int splits, cudaStream_t stream, int* status) {
+  if (bn == kMidBN) return launch_skinny_t<128, kMidBN>(args, tiles, splits, stream, status);
+  if (a_rows == 32) return launch_skinny_t<32, kSkinnyBN>(args, tiles, splits, stream, status);
+  if (a_rows == 64) return launch_skinny_t<64, kSkinnyBN>(args, tiles, splits, stream, status);
+  return launch_skinny_t<128, kSkinnyBN>(args, tiles, splits, stream, status);
 }
 
 }  // namespace

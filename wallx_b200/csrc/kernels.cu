@@ -187,7 +187,9 @@ rms_norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* _
 // ------------------------------------------------------------------------------ RMSNorm, one warp per row
 // For C = 256 * CH <= 2048 a warp owns a whole row: CH 16-byte loads per lane are in flight at
 // once and the reduction is shuffles only (no block barrier per row). Eight rows per block.
-template <int CH>
+// EARLY_W (few rows: the kernel is one chain of latencies) requests the weight chunks together with the row instead of
+// after the reduction; with many rows the extra registers would cost occupancy, so the streaming case keeps them late.
+template <int CH, bool EARLY_W>
 __global__ void __launch_bounds__(256)
 rms_norm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                          __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, const int* __restrict__ dest,
@@ -199,9 +201,13 @@ rms_norm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
   pdl_launch_dependents();
   for (int row = blockIdx.x * 8 + warp; row < T; row += gridDim.x * 8) {
     const BF8* xr = reinterpret_cast<const BF8*>(x + static_cast<size_t>(row) * C);
-    BF8 raw[CH];
+    BF8 raw[CH], wraw[EARLY_W ? CH : 1];
 #pragma unroll
     for (int c = 0; c < CH; ++c) raw[c] = xr[lane + 32 * c];
+    if (EARLY_W) {
+#pragma unroll
+      for (int c = 0; c < CH; ++c) wraw[c] = wr[lane + 32 * c];
+    }
     float v[CH][8];
     float ss = 0.f;
 #pragma unroll
@@ -218,7 +224,7 @@ rms_norm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
       float wf[8], o[8];
-      unpack8(wr[lane + 32 * c], wf);
+      unpack8(EARLY_W ? wraw[c] : wr[lane + 32 * c], wf);
 #pragma unroll
       for (int e = 0; e < 8; ++e) o[e] = wf[e] * bf16_round(v[c][e] * rstd);
       yr[lane + 32 * c] = pack8(o);
@@ -828,7 +834,11 @@ int rms_norm_fwd(const void* x, const void* w, void* y, float* rstd, const int* 
     __nv_bfloat16* yb = reinterpret_cast<__nv_bfloat16*>(y);
     cudaError_t e = cudaSuccess;
     switch (C / 256) {
-#define WX_CASE(n) case n: e = launch_kernel(rms_norm_fwd_warp_kernel<n>, dim3(g), dim3(256), 0, s, xb, wb, yb, rstd, dest, T, eps); break;
+#define WX_CASE(n)                                                                                                        \
+  case n:                                                                                                                 \
+    e = (T <= 1024) ? launch_kernel(rms_norm_fwd_warp_kernel<n, true>, dim3(g), dim3(256), 0, s, xb, wb, yb, rstd, dest, T, eps) \
+                    : launch_kernel(rms_norm_fwd_warp_kernel<n, false>, dim3(g), dim3(256), 0, s, xb, wb, yb, rstd, dest, T, eps); \
+    break;
       WX_CASE(1) WX_CASE(2) WX_CASE(3) WX_CASE(4) WX_CASE(5) WX_CASE(6) WX_CASE(7) WX_CASE(8)
 #undef WX_CASE
     }

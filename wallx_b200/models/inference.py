@@ -21,6 +21,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..ops import functional as F_
+from ..ops.gemm import inference_kernels
 from .llm import KVCache, StepContext
 
 
@@ -204,6 +205,7 @@ class FlowSampler:
         return static_out.clone()
 
 
+@inference_kernels()
 @torch.no_grad()
 def predict_flow(model, pred_horizon=None, action_dim=None, input_ids=None, action_chunk=None, dataset_names=None,
                  dof_mask=None, num_inference_timesteps=10, noise=None, reference_grid=False, use_cuda_graph=False,
@@ -268,7 +270,7 @@ class FlowEngine:
             self.grid_host = [[int(v) for v in g] for g in self.grid.tolist()]
         layout = {k: v for k, v in example.items() if k not in self.INPUT_KEYS and k not in ("action_chunk", "labels")}
         layout["image_grid_host"] = self.grid_host
-        with torch.no_grad():
+        with torch.no_grad(), inference_kernels():
             self.sampler = FlowSampler(model, self.static["input_ids"], dataset_names=self.names,
                                        pixel_values=self.static.get("pixel_values"),
                                        proprioception=self.static.get("proprioception"),
@@ -313,6 +315,7 @@ class FlowEngine:
             sig[ids_host == t] = i + 1
         return sig
 
+    @inference_kernels()
     def _run(self) -> None:
         s, m = self.sampler, self.model
         ids = self.static["input_ids"].reshape(-1).index_select(0, s.pack.pack_index)
@@ -413,6 +416,7 @@ class _Decoder:
         self.last_hidden = m.model(emb, ctx)
 
 
+@inference_kernels()
 @torch.no_grad()
 def generate(model, input_ids, max_new_tokens: int = 100, do_sample: bool = False, temperature: float = 1.0,
              eos_token_id=None, pad_token_id=None, top_k: Optional[int] = None, generator=None, **mm) -> torch.Tensor:
@@ -447,6 +451,7 @@ def generate(model, input_ids, max_new_tokens: int = 100, do_sample: bool = Fals
     return torch.cat([input_ids.to(dec.dev), gen], dim=1)
 
 
+@inference_kernels()
 @torch.no_grad()
 def predict_text(model, predict_mode: str, pred_horizon=None, action_dim=None, input_ids=None, attention_mask=None,
                  pixel_values=None, image_grid_thw=None, action_chunk=None, proprioception=None, dataset_names=None,

@@ -47,8 +47,48 @@ class GemmSpec:
                 self.row_map, self.dyn, self.out2, self.flags, self.m0, self.k0)
 
 
+INFERENCE_AUTO = 18  # "choose the tile shape, inference": also allows K-splitting clusters for prefix-sized problems
+
+
+_inference_depth = 0
+
+
+class inference_kernels:
+    """Context manager (re-entrant) around inference-only code: launches inside it may use kernels whose results are
+    deterministic but not bit-identical to the training kernels' (K-splitting clusters for prefix-sized problems).
+    Grad mode cannot serve as the signal: autograd functions run both their forward and their backward with it off."""
+
+    def __enter__(self):
+        global _inference_depth
+        _inference_depth += 1
+        return self
+
+    def __exit__(self, *exc):
+        global _inference_depth
+        _inference_depth -= 1
+        return False
+
+    def __call__(self, fn):
+        import functools
+
+        @functools.wraps(fn)
+        def wrapped(*a, **k):
+            with inference_kernels():
+                return fn(*a, **k)
+
+        return wrapped
+
+
+def _inference_launch() -> bool:
+    return _inference_depth > 0 and not torch.is_grad_enabled()
+
+
 def launch(specs: Sequence[GemmSpec], force_bn: int = 0) -> None:
-    """Run one or two problems in a single persistent launch."""
+    """Run one or two problems in a single persistent launch. Without a forced tile shape, launches made while autograd
+    is off inside an :class:`inference_kernels` region may use K-splitting clusters for problems of a few hundred rows (a
+    different, still deterministic, order of the sum over K); launches of a training step never do."""
+    if force_bn == 0 and _inference_launch():
+        force_bn = INFERENCE_AUTO
     _ext.get().gemm_grouped([s.as_tuple() for s in specs], int(force_bn))
 
 
