@@ -44,7 +44,7 @@ def test_few_row_gemm_matches_fp32_and_the_general_kernel(M, N, K):
     assert torch.equal(split, auto)
 
 
-@pytest.mark.parametrize("M,N,K", [(314, 2048, 11008), (200, 2560, 2048), (972, 1280, 3456), (1024, 2048, 2048),
+@pytest.mark.parametrize("M,N,K", [(314, 2048, 11008), (200, 2560, 4096), (972, 1280, 4160), (1024, 2048, 8192),
                                    (314, 4096, 2048)])
 def test_prefix_sized_gemm_on_k_splitting_clusters(M, N, K):
     """Launches made inside an ``inference_kernels`` region with autograd off may run a few hundred rows on 128 x 256

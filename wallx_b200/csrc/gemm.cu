@@ -871,7 +871,8 @@ int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* sta
   // Few rows (decode, denoise steps): clusters of CTAs that split K (gemm_skinny.cuh). force_bn = 16 selects that
   // kernel where it is legal, 17 the same with one CTA per column tile (no split); other forced widths bypass it.
   // force_bn = 18 is "automatic, inference": it also lets problems of up to 1024 rows whose 128 x 256 tiles fill less
-  // than half of the SMs run on K-splitting clusters (prefix passes: few tiles, long K, one serial chain per tile).
+  // than half of the SMs and whose K is 4096 or more run on K-splitting clusters (prefix passes: few tiles, long K, one
+  // serial chain per tile).
   // Training launches (0) never take that second path, so its different summation order cannot enter a comparison
   // of training runs.
   const bool infer = force_bn == 18;
@@ -898,7 +899,9 @@ int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* sta
       return launch_skinny(sargs, a_rows, kSkinnyBN, static_cast<int>(st), splits, stream, status);
     }
     if (force_bn == 16 || force_bn == 17) return -11;
-    if (infer && plain && max_m > BM && max_m <= 1024 && mid >= 1) {
+    // (measured in CUDA graphs at 314 rows: 35 against 54 us for K = 11008, but 24 against 15 us for K = 2048, where the
+    // hand-over and reduction of 128 x 256 partial tiles costs more than the shorter chain saves: long K only)
+    if (infer && plain && max_m > BM && max_m <= 1024 && mid >= 1 && min_nkb >= 64) {
       const int splits = skinny_splits(mid, min_nkb, num_sms());
       if (splits >= 2) {
         GemmArgs sargs;
