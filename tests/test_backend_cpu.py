@@ -142,3 +142,30 @@ def test_index_entry_points_and_reference_module_paths():
     p1, d1 = rb.get_rope_index(ids, None, None, None, am, 2, 900, 901, 902, 2.0)
     p2, d2 = ro.get_rope_index(ids, None, None, None, am, 2, 900, 901, 902, 2.0)
     assert torch.equal(p1, p2) and torch.equal(d1, d2)
+
+
+def test_inference_kernel_region_needs_both_the_region_and_grad_mode_off():
+    """Launches may pick inference-only kernels only inside an ``inference_kernels`` region with autograd off: grad mode
+    alone says nothing (autograd functions run forward and backward with it off)."""
+    import torch
+
+    from wallx_b200.ops import gemm as G
+
+    assert not G._inference_launch()
+    with torch.no_grad():
+        assert not G._inference_launch()
+        with G.inference_kernels():
+            assert G._inference_launch()
+            with G.inference_kernels():  # re-entrant
+                assert G._inference_launch()
+            assert G._inference_launch()
+        assert not G._inference_launch()
+    with G.inference_kernels():
+        assert not G._inference_launch()  # autograd on: a training step
+
+    @G.inference_kernels()
+    def f():
+        with torch.no_grad():
+            return G._inference_launch()
+
+    assert f() and not G._inference_launch()

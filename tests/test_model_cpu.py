@@ -177,6 +177,9 @@ def test_flow_sampler_with_prefix_cache_equals_full_recompute(setup):
             "proprioception", "agent_pos_mask", "dataset_names", "dof_mask", "image_grid_host", "pack_index", "seq_lens")
     sampler = FlowSampler(model, **{k: batch[k] for k in keys})
     n = 4
+    # the host knows that the suffix rows are all action tokens and the prefix rows are not: both passes run one expert as
+    # a plain FFN, and the comparison below is against the grouped two-expert path
+    assert sampler.ctx.plan.single_expert == 1 and sampler.ctx_pre.plan.single_expert == 0
     x_fast = sampler.sample(noise, num_steps=n)
 
     # oracle: full sequence every evaluation (the reference's procedure)
