@@ -34,14 +34,17 @@ def test_few_row_gemm_matches_fp32_and_the_general_kernel(M, N, K):
     again = G.gemm(a, w, bias=bias, residual=res, force_bn=16)
     single = G.gemm(a, w, bias=bias, residual=res, force_bn=17)
     wide = G.gemm(a, w, bias=bias, residual=res, force_bn=64)
-    auto = G.gemm(a, w, bias=bias, residual=res)
+    train = G.gemm(a, w, bias=bias, residual=res)
+    with torch.no_grad(), G.inference_kernels():
+        auto = G.gemm(a, w, bias=bias, residual=res)
     torch.cuda.synchronize()
     G.check_status()
     _close(split, ref, 1e-2, what="few-row gemm, K split over a cluster")
     _close(single, ref, 1e-2, what="few-row gemm, one CTA per column tile")
     assert torch.equal(single, wide), "few-row kernel (no split) and 64-wide tiles differ"
     assert torch.equal(split, again), "the sum over the cluster depends on timing"
-    assert torch.equal(split, auto)
+    assert torch.equal(split, auto), "inference launches split K"
+    assert torch.equal(single, train), "training launches do not"
 
 
 @pytest.mark.parametrize("M,N,K", [(314, 2048, 11008), (200, 2560, 4096), (972, 1280, 4160), (1024, 2048, 8192),

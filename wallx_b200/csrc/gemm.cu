@@ -873,8 +873,8 @@ int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* sta
   // force_bn = 18 is "automatic, inference": it also lets problems of up to 1024 rows whose 128 x 256 tiles fill less
   // than half of the SMs and whose K is 4096 or more run on K-splitting clusters (prefix passes: few tiles, long K, one
   // serial chain per tile).
-  // Training launches (0) never take that second path, so its different summation order cannot enter a comparison
-  // of training runs.
+  // Training launches (0) take neither that second path nor a K split of the few-row kernel, so a different summation
+  // order cannot enter a comparison of training runs.
   const bool infer = force_bn == 18;
   if (infer) force_bn = 0;
   if (!a_mn && !b_mn && (force_bn == 0 || force_bn == 16 || force_bn == 17)) {
@@ -895,7 +895,9 @@ int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* sta
       const int a_rows = skinny_rows(max_m);
       const int src = fill_args(sargs, calls, ncalls, kSkinnyBN, a_rows);
       if (src != 0) return src;
-      const int splits = force_bn == 17 ? 1 : skinny_splits(st, min_nkb, num_sms());
+      // K is split over a cluster for inference launches only: a training launch must give the bits of the general
+      // kernel (the fused-gather GEMM of a row-sharded weight is that kernel, and the plans are compared bit for bit)
+      const int splits = (infer || force_bn == 16) ? skinny_splits(st, min_nkb, num_sms()) : 1;
       return launch_skinny(sargs, a_rows, kSkinnyBN, static_cast<int>(st), splits, stream, status);
     }
     if (force_bn == 16 || force_bn == 17) return -11;

@@ -35,15 +35,22 @@ DEFAULT_PULLERS = int(_os.environ.get("WALLX_AG_PULLERS", "8"))
 _PULLERS_FROM_ENV = "WALLX_AG_PULLERS" in _os.environ
 
 
+STANDALONE_PULLERS = 16
+
+
 def auto_pullers(specs: Sequence[G.GemmSpec], weights: Sequence[GatheredWeight]) -> int:
-    """Copy CTAs for a launch: enough that the remote rows arrive within the multiplication's own time. A copy CTA
-    moves about 60 GB/s and should run at half of that to stay ahead of the tiles; never fewer than the default
-    (start-up of the gather is latency-bound), never more than 32 (every copy CTA is an SM the GEMM does not get)."""
+    """Copy CTAs for a launch. Weights of a training engine take the default (8: measured best inside the step, where
+    most backward gathers ride on the weight-gradient GEMMs and every copy CTA is an SM the multiplication does not
+    get). A stand-alone :class:`ShardedWeight` has nothing else to hide its gather behind: at least 16 (measured on the
+    dual-expert FFN at 2K-32K tokens: 16 beat 8 and 14 everywhere), more when the multiplication is too short for the
+    remote rows to arrive within it at about 30 GB/s per copy CTA, at most 32."""
+    if not all(isinstance(w, ShardedWeight) for w in weights):
+        return DEFAULT_PULLERS
     flops = sum(2.0 * s.M * s.N * s.K for s in specs)
     remote = sum(2.0 * w.rows * w.cols * (w.world - 1) / max(w.world, 1) for w in weights)
     t = max(flops / 1.2e15, 1e-6)
     n = int(-(-remote // (t * 30e9)))
-    n = max(DEFAULT_PULLERS, min(32, n))
+    n = max(STANDALONE_PULLERS, min(32, n))
     return (n + 1) & ~1
 
 
