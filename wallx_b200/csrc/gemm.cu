@@ -903,7 +903,11 @@ int gemm_launch(const GemmCall* calls, int ncalls, cudaStream_t stream, int* sta
     if (force_bn == 16 || force_bn == 17) return -11;
     // (measured in CUDA graphs at 314 rows: 35 against 54 us for K = 11008, but 24 against 15 us for K = 2048, where the
     // hand-over and reduction of 128 x 256 partial tiles costs more than the shorter chain saves: long K only)
-    if (infer && plain && max_m > BM && max_m <= 1024 && mid >= 1 && min_nkb >= 64) {
+    static const int mid_min_nkb = [] {
+      const char* e = getenv("WX_MID_MIN_NKB");
+      return e ? atoi(e) : 64;
+    }();
+    if (infer && plain && max_m > BM && max_m <= 1024 && mid >= 1 && min_nkb >= mid_min_nkb) {
       const int splits = skinny_splits(mid, min_nkb, num_sms());
       if (splits >= 2) {
         GemmArgs sargs;

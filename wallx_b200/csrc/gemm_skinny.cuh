@@ -237,15 +237,31 @@ gemm_skinny_kernel(const __grid_constant__ GemmArgs args, int* __restrict__ stat
 #pragma unroll
       for (int e = 0; e < 32; ++e) v[e] = 0.f;
       const uint32_t off = static_cast<uint32_t>((r * C::PITCH + c * 32) * 4);
-      for (int s = 0; s < splits; ++s) {
-        const uint32_t base = mapa_u32(partial_addr + off, static_cast<uint32_t>(s));
+      // two CTAs' pieces are requested before either is added (16 loads in flight); the sums keep the rank order
+      for (int s = 0; s < splits; s += 2) {
+        const bool two = s + 1 < splits;
+        const uint32_t base0 = mapa_u32(partial_addr + off, static_cast<uint32_t>(s));
+        const uint32_t base1 = mapa_u32(partial_addr + off, static_cast<uint32_t>(two ? s + 1 : s));
+        float4 x0[8], x1[8];
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4) x0[q4] = ld_cluster_f32x4(base0 + 16 * q4);
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4) x1[q4] = two ? ld_cluster_f32x4(base1 + 16 * q4) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int q4 = 0; q4 < 8; ++q4) {
-          const float4 x = ld_cluster_f32x4(base + 16 * q4);
-          v[4 * q4] += x.x;
-          v[4 * q4 + 1] += x.y;
-          v[4 * q4 + 2] += x.z;
-          v[4 * q4 + 3] += x.w;
+          v[4 * q4] += x0[q4].x;
+          v[4 * q4 + 1] += x0[q4].y;
+          v[4 * q4 + 2] += x0[q4].z;
+          v[4 * q4 + 3] += x0[q4].w;
+        }
+        if (two) {
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4) {
+            v[4 * q4] += x1[q4].x;
+            v[4 * q4 + 1] += x1[q4].y;
+            v[4 * q4 + 2] += x1[q4].z;
+            v[4 * q4 + 3] += x1[q4].w;
+          }
         }
       }
       long drow = static_cast<long>(m0) + r;
