@@ -342,7 +342,7 @@ def _zero3_worker(rank, world, port, tmp, clip):
 
 
 @pytest.mark.timeout(600)
-@pytest.mark.parametrize("world", [1, 2, 4])
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
 def test_row_sharded_parameters_train_like_resident_ones(tmp_path, world):
     """ZeRO-3 storage (rows of every weight per rank, whole-gradient reduction onto the owner's rows, AdamW on the
     rows, refresh by collective) gives bit-identical parameters to the resident plan when no clipping interferes:
