@@ -169,3 +169,28 @@ def test_inference_kernel_region_needs_both_the_region_and_grad_mode_off():
             return G._inference_launch()
 
     assert f() and not G._inference_launch()
+
+
+def test_copy_cta_count_for_fused_gathers():
+    """Weights of a training engine take the default count; stand-alone sharded weights at least 16, more when the
+    multiplication is short against the bytes that must arrive, never more than 32, always even."""
+    from wallx_b200.parallel import ag_linear as A
+    from wallx_b200.parallel.zero3 import GatheredWeight
+
+    class Spec:
+        def __init__(self, M, N, K):
+            self.M, self.N, self.K = M, N, K
+
+    def standalone(rows, cols, world):
+        w = A.ShardedWeight.__new__(A.ShardedWeight)
+        w.rows, w.cols, w.world = rows, cols, world
+        return w
+
+    engine_w = GatheredWeight(2048, 2048, 2, 0, [], None, None)
+    assert A.auto_pullers([Spec(4096, 2048, 2048)], [engine_w]) == A.DEFAULT_PULLERS
+    big = A.auto_pullers([Spec(32768, 22016, 2048)], [standalone(22016, 2048, 8)])
+    small = A.auto_pullers([Spec(256, 22016, 2048)], [standalone(22016, 2048, 8)])
+    assert big == A.STANDALONE_PULLERS
+    assert A.STANDALONE_PULLERS < small <= 32 and small % 2 == 0
+    # a mix of engine and stand-alone weights in one launch is an engine launch
+    assert A.auto_pullers([Spec(256, 64, 64), Spec(256, 64, 64)], [engine_w, standalone(64, 64, 2)]) == A.DEFAULT_PULLERS
