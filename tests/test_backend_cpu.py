@@ -170,6 +170,21 @@ def test_inference_kernel_region_needs_both_the_region_and_grad_mode_off():
 
     assert f() and not G._inference_launch()
 
+    # the region belongs to the thread that opened it
+    import threading
+
+    seen = []
+
+    def other():
+        with torch.no_grad():
+            seen.append(G._inference_launch())
+
+    with torch.no_grad(), G.inference_kernels():
+        t = threading.Thread(target=other)
+        t.start()
+        t.join()
+    assert seen == [False]
+
 
 def test_copy_cta_count_for_fused_gathers():
     """Weights of a training engine take the default count; stand-alone sharded weights at least 16, more when the

@@ -50,7 +50,9 @@ class GemmSpec:
 INFERENCE_AUTO = 18  # "choose the tile shape, inference": also allows K-splitting clusters for prefix-sized problems
 
 
-_inference_depth = 0
+import threading as _threading
+
+_region = _threading.local()  # per thread: an inference region of one thread says nothing about another thread's launches
 
 
 class inference_kernels:
@@ -59,13 +61,11 @@ class inference_kernels:
     Grad mode cannot serve as the signal: autograd functions run both their forward and their backward with it off."""
 
     def __enter__(self):
-        global _inference_depth
-        _inference_depth += 1
+        _region.depth = getattr(_region, "depth", 0) + 1
         return self
 
     def __exit__(self, *exc):
-        global _inference_depth
-        _inference_depth -= 1
+        _region.depth = getattr(_region, "depth", 1) - 1
         return False
 
     def __call__(self, fn):
@@ -80,7 +80,7 @@ class inference_kernels:
 
 
 def _inference_launch() -> bool:
-    return _inference_depth > 0 and not torch.is_grad_enabled()
+    return getattr(_region, "depth", 0) > 0 and not torch.is_grad_enabled()
 
 
 def launch(specs: Sequence[GemmSpec], force_bn: int = 0) -> None:
